@@ -1,0 +1,141 @@
+// Device-side primitives shared by the sm_100a kernels of this library.
+//
+// Everything here is register-level: 16-byte global accesses with cache hints, bf16 pair
+// packing, the E4M3 / UE8M0 (MXFP8) conversions, fixed-order warp reductions and the
+// IEEE-only exp used where an integer decision depends on a transcendental.  No kernel in
+// this library is a dense contraction, so there is no tensor-core code.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cstdint>
+
+namespace k3g {
+
+struct V8 { unsigned w[4]; };   // eight bf16 = one 16-byte vector
+
+// ---- global memory, 16 bytes at a time -------------------------------------------------
+// Streaming loads: read once through the non-coherent path, not allocated in L1.
+__device__ __forceinline__ V8 ld_stream(const void* p) {
+  V8 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+  return v;
+}
+// Plain (possibly remote / coherent) load: used for peer memory that another GPU wrote.
+__device__ __forceinline__ V8 ld_plain(const void* p) {
+  V8 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+  return v;
+}
+// Cached read-only load (small tables reused by every row: gamma, taps).
+__device__ __forceinline__ V8 ld_keep(const void* p) {
+  const uint4 t = __ldg((const uint4*)p);
+  V8 v; v.w[0] = t.x; v.w[1] = t.y; v.w[2] = t.z; v.w[3] = t.w;
+  return v;
+}
+__device__ __forceinline__ void st_stream(void* p, const V8& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};"
+               :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");
+}
+__device__ __forceinline__ void st_stream8(void* p, unsigned a, unsigned b) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" :: "l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void st_plain(void* p, const V8& v) {
+  *(uint4*)p = make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]);
+}
+
+// ---- bf16 pairs ---------------------------------------------------------------------------
+__device__ __forceinline__ float bf_lo(unsigned u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf_hi(unsigned u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ unsigned pack_bf2(float lo, float hi) {   // one cvt.rn.bf16x2.f32
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&h);
+}
+__device__ __forceinline__ __nv_bfloat162 as_bf2(unsigned u) { return *reinterpret_cast<const __nv_bfloat162*>(&u); }
+__device__ __forceinline__ unsigned from_bf2(__nv_bfloat162 h) { return *reinterpret_cast<const unsigned*>(&h); }
+// bf16x2 product / sum with one round-to-nearest-even per element (mul.rn / add.rn .bf16x2).
+__device__ __forceinline__ unsigned mul_bf2(unsigned a, unsigned b) { return from_bf2(__hmul2(as_bf2(a), as_bf2(b))); }
+__device__ __forceinline__ unsigned add_bf2(unsigned a, unsigned b) { return from_bf2(__hadd2(as_bf2(a), as_bf2(b))); }
+__device__ __forceinline__ unsigned absmax_bf2(unsigned m, unsigned x) {
+  return from_bf2(__hmax2(as_bf2(m), __habs2(as_bf2(x))));
+}
+__device__ __forceinline__ float land_bf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ---- fixed-order reductions --------------------------------------------------------------
+template <int LANES>
+__device__ __forceinline__ float butterfly_sum(float v) {
+#pragma unroll
+  for (int o = LANES / 2; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- MXFP8: E4M3 codes with one UE8M0 exponent per 32 elements ---------------------------
+// e = smallest integer with 448 * 2^e >= amax (0 when amax == 0), clamped to [-127, 127];
+// amax arrives as the bf16 bit pattern of a non-negative value.
+__device__ __forceinline__ int ue8m0_exp_from_bf16(unsigned amax_bf16) {
+  const unsigned E = (amax_bf16 >> 7) & 0xffu, man = amax_bf16 & 0x7fu;
+  int e = (int)E - 135 + (man > 0x60u ? 1 : 0);       // 448 = 1.75 * 2^8; 0x60 = fraction of 1.75
+  if (E == 0) e = -127;
+  e = max(e, -127);
+  if ((amax_bf16 & 0x7fffu) == 0) e = 0;
+  return e;                                           // bf16 magnitudes never reach e > 120
+}
+__device__ __forceinline__ float pow2_neg(int e) { return __uint_as_float((unsigned)(127 - e) << 23); }
+
+// two / four floats -> packed E4M3, round-to-nearest-even, saturating (cvt.rn.satfinite.e4m3x2.f32)
+__device__ __forceinline__ unsigned e4m3x2(float lo, float hi) {
+  return (unsigned)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ unsigned e4m3x4(float a, float b, float c, float d) {
+  return e4m3x2(a, b) | (e4m3x2(c, d) << 16);
+}
+// Eight bf16 (one V8) scaled by s (a power of two) -> eight E4M3 codes in two words.
+__device__ __forceinline__ void quant8(const V8& x, float s, unsigned& q0, unsigned& q1) {
+  q0 = e4m3x4(__fmul_rn(bf_lo(x.w[0]), s), __fmul_rn(bf_hi(x.w[0]), s),
+              __fmul_rn(bf_lo(x.w[1]), s), __fmul_rn(bf_hi(x.w[1]), s));
+  q1 = e4m3x4(__fmul_rn(bf_lo(x.w[2]), s), __fmul_rn(bf_hi(x.w[2]), s),
+              __fmul_rn(bf_lo(x.w[3]), s), __fmul_rn(bf_hi(x.w[3]), s));
+}
+// |max| over the eight bf16 of a vector, as a bf16 bit pattern.
+__device__ __forceinline__ unsigned absmax8(const V8& x) {
+  unsigned m = from_bf2(__habs2(as_bf2(x.w[0])));
+  m = absmax_bf2(m, x.w[1]);
+  m = absmax_bf2(m, x.w[2]);
+  m = absmax_bf2(m, x.w[3]);
+  const __nv_bfloat162 h = as_bf2(m);
+  const __nv_bfloat16 r = __hmax(__low2bfloat16(h), __high2bfloat16(h));
+  return (unsigned)__bfloat16_as_ushort(r);
+}
+__device__ __forceinline__ unsigned max_bf16_bits(unsigned a, unsigned b) { return a > b ? a : b; }  // non-negative bf16: bit order = value order
+
+// ---- deterministic exp / sigmoid (IEEE operations only) ---------------------------------
+// Same operation sequence as the host-side check uses; no approximate instruction, so the
+// top-k selection that depends on it is reproducible bit for bit on any IEEE machine.
+__device__ __forceinline__ float det_exp(float x) {
+  x = fminf(fmaxf(x, -80.0f), 80.0f);
+  const float t = __fmul_rn(x, 1.44269502162933349609375f);
+  const float n = rintf(t);
+  float f = __fmaf_rn(n, -0.693145751953125f, x);
+  f = __fmaf_rn(n, -1.42860676533018704503775e-06f, f);
+  float p = 1.98756915e-4f;
+  p = __fmaf_rn(p, f, 1.39819995e-3f);
+  p = __fmaf_rn(p, f, 8.33345205e-3f);
+  p = __fmaf_rn(p, f, 4.16657962e-2f);
+  p = __fmaf_rn(p, f, 1.66666657e-1f);
+  p = __fmaf_rn(p, f, 5.00000000e-1f);
+  p = __fmaf_rn(p, f, 1.0f);
+  p = __fmaf_rn(p, f, 1.0f);
+  return __uint_as_float(__float_as_uint(p) + ((unsigned)(int)n << 23));
+}
+__device__ __forceinline__ float det_sigmoid(float s) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, det_exp(-s))); }
+
+// Fast sigmoid for bf16-landed results: one ex2.approx and one rcp.approx.
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
+
+}  // namespace k3g

@@ -1,0 +1,140 @@
+// bf16 -> FP8 quantisation kernels.
+//
+//   kern_k3_moe_quant        MXFP8: E4M3 codes + one UE8M0 exponent per 32 consecutive elements
+//                            (replaces xiaguan/kern-k3 source/k3_moe_prefill_v4.cu:111-140)
+//   kern_quant_fp8_amax_v2   per-tensor pair: partial |max| per block            (replaces
+//   kern_quant_fp8_apply_v2  scale = amax / 448, y = e4m3(x / scale)              source/k3_quant_fp8_pair_v2.cu:42-95)
+//
+// MXFP8 layout: a thread owns one 16-byte vector (8 elements); the four threads of a group
+// are adjacent lanes, so the group amax is two xor-shuffles, every load is a coalesced 16 B
+// and every code store a coalesced 8 B.  The exponent is computed on the bf16 bits of amax
+// (exact integer arithmetic, no log2).
+//
+// Per-tensor pair: the amax pass walks the tensor forwards with ordinary (L2-allocating)
+// loads and the apply pass walks it backwards, so the tail the first pass left in the 126 MB
+// L2 is what the second pass reads first.
+#include "k3g_device.cuh"
+#include "k3g_host.h"
+
+using namespace k3g;
+
+extern "C" __global__ void __launch_bounds__(256) kern_k3_moe_quant(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                                                   uint8_t* __restrict__ sf, int rows, int cols) {
+  const long long nvec = (long long)rows * cols / 8;           // cols % 32 == 0: groups never straddle rows
+  const long long stride = (long long)gridDim.x * blockDim.x;  // a multiple of 32: groups stay lane-aligned
+  const int lane = threadIdx.x & 31;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x; i0 < nvec; i0 += stride) {
+    const long long i = i0 + threadIdx.x;
+    const bool live = i < nvec;                                // nvec % 4 == 0: a group is live or dead as a whole
+    V8 v = {{0u, 0u, 0u, 0u}};
+    if (live) v = ld_stream(x + i * 8);
+    unsigned am = absmax8(v);
+    am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    const int e = ue8m0_exp_from_bf16(am);
+    unsigned q0, q1;
+    quant8(v, pow2_neg(e), q0, q1);
+    unsigned sfb = (unsigned)(e + 127);
+    sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+    sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+    if (live) {
+      st_stream8(q + i * 8, q0, q1);
+      if ((lane & 15) == 0) {
+        // four scale bytes; the tail of the tensor may hold fewer than four groups
+        const long long g = i >> 2, ng = nvec >> 2;
+        if (g + 4 <= ng && ((reinterpret_cast<uintptr_t>(sf) + g) & 3) == 0) {
+          *reinterpret_cast<unsigned*>(sf + g) = sfb;
+        } else {
+          for (int k = 0; k < 4 && g + k < ng; ++k) sf[g + k] = (uint8_t)(sfb >> (8 * k));
+        }
+      }
+    }
+  }
+}
+
+#define K3G_QT 256
+
+__device__ __forceinline__ unsigned block_max_u32(unsigned m) {
+  __shared__ unsigned s[K3G_QT / 32];
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = m;
+  __syncthreads();
+  unsigned r = 0;
+#pragma unroll
+  for (int w = 0; w < K3G_QT / 32; ++w) r = max(r, s[w]);
+  __syncthreads();
+  return r;
+}
+
+// partials[b] = max |x| over block b's slice, as f32.  |bf16| ordering = unsigned ordering of
+// the low 15 bits, so the maximum is taken on bit patterns (exact, order-free).
+extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_amax_v2(const __nv_bfloat16* __restrict__ x, int n,
+                                                                           float* __restrict__ partials) {
+  const uint4* p = reinterpret_cast<const uint4*>(x);
+  const int nv = n >> 3;
+  unsigned m2 = 0;   // two 15-bit maxima, packed like the data
+  for (int i = blockIdx.x * K3G_QT + threadIdx.x; i < nv; i += gridDim.x * K3G_QT) {
+    const uint4 v = p[i];
+    m2 = __vmaxu2(m2, v.x & 0x7fff7fffu);
+    m2 = __vmaxu2(m2, v.y & 0x7fff7fffu);
+    m2 = __vmaxu2(m2, v.z & 0x7fff7fffu);
+    m2 = __vmaxu2(m2, v.w & 0x7fff7fffu);
+  }
+  unsigned m = max(m2 & 0xffffu, m2 >> 16);
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7))
+    m = max(m, (unsigned)__bfloat16_as_ushort(x[nv * 8 + threadIdx.x]) & 0x7fffu);
+  m = block_max_u32(m);
+  if (threadIdx.x == 0) partials[blockIdx.x] = __uint_as_float(m << 16);
+}
+
+extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_apply_v2(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, int n,
+                                                                            const float* __restrict__ partials, int nb,
+                                                                            float* __restrict__ scale_out) {
+  unsigned m = 0;   // partials are non-negative floats: bit order = value order
+  for (int b = threadIdx.x; b < nb; b += K3G_QT) m = max(m, __float_as_uint(partials[b]));
+  const float amax = __uint_as_float(block_max_u32(m));
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = scale;
+  const float inv = __fdiv_rn(1.f, scale);
+
+  const int nv = n >> 3;
+  const int total = gridDim.x * K3G_QT;
+  // backwards: start with the part of x the amax pass touched last
+  for (int i = nv - 1 - (blockIdx.x * K3G_QT + threadIdx.x); i >= 0; i -= total) {
+    const V8 v = ld_stream(x + (size_t)i * 8);
+    unsigned q0, q1;
+    quant8(v, inv, q0, q1);
+    st_stream8(y + (size_t)i * 8, q0, q1);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const int i = nv * 8 + threadIdx.x;
+    y[i] = (uint8_t)(e4m3x2(__fmul_rn(__bfloat162float(x[i]), inv), 0.f) & 0xffu);
+  }
+}
+
+#ifndef K3G_CUBIN_ONLY
+K3G_API int k3g_moe_quant(const void* x, void* q, void* sf, int rows, int cols, int grid_hint, void* stream) {
+  K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(q); K3G_REQUIRE_PTR(sf);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE(((uintptr_t)q & 7) == 0, K3G_EALIGN);
+  K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
+  const long long nvec = (long long)rows * cols / 8;
+  if (nvec == 0) return K3G_OK;
+  long long grid = (nvec + 255) / 256;
+  if (grid_hint > 0 && grid_hint < grid) grid = grid_hint;
+  K3G_REQUIRE(grid <= 0x7fffffffLL, K3G_ELIMIT);
+  kern_k3_moe_quant<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)sf, rows, cols);
+  return k3g_launch_status();
+}
+
+// op `quant_fp8_tensor` of the reference manifest: both launches share one grid width, and
+// partials must hold that many floats.
+K3G_API int k3g_quant_fp8_tensor(const void* x, void* y, void* scale_out, void* partials, int n, int grid, void* stream) {
+  K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(y); K3G_REQUIRE_PTR(partials);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE(((uintptr_t)y & 7) == 0, K3G_EALIGN);
+  K3G_REQUIRE(n >= 0 && grid > 0, K3G_ESHAPE);
+  kern_quant_fp8_amax_v2<<<grid, K3G_QT, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, n, (float*)partials);
+  kern_quant_fp8_apply_v2<<<grid, K3G_QT, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (uint8_t*)y, n, (const float*)partials,
+                                                                  grid, (float*)scale_out);
+  return k3g_launch_status();
+}
+#endif

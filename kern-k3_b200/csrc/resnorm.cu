@@ -1,0 +1,445 @@
+// Residual stream of K3 prefill: landing add, attention-residual mix, RMSNorm, and the
+// fused MXFP8 epilogue.
+//
+// Replaces, behind the same entry names and parameter lists, the kernels of
+// xiaguan/kern-k3 source/k3_residual_v2.cu:
+//   kern_k3_attnres_rms           (:260-284)   K1a
+//   kern_k3_land_add_attnres_rms  (:295-345)   K1b (bf16 or f32 landing)
+//   kern_k3_land_add2             (:349-392)   K1c
+// and adds the fusion the reference runs as separate launches:
+//   k3g_resnorm_mxfp8_kernel: residual + delta -> residual_out (bf16), RMSNorm * gamma,
+//   then the MXFP8 quantisation of source/k3_moe_prefill_v4.cu:111-140 on the normed row
+//   while it is still in registers, so every activation byte crosses HBM once.
+//
+// Geometry.  A row of H = 1024 * VPT bf16 is owned by a team of 128 threads; thread t owns
+// the 16-byte vectors t + 128 v, v < VPT.  That is the assignment the reference's fixed-order
+// reduction is defined on (serial fma chain per thread, xor-butterfly per warp, the four
+// warp partials summed in order), so sums -- and through them the bf16 normed row and the
+// UE8M0 scales -- do not depend on how rows are scheduled.  A 32-element MXFP8 group is
+// four consecutive vectors, i.e. four adjacent lanes: its amax is two xor-shuffles.
+// All row traffic is 16-byte, coalesced, streaming (evict-first); the 14 KB gamma row stays
+// cached.  One block = one team; the grid walks rows with stride gridDim.x, so both the
+// reference launch (grid = rows) and a persistent launch are valid.
+#include "k3g_device.cuh"
+#include "k3g_host.h"
+
+namespace k3g {
+
+constexpr int kTeam = 128;
+constexpr int kNbMax = 8;
+
+template <int VPT>
+__device__ __forceinline__ float team_sumsq(const V8 (&x)[VPT], float* s_red, int lane, int warp) {
+  float sq = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = bf_lo(x[v].w[j]), hi = bf_hi(x[v].w[j]);
+      sq = __fmaf_rn(lo, lo, sq);
+      sq = __fmaf_rn(hi, hi, sq);
+    }
+  }
+  sq = butterfly_sum<32>(sq);
+  if (lane == 0) s_red[warp] = sq;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < kTeam / 32; ++w) tot = __fadd_rn(tot, s_red[w]);
+  return tot;
+}
+
+// RMSNorm of the team's row x (bf16 in registers) with optional MXFP8 epilogue.
+//   normed = bf16(bf16(x * r) * gamma),  r = rsqrt_rn(fma(sum x^2, 1/H, eps))
+template <int VPT, bool STORE_NORMED, bool QUANT>
+__device__ __forceinline__ void team_rms_store(const V8 (&x)[VPT], const __nv_bfloat16* __restrict__ gamma,
+                                               __nv_bfloat16* __restrict__ normed_row, uint8_t* __restrict__ q_row,
+                                               uint8_t* __restrict__ sf_row, float eps, float* s_red, int t) {
+  constexpr int H = VPT * 1024;
+  const int lane = t & 31, warp = t >> 5;
+  const float tot = team_sumsq<VPT>(x, s_red, lane, warp);
+  const float r = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int u = (t + v * kTeam) * 8;
+    const V8 g = ld_keep(gamma + u);
+    V8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(x[v].w[j]), r), __fmul_rn(bf_hi(x[v].w[j]), r)), g.w[j]);
+    if (STORE_NORMED) st_stream(normed_row + u, o);
+    if (QUANT) {
+      unsigned am = absmax8(o);
+      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
+      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
+      const int e = ue8m0_exp_from_bf16(am);
+      unsigned q0, q1;
+      quant8(o, pow2_neg(e), q0, q1);
+      st_stream8(q_row + u, q0, q1);
+      // the warp's eight scale bytes: lanes 0 and 16 each store four
+      unsigned sfb = (unsigned)(e + 127);
+      sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+      sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+      if ((lane & 15) == 0) *reinterpret_cast<unsigned*>(sf_row + (u >> 5)) = sfb;
+    }
+  }
+}
+
+// Attention-residual mix of source/k3_residual_v2.cu:122-223: candidates 0..nb-1 are the
+// snapshot rows, candidate nb is the prefix row held in x (overwritten with the mix).
+template <int VPT>
+__device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat16* __restrict__ blk_row,
+                                                 const float* __restrict__ sw, int nb, float eps, float* s_mix, int t) {
+  constexpr int H = VPT * 1024;
+  constexpr int NW = kTeam / 32;
+  const int lane = t & 31, warp = t >> 5;
+  const int ncand = nb + 1;
+  // pass 1: (sum x^2, sum x*sw) per candidate, candidate by candidate (same per-thread order)
+  for (int c = 0; c < ncand; ++c) {
+    float sq = 0.f, dp = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int u = (t + v * kTeam) * 8;
+      const V8 cv = (c < nb) ? ld_plain(blk_row + (size_t)c * H + u) : x[v];
+      const float4 a = __ldg((const float4*)(sw + u)), b = __ldg((const float4*)(sw + u + 4));
+      const float s8[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf_lo(cv.w[j]), hi = bf_hi(cv.w[j]);
+        sq = __fmaf_rn(lo, lo, sq);  sq = __fmaf_rn(hi, hi, sq);
+        dp = __fmaf_rn(lo, s8[2 * j], dp);  dp = __fmaf_rn(hi, s8[2 * j + 1], dp);
+      }
+    }
+    sq = butterfly_sum<32>(sq);
+    dp = butterfly_sum<32>(dp);
+    if (lane == 0) { s_mix[(2 * c) * NW + warp] = sq; s_mix[(2 * c + 1) * NW + warp] = dp; }
+  }
+  __syncthreads();
+  float sc = -3.0e38f;
+  if (lane < ncand) {
+    float sqv = 0.f, dpv = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      sqv = __fadd_rn(sqv, s_mix[(2 * lane) * NW + w]);
+      dpv = __fadd_rn(dpv, s_mix[(2 * lane + 1) * NW + w]);
+    }
+    sc = __fmul_rn(dpv, __frsqrt_rn(__fmaf_rn(sqv, 1.0f / (float)H, eps)));
+  }
+  float mx = sc;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const float ex = (lane < ncand) ? det_exp(__fadd_rn(sc, -mx)) : 0.f;
+  const float den = butterfly_sum<32>(ex);
+  const float pmine = __fdiv_rn(ex, den);
+  const float pp = __shfl_sync(0xffffffffu, pmine, nb);
+  __syncthreads();   // s_mix is reused by the next row of a persistent launch
+  // pass 2: mixed = bf16(p_prefix * x + sum_c p_c * cand_c), candidates ascending
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    const int u = (t + v * kTeam) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[2 * j] = __fmul_rn(pp, bf_lo(x[v].w[j]));
+      acc[2 * j + 1] = __fmul_rn(pp, bf_hi(x[v].w[j]));
+    }
+    for (int c = 0; c < nb; ++c) {
+      const float pc = __shfl_sync(0xffffffffu, pmine, c);
+      const V8 cv = ld_plain(blk_row + (size_t)c * H + u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = __fmaf_rn(pc, bf_lo(cv.w[j]), acc[2 * j]);
+        acc[2 * j + 1] = __fmaf_rn(pc, bf_hi(cv.w[j]), acc[2 * j + 1]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[v].w[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
+  }
+}
+
+// ---- fused residual add + RMSNorm + MXFP8 ------------------------------------------------
+template <int VPT, bool STORE_NORMED>
+__global__ void __launch_bounds__(kTeam, 4) resnorm_mxfp8_kernel(
+    const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta,
+    const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ residual_out,
+    uint8_t* __restrict__ q, uint8_t* __restrict__ sf, __nv_bfloat16* __restrict__ normed, int rows, float eps) {
+  constexpr int H = VPT * 1024;
+  __shared__ float s_red[2][kTeam / 32];
+  const int t = threadIdx.x;
+  int it = 0;
+  for (int b = blockIdx.x; b < rows; b += gridDim.x, ++it) {
+    const size_t base = (size_t)b * H;
+    V8 a[VPT], d[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) a[v] = ld_stream(residual + base + (t + v * kTeam) * 8);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) d[v] = ld_stream(delta + base + (t + v * kTeam) * 8);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[v].w[j] = add_bf2(a[v].w[j], d[v].w[j]);
+      st_stream(residual_out + base + (t + v * kTeam) * 8, a[v]);
+    }
+    team_rms_store<VPT, STORE_NORMED, true>(a, gamma, STORE_NORMED ? normed + base : nullptr, q + base,
+                                             sf + (size_t)b * (H / 32), eps, s_red[it & 1], t);
+  }
+}
+
+// ---- K1a ----------------------------------------------------------------------------------
+template <int VPT>
+__device__ __forceinline__ void attnres_rms_body(const __nv_bfloat16* __restrict__ prefix, __nv_bfloat16* __restrict__ blocks,
+                                                 const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma,
+                                                 __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps) {
+  constexpr int H = VPT * 1024;
+  __shared__ float s_red[2][kTeam / 32];
+  __shared__ float s_mix[(kNbMax + 1) * 2 * (kTeam / 32)];
+  const int t = threadIdx.x;
+  int it = 0;
+  for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
+    const size_t base = (size_t)b * H;
+    V8 x[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) x[v] = ld_stream(prefix + base + (t + v * kTeam) * 8);
+    __nv_bfloat16* blk_row = blocks + (size_t)b * kNbMax * H;
+    if (snapshot && nb < kNbMax) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) st_plain(blk_row + (size_t)nb * H + (t + v * kTeam) * 8, x[v]);
+    }
+    if (nb > 0) team_attnres_mix<VPT>(x, blk_row, sw, nb, eps, s_mix, t);
+    team_rms_store<VPT, true, false>(x, gamma, normed + base, nullptr, nullptr, eps, s_red[it & 1], t);
+  }
+}
+
+// ---- K1b ----------------------------------------------------------------------------------
+template <int VPT, bool LAND_BF16>
+__device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix,
+                                                          const __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
+                                                          const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,
+                                                          __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps) {
+  constexpr int H = VPT * 1024;
+  __shared__ float s_red[2][kTeam / 32];
+  __shared__ float s_mix[(kNbMax + 1) * 2 * (kTeam / 32)];
+  const int t = threadIdx.x;
+  int it = 0;
+  for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
+    const size_t base = (size_t)b * H;
+    V8 x[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const size_t off = base + (t + v * kTeam) * 8;
+      V8 p;
+      if (LAND_BF16) {
+        p = ld_stream((const __nv_bfloat16*)partial + off);
+      } else {
+        const V8 f0 = ld_stream((const float*)partial + off), f1 = ld_stream((const float*)partial + off + 4);
+        p.w[0] = pack_bf2(__uint_as_float(f0.w[0]), __uint_as_float(f0.w[1]));
+        p.w[1] = pack_bf2(__uint_as_float(f0.w[2]), __uint_as_float(f0.w[3]));
+        p.w[2] = pack_bf2(__uint_as_float(f1.w[0]), __uint_as_float(f1.w[1]));
+        p.w[3] = pack_bf2(__uint_as_float(f1.w[2]), __uint_as_float(f1.w[3]));
+      }
+      if (snapshot) {
+        x[v] = p;
+      } else {
+        const V8 pr = ld_stream(prefix + off);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr.w[j], p.w[j]);
+      }
+      st_stream(prefix2 + off, x[v]);
+    }
+    if (nb > 0) team_attnres_mix<VPT>(x, blocks + (size_t)b * kNbMax * H, sw, nb, eps, s_mix, t);
+    team_rms_store<VPT, true, false>(x, gamma, normed + base, nullptr, nullptr, eps, s_red[it & 1], t);
+  }
+}
+
+// ---- K1c ----------------------------------------------------------------------------------
+template <int VPT, bool LAND_BF16>
+__device__ __forceinline__ void land_add2_body(const void* __restrict__ p1, const void* __restrict__ p2,
+                                               const __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ hidden,
+                                               int two, int B) {
+  constexpr int H = VPT * 1024;
+  const int t = threadIdx.x;
+  for (int b = blockIdx.x; b < B; b += gridDim.x) {
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const size_t off = (size_t)b * H + (t + v * kTeam) * 8;
+      const V8 pr = ld_stream(prefix2 + off);
+      float l1[8], l2[8];
+      if (LAND_BF16) {
+        const V8 a = ld_stream((const __nv_bfloat16*)p1 + off);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { l1[2 * j] = bf_lo(a.w[j]); l1[2 * j + 1] = bf_hi(a.w[j]); }
+        if (two) {
+          const V8 c = ld_stream((const __nv_bfloat16*)p2 + off);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { l2[2 * j] = bf_lo(c.w[j]); l2[2 * j + 1] = bf_hi(c.w[j]); }
+        }
+      } else {
+        const V8 a0 = ld_stream((const float*)p1 + off), a1 = ld_stream((const float*)p1 + off + 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { l1[j] = land_bf(__uint_as_float(a0.w[j])); l1[4 + j] = land_bf(__uint_as_float(a1.w[j])); }
+        if (two) {
+          const V8 c0 = ld_stream((const float*)p2 + off), c1 = ld_stream((const float*)p2 + off + 4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { l2[j] = land_bf(__uint_as_float(c0.w[j])); l2[4 + j] = land_bf(__uint_as_float(c1.w[j])); }
+        }
+      }
+      V8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float x = __fadd_rn(bf_lo(pr.w[j]), l1[2 * j]), y = __fadd_rn(bf_hi(pr.w[j]), l1[2 * j + 1]);
+        if (two) { x = __fadd_rn(x, l2[2 * j]); y = __fadd_rn(y, l2[2 * j + 1]); }
+        o.w[j] = pack_bf2(x, y);
+      }
+      st_stream(hidden + off, o);
+    }
+  }
+}
+
+}  // namespace k3g
+
+using namespace k3g;
+
+// ---- manifest entry points (reference ABI; H = 7168 and eps = 1e-5 are build constants
+//      there: source/k3_residual_v2.cu:51-54) ------------------------------------------------
+#ifndef K3G_RES_VPT
+#define K3G_RES_VPT 7
+#endif
+#ifndef K3G_RES_EPS
+#define K3G_RES_EPS 1e-5f
+#endif
+
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms(
+    const __nv_bfloat16* __restrict__ prefix, __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
+    const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B) {
+  attnres_rms_body<K3G_RES_VPT>(prefix, blocks, sw, gamma, normed, nb, snapshot, B, K3G_RES_EPS);
+}
+
+#if defined(K3G_CUBIN_ONLY)
+// one landing dtype per module, as in the reference (-DLAND_BF16 selects bf16)
+#ifdef LAND_BF16
+typedef __nv_bfloat16 k3g_land_t;
+#define K3G_LAND_IS_BF16 true
+#else
+typedef float k3g_land_t;
+#define K3G_LAND_IS_BF16 false
+#endif
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rms(
+    const k3g_land_t* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix, const __nv_bfloat16* __restrict__ blocks,
+    const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,
+    __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B) {
+  land_add_attnres_rms_body<K3G_RES_VPT, K3G_LAND_IS_BF16>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, K3G_RES_EPS);
+}
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add2(
+    const k3g_land_t* __restrict__ p1, const k3g_land_t* __restrict__ p2, const __nv_bfloat16* __restrict__ prefix2,
+    __nv_bfloat16* __restrict__ hidden, int two, int B) {
+  land_add2_body<K3G_RES_VPT, K3G_LAND_IS_BF16>(p1, p2, prefix2, hidden, two, B);
+}
+#else
+
+// ---- library build: width- and dtype-generic kernels behind the C ABI ----------------------
+template <int VPT>
+__global__ void __launch_bounds__(128, 4) attnres_rms_kernel(const __nv_bfloat16* prefix, __nv_bfloat16* blocks, const float* sw,
+                                                            const __nv_bfloat16* gamma, __nv_bfloat16* normed, int nb, int snapshot, int B, float eps) {
+  attnres_rms_body<VPT>(prefix, blocks, sw, gamma, normed, nb, snapshot, B, eps);
+}
+template <int VPT, bool LB>
+__global__ void __launch_bounds__(128, 4) land_add_attnres_rms_kernel(const void* partial, const __nv_bfloat16* prefix, const __nv_bfloat16* blocks,
+                                                                     const float* sw, const __nv_bfloat16* gamma, __nv_bfloat16* prefix2,
+                                                                     __nv_bfloat16* normed, int nb, int snapshot, int B, float eps) {
+  land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps);
+}
+template <int VPT, bool LB>
+__global__ void __launch_bounds__(128, 4) land_add2_kernel(const void* p1, const void* p2, const __nv_bfloat16* prefix2,
+                                                          __nv_bfloat16* hidden, int two, int B) {
+  land_add2_body<VPT, LB>(p1, p2, prefix2, hidden, two, B);
+}
+
+#define K3G_DISPATCH_VPT(H, ...)                           \
+  switch ((H) / 1024) {                                    \
+    case 1: { constexpr int VPT = 1; __VA_ARGS__; } break; \
+    case 2: { constexpr int VPT = 2; __VA_ARGS__; } break; \
+    case 4: { constexpr int VPT = 4; __VA_ARGS__; } break; \
+    case 7: { constexpr int VPT = 7; __VA_ARGS__; } break; \
+    case 8: { constexpr int VPT = 8; __VA_ARGS__; } break; \
+    default: return K3G_ESHAPE;                            \
+  }
+
+static inline int res_grid(int rows, int grid_hint) { return grid_hint > 0 ? (grid_hint < rows ? grid_hint : rows) : rows; }
+
+K3G_API int k3g_resnorm_mxfp8(const void* residual, const void* delta, const void* gamma, void* residual_out, void* q,
+                              void* sf, void* normed_opt, int rows, int H, float eps, int grid_hint, void* stream) {
+  K3G_REQUIRE_PTR(residual); K3G_REQUIRE_PTR(delta); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(residual_out);
+  K3G_REQUIRE_PTR(q); K3G_REQUIRE_PTR(sf);
+  K3G_REQUIRE_ALIGNED(residual); K3G_REQUIRE_ALIGNED(delta); K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(residual_out);
+  K3G_REQUIRE_ALIGNED(q); K3G_REQUIRE_ALIGNED(sf); K3G_REQUIRE_ALIGNED(normed_opt);
+  K3G_REQUIRE(rows >= 0 && H > 0 && H % 1024 == 0, K3G_ESHAPE);
+  if (rows == 0) return K3G_OK;
+  const int grid = res_grid(rows, grid_hint);
+  K3G_DISPATCH_VPT(H, {
+    if (normed_opt)
+      resnorm_mxfp8_kernel<VPT, true><<<grid, kTeam, 0, k3g_stream(stream)>>>(
+          (const __nv_bfloat16*)residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)residual_out,
+          (uint8_t*)q, (uint8_t*)sf, (__nv_bfloat16*)normed_opt, rows, eps);
+    else
+      resnorm_mxfp8_kernel<VPT, false><<<grid, kTeam, 0, k3g_stream(stream)>>>(
+          (const __nv_bfloat16*)residual, (const __nv_bfloat16*)delta, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)residual_out,
+          (uint8_t*)q, (uint8_t*)sf, nullptr, rows, eps);
+  });
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_attnres_rms(const void* prefix, void* blocks, const void* sw, const void* gamma, void* normed, int nb,
+                            int snapshot, int B, int H, float eps, void* stream) {
+  K3G_REQUIRE_PTR(prefix); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(normed);
+  K3G_REQUIRE(nb >= 0 && nb <= kNbMax, K3G_ERANGE);
+  if (nb > 0 || snapshot) K3G_REQUIRE_PTR(blocks);
+  if (nb > 0) K3G_REQUIRE_PTR(sw);
+  K3G_REQUIRE_ALIGNED(prefix); K3G_REQUIRE_ALIGNED(blocks); K3G_REQUIRE_ALIGNED(sw); K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(normed);
+  K3G_REQUIRE(B >= 0 && H > 0 && H % 1024 == 0, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  K3G_DISPATCH_VPT(H, (attnres_rms_kernel<VPT><<<B, kTeam, 0, k3g_stream(stream)>>>(
+      (const __nv_bfloat16*)prefix, (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed,
+      nb, snapshot, B, eps)));
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_land_add_attnres_rms(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+                                     const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
+                                     int B, int H, float eps, void* stream) {
+  K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(prefix2); K3G_REQUIRE_PTR(normed);
+  if (!snapshot) K3G_REQUIRE_PTR(prefix);
+  K3G_REQUIRE(nb >= 0 && nb <= kNbMax, K3G_ERANGE);
+  if (nb > 0) { K3G_REQUIRE_PTR(blocks); K3G_REQUIRE_PTR(sw); }
+  K3G_REQUIRE_ALIGNED(partial); K3G_REQUIRE_ALIGNED(prefix); K3G_REQUIRE_ALIGNED(blocks); K3G_REQUIRE_ALIGNED(sw);
+  K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(prefix2); K3G_REQUIRE_ALIGNED(normed);
+  K3G_REQUIRE(B >= 0 && H > 0 && H % 1024 == 0, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  if (partial_is_bf16) {
+    K3G_DISPATCH_VPT(H, (land_add_attnres_rms_kernel<VPT, true><<<B, kTeam, 0, k3g_stream(stream)>>>(
+        partial, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma,
+        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps)));
+  } else {
+    K3G_DISPATCH_VPT(H, (land_add_attnres_rms_kernel<VPT, false><<<B, kTeam, 0, k3g_stream(stream)>>>(
+        partial, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma,
+        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps)));
+  }
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_land_add2(const void* p1, const void* p2, int partial_is_bf16, const void* prefix2, void* hidden, int two,
+                          int B, int H, void* stream) {
+  K3G_REQUIRE_PTR(p1); K3G_REQUIRE_PTR(prefix2); K3G_REQUIRE_PTR(hidden);
+  if (two) K3G_REQUIRE_PTR(p2);
+  K3G_REQUIRE_ALIGNED(p1); K3G_REQUIRE_ALIGNED(p2); K3G_REQUIRE_ALIGNED(prefix2); K3G_REQUIRE_ALIGNED(hidden);
+  K3G_REQUIRE(B >= 0 && H > 0 && H % 1024 == 0, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  if (partial_is_bf16) {
+    K3G_DISPATCH_VPT(H, (land_add2_kernel<VPT, true><<<B, kTeam, 0, k3g_stream(stream)>>>(p1, p2, (const __nv_bfloat16*)prefix2,
+                                                                                         (__nv_bfloat16*)hidden, two, B)));
+  } else {
+    K3G_DISPATCH_VPT(H, (land_add2_kernel<VPT, false><<<B, kTeam, 0, k3g_stream(stream)>>>(p1, p2, (const __nv_bfloat16*)prefix2,
+                                                                                          (__nv_bfloat16*)hidden, two, B)));
+  }
+  return k3g_launch_status();
+}
+#endif  // K3G_CUBIN_ONLY

@@ -64,6 +64,118 @@ int k3g_moe_quant(const void* x, void* q, void* sf, int rows, int cols, int grid
  * (op quant_fp8_tensor): per-tensor E4M3; partials holds `grid` floats. */
 int k3g_quant_fp8_tensor(const void* x, void* y, void* scale_out, void* partials, int n, int grid, void* stream);
 
+/* ---- router and MoE routing ------------------------------------------------------------------ */
+
+/* kern_k3_router_topk, source/k3_router_argmax.cu:87 (op router_topk).  experts must be 224; topk 8 or
+ * 16.  idx/wts are [B, topk] in pick order.  The sigmoid is evaluated with IEEE-only operations. */
+int k3g_router_topk(const void* S, const void* bias, const void* rs, void* idx, void* wts, int B, int experts,
+                    int topk, void* stream);
+
+/* kern_k3_moe_route_count, source/k3_moe_prefill_v4.cu:142 (op moe_route_count).  E local experts;
+ * placement strided (id % ep_ranks == rank, slot id / ep_ranks) or blocked (source :100-109). */
+int k3g_moe_route_count(const void* ids, int T, int rank, int E, int topk, int ep_ranks, int strided, void* blockcount,
+                        void* stream);
+
+/* kern_k3_moe_route_tables, source/k3_moe_prefill_v4.cu:159 (op moe_route_tables). */
+int k3g_moe_route_tables(const void* blockcount, int blocks, int E, int tile, void* blockoff, void* cta_batch,
+                         void* cta_limit, void* num_non_exiting, void* total_padded, void* route_map, void* stream);
+
+/* kern_k3_moe_route_scatter, source/k3_moe_prefill_v4.cu:205 (op moe_route_scatter). */
+int k3g_moe_route_scatter(const void* ids, const void* blockoff, int T, int rank, int E, int topk, int ep_ranks,
+                          int strided, void* route_map, void* exp2perm, void* stream);
+
+/* kern_k3_moe_finalize, source/k3_moe_prefill_v4.cu:254 (op moe_finalize). */
+int k3g_moe_finalize(const void* fc2, const void* exp2perm, const void* wts, void* out, int T, int cols, int topk,
+                     void* stream);
+
+/* Finalize fused with the one-partial residual add of kern_k3_land_add2 (source/k3_residual_v2.cu:349,
+ * two = 0): out = bf16(residual + bf16(sum_k w * fc2[row_k])).  Benchmark configuration 2 combine. */
+int k3g_finalize_residual(const void* fc2, const void* exp2perm, const void* wts, const void* residual, void* out, int T,
+                          int cols, int topk, void* stream);
+
+/* Dispatch gather (benchmark configuration 2): out row r = row route_map[r] of the MXFP8 token rows
+ * (q [*, cols] codes, sf [*, cols/32] scales).  The reference leaves this gather to its grouped GEMM,
+ * which reads route_map (source/k3_moe_prefill_v4.cu:36-46). */
+int k3g_permute_gather(const void* q, const void* sf, const void* route_map, long long rows, int cols, void* out_q,
+                       void* out_sf, void* stream);
+
+/* ---- collectives over NVLink peer pointers ---------------------------------------------------- */
+/* Peer tables (`*_peer`) are device arrays of u64 addresses, one per rank, own rank included, as the
+ * reference's runtime provides them (scripts/gen_collectives_p2p.py:77-86).  `flags` is this rank's
+ * u64 counter table: flags[0] the epoch, flags[slot >= 1] one counter per collective call site.
+ * `status` (device, 4 x u32, may be null) receives {1, slot, peer, observed} when a wait expires. */
+
+/* kern_k3_flags_init, source/k3_collectives.cu:64 (op k3_flags_init). */
+int k3g_flags_init(void* flags, int n, void* stream);
+
+/* kern_k3_epoch_bump, source/k3_collectives.cu:74 (op k3_epoch_bump): flags[0] += units. */
+int k3g_epoch_bump(void* flags, int units, void* stream);
+
+/* kern_k3_rs_arrive1, source/k3_rs_arrive_v2.cu:41 (ops k3_allgather_push and the first launch of
+ * k3_reducescatter_bf16): flags[slot] += units, then wait for every peer's flags[slot] >= flags[0]. */
+int k3g_rs_arrive(void* flags, const void* flags_peer, int units, int slot, int nranks, long long timeout_us, void* status,
+                  void* stream);
+
+/* kern_k3_rs_pull, source/k3_reducescatter_pull_nr4.cu:124 (second launch of k3_reducescatter_bf16).
+ * order = 2 * ownpos + descend (source/k3_collectives.cu:222-236); 2 * (nranks - 1) is the ring order. */
+int k3g_rs_pull(const void* src, void* dst, const void* src_peer, long long count, int order, int rank, int nranks, int grid,
+                void* stream);
+
+/* kern_k3_allgather4_push, source/k3_allgather4_v3.cu:61 (op k3_allgather4_push).  Launches `units`
+ * blocks; every block contributes one arrival, so `units` must be the epoch increment. */
+int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long long n0, const void* s1, void* d1, const void* p1,
+                        long long n1, const void* s2, void* d2, const void* p2, long long n2, const void* s3, void* d3,
+                        const void* p3, long long n3, void* flags, const void* flags_peer, int slot, int rank, int nranks,
+                        int units, long long timeout_us, void* status, void* stream);
+
+/* Fused reduce-scatter -> residual add -> RMSNorm -> MXFP8 -> all-gather (benchmark configuration 1):
+ * kern_k3_rs_pull + kern_k3_land_add_attnres_rms (nb = 0) + kern_k3_moe_quant + the all-gather push of
+ * kern_k3_attnres_rms_push (source/k3_residual_push_add2.cu:356-360) in one kernel.  Bracket it with
+ * k3g_rs_arrive before (partials ready) and after (pushes landed). */
+int k3g_rs_resnorm_mxfp8_ag(const void* partial, const void* partial_peer, const void* residual, const void* gamma,
+                            void* residual_out, void* q_all, const void* q_all_peer, void* sf_all, const void* sf_all_peer,
+                            int rows, int H, float eps, int rank, int nranks, int grid_hint, void* stream);
+
+/* Status of the last expired wait of a launch that had no status pointer (host_status: 4 x u32). */
+int k3g_wait_status(void* host_status, int clear, void* stream);
+
+/* Set-up helpers standing in for the reference's external runtime (allocation + peer mapping with CUDA
+ * IPC, one process per GPU).  These allocate / synchronise; handles are 64 bytes. */
+int k3g_peer_alloc(long long bytes, void** host_out_dptr);
+int k3g_peer_free(void* dptr);
+int k3g_peer_export(void* dptr, void* host_handle64);
+int k3g_peer_open(const void* host_handle64, void** host_out_dptr);
+int k3g_peer_close(void* dptr);
+/* Returns the SM count of the current device (> 0); host_cc receives major * 10 + minor. */
+int k3g_device_sms(int* host_cc);
+
+/* ---- MLA prep ----------------------------------------------------------------------------------- */
+
+/* kern_k3_mla_prep_head + kern_k3_mla_prep_gate, source/k3_mla_prep_v2.cu:130,91 (op mla_prep; bf16
+ * partial as in source/k3_mla_prep_bf16.cu).  mla_gate may be null (head only). */
+int k3g_mla_prep(const void* partial, int partial_is_bf16, const void* gamma_q, const void* gamma_kv, const void* slot_mapping,
+                 void* slab, long long layer_off, long long page_stride, void* q_norm, void* mla_gate, int B, int inner,
+                 float eps, void* stream);
+
+/* Benchmark configuration 3: latent RMSNorm + RoPE on the rope slices of q and k + k_rope broadcast into
+ * the packed k buffer.  rope_tab [T, 64] bf16 = cos(32) | sin(32) (table convention of
+ * source/weight_prep.cu:34-45); half-split pairing.  No counterpart kernel in the reference. */
+int k3g_mla_prep_rope_pack(const void* kv, const void* q, const void* gamma_kv, const void* rope_tab, void* q_out, void* k_out,
+                           void* latent_out, int T, int heads, float eps, void* stream);
+
+/* ---- KDA -------------------------------------------------------------------------------------------- */
+
+/* kern_k3_span_gather, source/k3_span_gather_v3.cu:251 (op span_gather_v2), with the window passed
+ * directly instead of through the KDA state line. */
+int k3g_span_gather(const void* partial, long long row_stride, const void* cw, int taps_bf16, void* win, const void* wsm_partial,
+                    void* span_q, void* span_k, void* span_v, void* span_beta, void* span_flow, int heads, int at, int span,
+                    int rows_per_block, void* stream);
+
+/* kern_k3_kda_out_gate, source/k3_kda_out_gate_v3.cu:36 (op kda_out_gate_v2), optionally with the
+ * MXFP8 epilogue of benchmark configuration 4. */
+int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_stride, long long gate_off, const void* gamma_o,
+                     void* gated, void* q, void* sf, int heads, int at, int span, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,304 @@
+// KDA glue: causal depthwise conv (width 4) + SiLU on the q/k/v streams, and the output gate
+// (per-head RMSNorm x sigmoid(gate)) with an optional fused MXFP8 epilogue.
+//
+// Replaces, behind the same entry names and parameter lists, xiaguan/kern-k3
+//   kern_k3_span_gather    source/k3_span_gather_v3.cu:251-293 (row math :131-142, window :236-248)
+//   kern_k3_kda_out_gate   source/k3_kda_out_gate_v3.cu:36-118
+//
+// span conv.  Stream s in {q,k,v}; x_i[c] = partial[(at + i) * row_stride + s * inner + c], rows
+// i < 0 come from the stored 3-row window; y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-2}, w1,
+// x_{i-3} * w0))); sb = bf16(y); out = bf16(sb * sigmoid(sb)); the new window is the last three
+// INPUT rows.  A thread owns 8 consecutive columns (one 16-byte vector) and walks a run of rows
+// with the three previous inputs sliding in registers, four row loads in flight at a time;
+// rows per block = ceil(span / gridDim.z), so the reference launch (16 rows) and a coarser one
+// (fewer halo re-reads) are both valid.  The sigmoid is ex2.approx + rcp.approx, as in the
+// reference: two MUFU ops per element is what a 6.5 TB/s stream leaves room for.
+//
+// output gate.  16 lanes per head, 8 consecutive d per lane: ss = fma chain, xor-butterfly over
+// the 16 lanes, r = rsqrt(fma(ss, 1/128, eps)); o = bf16((a * r) * gamma_o); gt = bf16(sigmoid(g));
+// gated = bf16(o * gt).  A 32-element MXFP8 group is four lanes of one head.
+#include "k3g_device.cuh"
+#include "k3g_host.h"
+
+using namespace k3g;
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const V8& v, float* x) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { x[2 * j] = bf_lo(v.w[j]); x[2 * j + 1] = bf_hi(v.w[j]); }
+}
+
+template <bool TAPS_BF16>
+__device__ __forceinline__ void load_taps(const void* cw, size_t off, float* w) {
+  if (TAPS_BF16) {
+    unpack8(ld_keep(reinterpret_cast<const __nv_bfloat16*>(cw) + off), w);
+  } else {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(cw) + off));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(cw) + off + 4));
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  }
+}
+
+__device__ __forceinline__ V8 conv_silu_row(const float* t0, const float* t1, const float* t2, const float* x, const float (*w)[8]) {
+  V8 o;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float y[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int k = 2 * j + h;
+      float a = __fmul_rn(t0[k], w[0][k]);
+      a = __fmaf_rn(t1[k], w[1][k], a);
+      a = __fmaf_rn(t2[k], w[2][k], a);
+      y[h] = __fmaf_rn(x[k], w[3][k], a);
+    }
+    const unsigned sbp = pack_bf2(y[0], y[1]);
+    const float s0 = bf_lo(sbp), s1 = bf_hi(sbp);
+    o.w[j] = pack_bf2(s0 * fast_sigmoid(s0), s1 * fast_sigmoid(s1));
+  }
+  return o;
+}
+
+constexpr int kChunk = 4;
+
+template <bool TAPS_BF16>
+__device__ __forceinline__ void span_stream(const __nv_bfloat16* __restrict__ partial, long long row_stride, const void* __restrict__ cw,
+                                            __nv_bfloat16* win, __nv_bfloat16* __restrict__ out, int inner, int s, int c, int row0,
+                                            int row1, int span) {
+  float w[4][8];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) load_taps<TAPS_BF16>(cw, ((size_t)s * 4 + t) * inner + c, w[t]);
+  const __nv_bfloat16* col = partial + (size_t)s * inner + c;
+  const bool first = row0 == 0;
+  float x[kChunk + 3][8];
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    const int i = row0 - 3 + t;
+    unpack8(i < 0 ? ld_plain(win + (size_t)(i + 3) * inner + c) : ld_stream(col + (size_t)i * row_stride), x[t]);
+  }
+  for (int r0 = row0; r0 < row1; r0 += kChunk) {
+    V8 raw[kChunk];
+#pragma unroll
+    for (int r = 0; r < kChunk; ++r)
+      if (r0 + r < row1) raw[r] = ld_stream(col + (size_t)(r0 + r) * row_stride);
+#pragma unroll
+    for (int r = 0; r < kChunk; ++r)
+      if (r0 + r < row1) unpack8(raw[r], x[3 + r]);
+#pragma unroll
+    for (int r = 0; r < kChunk; ++r)
+      if (r0 + r < row1) st_stream(out + (size_t)(r0 + r) * inner + c, conv_silu_row(x[r], x[r + 1], x[r + 2], x[r + 3], w));
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) x[t][k] = x[kChunk + t][k];
+  }
+  if (first) {
+    // new window = inputs span-3 .. span-1 (old window rows when span < 3); this thread has
+    // already read every old tap it needs, and no other thread touches these columns
+    V8 nw[3];
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+      const int i = span - 3 + t;
+      nw[t] = i < 0 ? ld_plain(win + (size_t)(i + 3) * inner + c) : ld_stream(col + (size_t)i * row_stride);
+    }
+#pragma unroll
+    for (int t = 0; t < 3; ++t) st_plain(win + (size_t)t * inner + c, nw[t]);
+  }
+}
+
+// beta transpose + flow landing for the rows of one block
+__device__ __forceinline__ void span_beta_flow(const float* __restrict__ wsm, int heads, __nv_bfloat16* __restrict__ span_beta,
+                                               __nv_bfloat16* __restrict__ span_flow, int row0, int row1, int span) {
+  const int R = row1 - row0;
+  for (int idx = threadIdx.x; idx < R * heads; idx += blockDim.x) {
+    const int h = idx / R, i = row0 + idx % R;
+    span_beta[(size_t)h * span + i] = __float2bfloat16_rn(wsm[(size_t)i * 256 + h]);
+  }
+  for (int idx = threadIdx.x; idx < R * 32; idx += blockDim.x) {
+    const int i = row0 + idx / 32, c4 = (idx % 32) * 4;
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(wsm + (size_t)i * 256 + 96 + c4));
+    *reinterpret_cast<uint2*>(span_flow + (size_t)i * 128 + c4) = make_uint2(pack_bf2(v.x, v.y), pack_bf2(v.z, v.w));
+  }
+}
+
+// grid (ceil(inner / 1024), 4, row chunks), block 128: y < 3 = stream, y == 3 = beta/flow (optional)
+template <bool TAPS_BF16>
+__device__ __forceinline__ void span_gather_body(const __nv_bfloat16* __restrict__ partial, long long row_stride, const void* __restrict__ cw,
+                                                 __nv_bfloat16* win_base, const float* __restrict__ wsm_partial, __nv_bfloat16* span_q,
+                                                 __nv_bfloat16* span_k, __nv_bfloat16* span_v, __nv_bfloat16* span_beta,
+                                                 __nv_bfloat16* span_flow, int heads, int at, int span) {
+  const int inner = heads * 128;
+  const int rpb = (span + gridDim.z - 1) / gridDim.z;
+  const int row0 = blockIdx.z * rpb, row1 = min(span, row0 + rpb);
+  if (row0 >= span) return;
+  if (blockIdx.y == 3) {
+    if (blockIdx.x == 0 && wsm_partial) span_beta_flow(wsm_partial + (size_t)at * 256, heads, span_beta, span_flow, row0, row1, span);
+    return;
+  }
+  const int s = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= inner) return;
+  __nv_bfloat16* out = s == 0 ? span_q : s == 1 ? span_k : span_v;
+  span_stream<TAPS_BF16>(partial + (size_t)at * row_stride, row_stride, cw, win_base + (size_t)s * 3 * inner, out, inner, s, c, row0, row1,
+                         span);
+}
+
+template <bool TAPS_BF16>
+__global__ void __launch_bounds__(128) span_conv_kernel(const __nv_bfloat16* partial, long long row_stride, const void* cw, __nv_bfloat16* win,
+                                                        const float* wsm_partial, __nv_bfloat16* span_q, __nv_bfloat16* span_k,
+                                                        __nv_bfloat16* span_v, __nv_bfloat16* span_beta, __nv_bfloat16* span_flow,
+                                                        int heads, int at, int span) {
+  span_gather_body<TAPS_BF16>(partial, row_stride, cw, win, wsm_partial, span_q, span_k, span_v, span_beta, span_flow, heads, at, span);
+}
+
+// ---- output gate -----------------------------------------------------------------------------------
+template <bool STORE_GATED, bool QUANT>
+__device__ __forceinline__ void out_gate_body(const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ gate,
+                                              long long gate_stride, long long gate_off, const float* __restrict__ gamma_o,
+                                              __nv_bfloat16* __restrict__ gated, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                              int heads, int at, int span, float eps) {
+  const int inner = heads * 128;
+  const int tpr = heads * 16;                                  // threads per row
+  const long long total = (long long)span * tpr;
+  const long long nthreads = (long long)gridDim.x * gridDim.y * blockDim.x;
+  const int lane = threadIdx.x & 31;
+  const long long first = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * blockDim.x;
+  for (long long base = first; base < total; base += nthreads) {   // block-uniform trip count; tpr % 32 == 0 keeps warps whole
+    const long long g = base + threadIdx.x;
+    const bool live = g < total;
+    const long long i = live ? g / tpr : 0;
+    const int col = live ? (int)(g - i * tpr) * 8 : 0;
+    const long long b = at + i;
+    V8 av = {{0u, 0u, 0u, 0u}}, gv = {{0u, 0u, 0u, 0u}};
+    if (live) {
+      av = ld_stream(attn + (size_t)i * inner + col);
+      gv = ld_stream(gate + (size_t)b * gate_stride + gate_off + col);
+    }
+    float a[8], gg[8], gm[8];
+    unpack8(av, a);
+    unpack8(gv, gg);
+    const int d0 = col & 127;
+    const float4 m0 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0)), m1 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0 + 4));
+    gm[0] = m0.x; gm[1] = m0.y; gm[2] = m0.z; gm[3] = m0.w; gm[4] = m1.x; gm[5] = m1.y; gm[6] = m1.z; gm[7] = m1.w;
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss = __fmaf_rn(a[k], a[k], ss);
+    ss = butterfly_sum<16>(ss);
+    const float r = __frsqrt_rn(__fmaf_rn(ss, 1.0f / 128.0f, eps));
+    V8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned ov = pack_bf2(__fmul_rn(__fmul_rn(a[2 * j], r), gm[2 * j]), __fmul_rn(__fmul_rn(a[2 * j + 1], r), gm[2 * j + 1]));
+      const unsigned gt = pack_bf2(fast_sigmoid(gg[2 * j]), fast_sigmoid(gg[2 * j + 1]));
+      o.w[j] = mul_bf2(ov, gt);
+    }
+    if (STORE_GATED && live) st_stream(gated + (size_t)b * inner + col, o);
+    if (QUANT) {
+      unsigned am = absmax8(o);
+      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
+      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
+      const int e = ue8m0_exp_from_bf16(am);
+      unsigned q0, q1;
+      quant8(o, pow2_neg(e), q0, q1);
+      unsigned sfb = (unsigned)(e + 127);
+      sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+      sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+      if (live) {
+        st_stream8(q + (size_t)b * inner + col, q0, q1);
+        if ((lane & 15) == 0) *reinterpret_cast<unsigned*>(sf + (((size_t)b * inner + col) >> 5)) = sfb;
+      }
+    }
+  }
+}
+
+template <bool STORE_GATED, bool QUANT>
+__global__ void __launch_bounds__(256) out_gate_kernel(const __nv_bfloat16* attn, const __nv_bfloat16* gate, long long gate_stride,
+                                                       long long gate_off, const float* gamma_o, __nv_bfloat16* gated, uint8_t* q,
+                                                       uint8_t* sf, int heads, int at, int span, float eps) {
+  out_gate_body<STORE_GATED, QUANT>(attn, gate, gate_stride, gate_off, gamma_o, gated, q, sf, heads, at, span, eps);
+}
+
+}  // namespace
+
+// ---- manifest entry points (HEADS is a build constant there) -------------------------------------
+#ifndef HEADS
+#define HEADS 24
+#endif
+#define K3G_KDA_INNER (HEADS * 128)
+#define K3G_KDA_REC_BYTES ((long long)HEADS * 128 * 128 * 4)
+
+extern "C" __global__ void __launch_bounds__(128) kern_k3_span_gather(
+    const __nv_bfloat16* __restrict__ partial, const float* __restrict__ cw, void* __restrict__ kda_base, const int* __restrict__ line_index,
+    long long line_bytes, const float* __restrict__ wsm_partial, __nv_bfloat16* __restrict__ span_q, __nv_bfloat16* __restrict__ span_k,
+    __nv_bfloat16* __restrict__ span_v, __nv_bfloat16* __restrict__ span_beta, __nv_bfloat16* __restrict__ span_flow,
+    const int* __restrict__ span_at, int span) {
+  const int at = span_at[0];
+  // the window rows live in the sequence's KDA state line, after the recurrent state
+  __nv_bfloat16* win = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(kda_base) + (long long)line_index[at] * line_bytes + K3G_KDA_REC_BYTES);
+  span_gather_body<false>(partial, 4LL * K3G_KDA_INNER, cw, win, wsm_partial, span_q, span_k, span_v, span_beta, span_flow, HEADS, at, span);
+}
+
+extern "C" __global__ void __launch_bounds__(128) kern_k3_kda_out_gate(const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ gate_partial,
+                                                                      const float* __restrict__ gamma_o, __nv_bfloat16* __restrict__ gated,
+                                                                      const int* __restrict__ span_at, int span) {
+  out_gate_body<true, false>(attn, gate_partial, 4LL * K3G_KDA_INNER, 3LL * K3G_KDA_INNER, gamma_o, gated, nullptr, nullptr, HEADS, span_at[0],
+                             span, 1e-5f);
+}
+
+#ifndef K3G_CUBIN_ONLY
+// Conv + SiLU on the three streams.  win: [3 streams][3 rows][inner] bf16, read as the initial
+// state and overwritten with the final one (zero-fill it for a zero initial state).  cw:
+// [3][4][inner] taps, f32 or bf16.  wsm_partial (f32 [rows, 256]) may be null: then span_beta /
+// span_flow are not produced.  rows_per_block <= 0 selects 32.
+K3G_API int k3g_span_gather(const void* partial, long long row_stride, const void* cw, int taps_bf16, void* win, const void* wsm_partial,
+                            void* span_q, void* span_k, void* span_v, void* span_beta, void* span_flow, int heads, int at, int span,
+                            int rows_per_block, void* stream) {
+  K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(cw); K3G_REQUIRE_PTR(win); K3G_REQUIRE_PTR(span_q); K3G_REQUIRE_PTR(span_k); K3G_REQUIRE_PTR(span_v);
+  if (wsm_partial) { K3G_REQUIRE_PTR(span_beta); K3G_REQUIRE_PTR(span_flow); K3G_REQUIRE_ALIGNED(wsm_partial); }
+  K3G_REQUIRE_ALIGNED(partial); K3G_REQUIRE_ALIGNED(cw); K3G_REQUIRE_ALIGNED(win); K3G_REQUIRE_ALIGNED(span_q); K3G_REQUIRE_ALIGNED(span_k);
+  K3G_REQUIRE_ALIGNED(span_v);
+  K3G_REQUIRE(heads > 0 && heads <= 512 && span >= 0 && at >= 0 && row_stride >= 3LL * heads * 128 && row_stride % 8 == 0, K3G_ESHAPE);
+  if (span == 0) return K3G_OK;
+  const int rpb = rows_per_block > 0 ? rows_per_block : 32;
+  const int inner = heads * 128;
+  const dim3 grid((inner + 1023) / 1024, wsm_partial ? 4 : 3, (span + rpb - 1) / rpb);
+  K3G_REQUIRE(grid.z <= 65535, K3G_ELIMIT);
+  if (taps_bf16)
+    span_conv_kernel<true><<<grid, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)partial, row_stride, cw, (__nv_bfloat16*)win,
+                                                                (const float*)wsm_partial, (__nv_bfloat16*)span_q, (__nv_bfloat16*)span_k,
+                                                                (__nv_bfloat16*)span_v, (__nv_bfloat16*)span_beta, (__nv_bfloat16*)span_flow,
+                                                                heads, at, span);
+  else
+    span_conv_kernel<false><<<grid, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)partial, row_stride, cw, (__nv_bfloat16*)win,
+                                                                 (const float*)wsm_partial, (__nv_bfloat16*)span_q, (__nv_bfloat16*)span_k,
+                                                                 (__nv_bfloat16*)span_v, (__nv_bfloat16*)span_beta, (__nv_bfloat16*)span_flow,
+                                                                 heads, at, span);
+  return k3g_launch_status();
+}
+
+// Output gate.  gate element (row b, column c) = gate[b * gate_stride + gate_off + c].  gated may be
+// null when only the MXFP8 form is wanted; q / sf may be null when only bf16 is wanted.
+K3G_API int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_stride, long long gate_off, const void* gamma_o,
+                             void* gated, void* q, void* sf, int heads, int at, int span, float eps, void* stream) {
+  K3G_REQUIRE_PTR(attn); K3G_REQUIRE_PTR(gate); K3G_REQUIRE_PTR(gamma_o);
+  K3G_REQUIRE(gated != nullptr || (q != nullptr && sf != nullptr), K3G_ENULL);
+  K3G_REQUIRE((q == nullptr) == (sf == nullptr), K3G_ENULL);
+  K3G_REQUIRE_ALIGNED(attn); K3G_REQUIRE_ALIGNED(gate); K3G_REQUIRE_ALIGNED(gamma_o); K3G_REQUIRE_ALIGNED(gated);
+  K3G_REQUIRE(((uintptr_t)q & 7) == 0 && ((uintptr_t)sf & 3) == 0, K3G_EALIGN);
+  K3G_REQUIRE(heads > 0 && heads % 2 == 0 && span >= 0 && at >= 0 && gate_stride % 8 == 0 && gate_off % 8 == 0, K3G_ESHAPE);
+  if (span == 0) return K3G_OK;
+  const long long total = (long long)span * heads * 16;
+  const long long blocks = (total + 255) / 256;
+  K3G_REQUIRE(blocks <= 0x7fffffffLL, K3G_ELIMIT);
+  const dim3 grid((unsigned)blocks, 1, 1);
+  cudaStream_t st = k3g_stream(stream);
+#define K3G_OG_ARGS (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, gate_stride, gate_off, (const float*)gamma_o, \
+    (__nv_bfloat16*)gated, (uint8_t*)q, (uint8_t*)sf, heads, at, span, eps
+  if (gated && q) out_gate_kernel<true, true><<<grid, 256, 0, st>>>(K3G_OG_ARGS);
+  else if (gated) out_gate_kernel<true, false><<<grid, 256, 0, st>>>(K3G_OG_ARGS);
+  else out_gate_kernel<false, true><<<grid, 256, 0, st>>>(K3G_OG_ARGS);
+#undef K3G_OG_ARGS
+  return k3g_launch_status();
+}
+#endif

@@ -1,0 +1,375 @@
+// MoE routing tables, dispatch gather and top-k combine around the grouped expert GEMMs.
+//
+// Replaces, behind the same entry names and parameter lists, the routing kernels of
+// xiaguan/kern-k3 source/k3_moe_prefill_v4.cu:
+//   kern_k3_moe_route_count    (:142-157)  per-256-token-block histogram of the local experts
+//   kern_k3_moe_route_tables   (:159-203)  tile-padded expert offsets, per-block offsets, CTA work list
+//   kern_k3_moe_route_scatter  (:205-252)  stable expert-sorted permutation (route_map, exp2perm)
+//   kern_k3_moe_finalize       (:254-302)  out[t] = bf16(sum_k w[t,k] * fc2[exp2perm[t,k]])
+// and adds two config-level kernels the reference leaves to other launches:
+//   permute_gather     rows of MXFP8 codes + scales copied into expert-sorted order (the reference's
+//                      grouped GEMM gathers rows itself through route_map)
+//   finalize_residual  finalize fused with the one-partial residual add of kern_k3_land_add2
+//                      (source/k3_residual_v2.cu:349-392), keeping both bf16 landings.
+//
+// All tables are integer-only and deterministic: the rank of an expanded id (t, k) among the ids
+// of the same expert inside its 256-token block is its position in ascending (t, k) order (a
+// stable counting sort), computed from warp match masks plus a scan over the block's 32-id groups.
+#include "k3g_device.cuh"
+#include "k3g_host.h"
+
+using namespace k3g;
+
+namespace {
+
+constexpr int kMaxE = 64;          // local experts per rank (224 / 4 = 56 in the reference deployment)
+constexpr int kRouteBlock = 256;   // tokens per routing block
+constexpr int kMaxTopk = 16;
+constexpr int kMaxGroups = kRouteBlock * kMaxTopk / 32;   // 128 groups of 32 expanded ids
+
+__device__ __forceinline__ int local_expert(int id, int rank, int E, int ep_ranks, int strided) {
+  if (strided) {
+    if (id % ep_ranks != rank) return -1;
+    const int e = id / ep_ranks;
+    return e < E ? e : -1;
+  }
+  const int e = id - rank * E;
+  return (e >= 0 && e < E) ? e : -1;
+}
+
+__device__ __forceinline__ void route_count_body(const int* __restrict__ ids, int T, int rank, int E, int topk, int ep_ranks,
+                                                 int strided, int* __restrict__ blockcount) {
+  __shared__ int cnt[kMaxE];
+  for (int b = blockIdx.x; b * kRouteBlock < T; b += gridDim.x) {
+    if (threadIdx.x < E) cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const long long lo = (long long)b * kRouteBlock * topk;
+    const long long hi = min((long long)T, (long long)(b + 1) * kRouteBlock) * topk;
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const int e = local_expert(ids[i], rank, E, ep_ranks, strided);
+      if (e >= 0) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < E) blockcount[(size_t)b * E + threadIdx.x] = cnt[threadIdx.x];
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ void route_tables_body(const int* __restrict__ blockcount, int blocks, int E, int tile,
+                                                  int* __restrict__ blockoff, int* __restrict__ cta_batch, int* __restrict__ cta_limit,
+                                                  int* __restrict__ num_non_exiting, int* __restrict__ total_padded,
+                                                  int* __restrict__ route_map) {
+  __shared__ int count[kMaxE], off[kMaxE + 1];
+  // count[e]: one warp per expert, lanes over blocks (integer sums: order-free)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    int run = 0;
+    for (int b = lane; b < blocks; b += 32) run += blockcount[(size_t)b * E + e];
+    run = __reduce_add_sync(0xffffffffu, run);
+    if (lane == 0) count[e] = run;
+  }
+  __syncthreads();
+  if (warp == 0) {   // exclusive scan of ceil(count / tile) over up to 64 experts: two per lane
+    const int e0 = 2 * lane, e1 = 2 * lane + 1;
+    const int c0 = e0 < E ? (count[e0] + tile - 1) / tile : 0;
+    const int c1 = e1 < E ? (count[e1] + tile - 1) / tile : 0;
+    int incl = c0 + c1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int excl = incl - (c0 + c1);
+    if (e0 < E) off[e0] = excl;
+    if (e1 < E) off[e1] = excl + c0;
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (lane == 0) {
+      off[E] = total;
+      num_non_exiting[0] = total;
+      total_padded[0] = total * tile;
+    }
+  }
+  __syncthreads();
+  // blockoff[b][e] = tile * off[e] + (count of e in blocks before b): warp per expert, chunked scan
+  for (int e = warp; e < E; e += nwarps) {
+    int run = off[e] * tile;
+    for (int b0 = 0; b0 < blocks; b0 += 32) {
+      const int b = b0 + lane;
+      const int c = b < blocks ? blockcount[(size_t)b * E + e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (b < blocks) blockoff[(size_t)b * E + e] = run + incl - c;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    // padding rows of the expert's last tile route token 0
+    for (int r = off[e] * tile + count[e] + lane; r < off[e + 1] * tile; r += 32) route_map[r] = 0;
+  }
+  for (int i = threadIdx.x; i < off[E]; i += blockDim.x) {
+    int lo = 0, hi = E;     // largest j with off[j] <= i and off[j + 1] > i
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (off[mid] <= i) lo = mid; else hi = mid; }
+    while (off[lo + 1] <= i) ++lo;   // skip experts with no tiles
+    cta_batch[i] = lo;
+    cta_limit[i] = min((i + 1) * tile, off[lo] * tile + count[lo]);
+  }
+}
+
+__device__ __forceinline__ void route_scatter_body(const int* __restrict__ ids, const int* __restrict__ blockoff, int T, int rank,
+                                                   int E, int topk, int ep_ranks, int strided, int* __restrict__ route_map,
+                                                   int* __restrict__ exp2perm) {
+  __shared__ int hist[kMaxGroups][kMaxE];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const unsigned below = (1u << lane) - 1u;
+  const int groups = kRouteBlock * topk / 32;
+  for (int blk = blockIdx.x; blk * kRouteBlock < T; blk += gridDim.x) {
+    const long long base = (long long)blk * kRouteBlock * topk;
+    const long long end = (long long)T * topk;
+    for (int i = threadIdx.x; i < groups * kMaxE; i += blockDim.x) (&hist[0][0])[i] = 0;
+    __syncthreads();
+    for (int g = warp; g < groups; g += nwarps) {
+      const long long i = base + g * 32 + lane;
+      int e = -1;
+      if (i < end) e = local_expert(ids[i], rank, E, ep_ranks, strided);
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (e >= 0 && (peers & below) == 0) hist[g][e] = __popc(peers);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      int run = 0;
+      for (int g = 0; g < groups; ++g) { const int c = hist[g][e]; hist[g][e] = run; run += c; }
+    }
+    __syncthreads();
+    for (int g = warp; g < groups; g += nwarps) {
+      const long long i = base + g * 32 + lane;
+      int e = -1;
+      if (i < end) e = local_expert(ids[i], rank, E, ep_ranks, strided);
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (i >= end) continue;
+      if (e < 0) { exp2perm[i] = -1; continue; }
+      const int row = blockoff[(size_t)blk * E + e] + hist[g][e] + __popc(peers & below);
+      route_map[row] = (int)(i / topk);
+      exp2perm[i] = row;
+    }
+    __syncthreads();
+  }
+}
+
+// Combine: one token per 128-thread team pass; live (row, weight) pairs compacted in ascending k.
+template <bool RESIDUAL>
+__device__ __forceinline__ void finalize_body(const __nv_bfloat16* __restrict__ fc2, const int* __restrict__ exp2perm,
+                                              const float* __restrict__ wts, const __nv_bfloat16* __restrict__ residual,
+                                              __nv_bfloat16* __restrict__ out, int T, int cols, int topk) {
+  __shared__ int s_row[2][kMaxTopk];
+  __shared__ float s_w[2][kMaxTopk];
+  __shared__ int s_n[2];
+  const int nvec = cols >> 3;
+  int it = 0;
+  for (int t = blockIdx.x; t < T; t += gridDim.x, ++it) {
+    const int buf = it & 1;
+    if (threadIdx.x < 32) {
+      const int k = threadIdx.x;
+      const int p = k < topk ? exp2perm[(size_t)t * topk + k] : -1;
+      const unsigned live = __ballot_sync(0xffffffffu, p >= 0);
+      if (p >= 0) {
+        const int pos = __popc(live & ((1u << k) - 1u));
+        s_row[buf][pos] = p;
+        s_w[buf][pos] = wts[(size_t)t * topk + k];
+      }
+      if (k == 0) s_n[buf] = __popc(live);
+    }
+    __syncthreads();
+    const int n = s_n[buf];
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int l = 0; l < 8; ++l) acc[l] = 0.f;
+      int i = 0;
+      for (; i + 4 <= n; i += 4) {           // four row loads in flight
+        V8 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x[u] = ld_stream(fc2 + (size_t)s_row[buf][i + u] * cols + v * 8);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float w = s_w[buf][i + u];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] = __fmaf_rn(w, bf_lo(x[u].w[j]), acc[2 * j]);
+            acc[2 * j + 1] = __fmaf_rn(w, bf_hi(x[u].w[j]), acc[2 * j + 1]);
+          }
+        }
+      }
+      for (; i < n; ++i) {
+        const V8 x = ld_stream(fc2 + (size_t)s_row[buf][i] * cols + v * 8);
+        const float w = s_w[buf][i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] = __fmaf_rn(w, bf_lo(x.w[j]), acc[2 * j]);
+          acc[2 * j + 1] = __fmaf_rn(w, bf_hi(x.w[j]), acc[2 * j + 1]);
+        }
+      }
+      V8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o.w[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
+      if (RESIDUAL) {
+        const V8 r = ld_stream(residual + (size_t)t * cols + v * 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o.w[j] = add_bf2(r.w[j], o.w[j]);
+      }
+      st_stream(out + (size_t)t * cols + v * 8, o);
+    }
+  }
+}
+
+// dst row r = src row route_map[r]: `cols` code bytes and cols / 32 scale bytes per row.
+__global__ void __launch_bounds__(128) permute_gather_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                                             const int* __restrict__ route_map, long long rows, int cols,
+                                                             uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
+  const int qv = cols >> 4, sfb = cols >> 5;
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const long long t = route_map[r];
+    const uint4* src = reinterpret_cast<const uint4*>(q + t * cols);
+    uint4* dst = reinterpret_cast<uint4*>(out_q + r * cols);
+    for (int v = threadIdx.x; v < qv; v += blockDim.x) {
+      const uint4 x = __ldg(src + v);       // a token row is read once per expert it routes to: keep it cached
+      __stcs(dst + v, x);
+    }
+    if ((sfb & 15) == 0) {
+      const int sv = sfb >> 4;
+      if ((int)threadIdx.x < sv)
+        __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + threadIdx.x, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + threadIdx.x));
+    } else {
+      for (int b = threadIdx.x; b < sfb; b += blockDim.x) out_sf[r * sfb + b] = sf[t * sfb + b];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) route_count_kernel(const int* ids, int T, int rank, int E, int topk, int ep_ranks,
+                                                          int strided, int* blockcount) {
+  route_count_body(ids, T, rank, E, topk, ep_ranks, strided, blockcount);
+}
+__global__ void __launch_bounds__(1024) route_tables_kernel(const int* blockcount, int blocks, int E, int tile, int* blockoff,
+                                                            int* cta_batch, int* cta_limit, int* nne, int* total, int* route_map) {
+  route_tables_body(blockcount, blocks, E, tile, blockoff, cta_batch, cta_limit, nne, total, route_map);
+}
+__global__ void __launch_bounds__(512) route_scatter_kernel(const int* ids, const int* blockoff, int T, int rank, int E, int topk,
+                                                            int ep_ranks, int strided, int* route_map, int* exp2perm) {
+  route_scatter_body(ids, blockoff, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm);
+}
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(128) finalize_kernel(const __nv_bfloat16* fc2, const int* exp2perm, const float* wts,
+                                                       const __nv_bfloat16* residual, __nv_bfloat16* out, int T, int cols, int topk) {
+  finalize_body<RESIDUAL>(fc2, exp2perm, wts, residual, out, T, cols, topk);
+}
+
+}  // namespace
+
+// ---- manifest entry points: TOPK = 16 and the expert placement are build constants there
+//      (source/k3_moe_prefill_v4.cu:87, :100-109) ---------------------------------------------
+#ifndef EP_RANKS
+#define EP_RANKS 4
+#endif
+#ifdef EP_STRIDED
+#define K3G_EP_STRIDED 1
+#else
+#define K3G_EP_STRIDED 0
+#endif
+
+extern "C" __global__ void __launch_bounds__(256) kern_k3_moe_route_count(const int* __restrict__ ids, int T, int rank, int E,
+                                                                         int* __restrict__ blockcount) {
+  route_count_body(ids, T, rank, E, 16, EP_RANKS, K3G_EP_STRIDED, blockcount);
+}
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_moe_route_tables(const int* __restrict__ blockcount, int blocks, int E, int tile,
+                                                                           int* __restrict__ blockoff, int* __restrict__ cta_batch,
+                                                                           int* __restrict__ cta_limit, int* __restrict__ num_non_exiting,
+                                                                           int* __restrict__ total_padded, int* __restrict__ route_map) {
+  route_tables_body(blockcount, blocks, E, tile, blockoff, cta_batch, cta_limit, num_non_exiting, total_padded, route_map);
+}
+extern "C" __global__ void __launch_bounds__(512) kern_k3_moe_route_scatter(const int* __restrict__ ids, const int* __restrict__ blockoff,
+                                                                           int T, int rank, int E, int* __restrict__ route_map,
+                                                                           int* __restrict__ exp2perm) {
+  route_scatter_body(ids, blockoff, T, rank, E, 16, EP_RANKS, K3G_EP_STRIDED, route_map, exp2perm);
+}
+extern "C" __global__ void __launch_bounds__(128) kern_k3_moe_finalize(const __nv_bfloat16* __restrict__ fc2, const int* __restrict__ exp2perm,
+                                                                      const float* __restrict__ wts, __nv_bfloat16* __restrict__ out,
+                                                                      int T, int cols) {
+  finalize_body<false>(fc2, exp2perm, wts, nullptr, out, T, cols, 16);
+}
+
+#ifndef K3G_CUBIN_ONLY
+static int check_route(int T, int E, int topk, int ep_ranks) {
+  K3G_REQUIRE(T >= 0 && E > 0 && E <= kMaxE, K3G_ESHAPE);
+  K3G_REQUIRE(topk > 0 && topk <= kMaxTopk && (kRouteBlock * topk) % 32 == 0, K3G_ESHAPE);
+  K3G_REQUIRE(ep_ranks > 0, K3G_ESHAPE);
+  return K3G_OK;
+}
+
+K3G_API int k3g_moe_route_count(const void* ids, int T, int rank, int E, int topk, int ep_ranks, int strided, void* blockcount,
+                                void* stream) {
+  K3G_REQUIRE_PTR(ids); K3G_REQUIRE_PTR(blockcount);
+  if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
+  K3G_REQUIRE(rank >= 0 && rank < ep_ranks, K3G_ERANGE);
+  if (T == 0) return K3G_OK;
+  route_count_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 256, 0, k3g_stream(stream)>>>((const int*)ids, T, rank, E, topk, ep_ranks,
+                                                                                        strided, (int*)blockcount);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_moe_route_tables(const void* blockcount, int blocks, int E, int tile, void* blockoff, void* cta_batch,
+                                 void* cta_limit, void* num_non_exiting, void* total_padded, void* route_map, void* stream) {
+  K3G_REQUIRE_PTR(blockcount); K3G_REQUIRE_PTR(blockoff); K3G_REQUIRE_PTR(cta_batch); K3G_REQUIRE_PTR(cta_limit);
+  K3G_REQUIRE_PTR(num_non_exiting); K3G_REQUIRE_PTR(total_padded); K3G_REQUIRE_PTR(route_map);
+  K3G_REQUIRE(blocks >= 0 && E > 0 && E <= kMaxE && tile > 0, K3G_ESHAPE);
+  route_tables_kernel<<<1, 1024, 0, k3g_stream(stream)>>>((const int*)blockcount, blocks, E, tile, (int*)blockoff, (int*)cta_batch,
+                                                         (int*)cta_limit, (int*)num_non_exiting, (int*)total_padded, (int*)route_map);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_moe_route_scatter(const void* ids, const void* blockoff, int T, int rank, int E, int topk, int ep_ranks,
+                                  int strided, void* route_map, void* exp2perm, void* stream) {
+  K3G_REQUIRE_PTR(ids); K3G_REQUIRE_PTR(blockoff); K3G_REQUIRE_PTR(route_map); K3G_REQUIRE_PTR(exp2perm);
+  if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
+  K3G_REQUIRE(rank >= 0 && rank < ep_ranks, K3G_ERANGE);
+  if (T == 0) return K3G_OK;
+  route_scatter_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 512, 0, k3g_stream(stream)>>>(
+      (const int*)ids, (const int*)blockoff, T, rank, E, topk, ep_ranks, strided, (int*)route_map, (int*)exp2perm);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_moe_finalize(const void* fc2, const void* exp2perm, const void* wts, void* out, int T, int cols, int topk,
+                             void* stream) {
+  K3G_REQUIRE_PTR(fc2); K3G_REQUIRE_PTR(exp2perm); K3G_REQUIRE_PTR(wts); K3G_REQUIRE_PTR(out);
+  K3G_REQUIRE_ALIGNED(fc2); K3G_REQUIRE_ALIGNED(out);
+  K3G_REQUIRE(T >= 0 && cols > 0 && cols % 8 == 0 && topk > 0 && topk <= kMaxTopk, K3G_ESHAPE);
+  if (T == 0) return K3G_OK;
+  finalize_kernel<false><<<T, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)fc2, (const int*)exp2perm, (const float*)wts, nullptr,
+                                                           (__nv_bfloat16*)out, T, cols, topk);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_finalize_residual(const void* fc2, const void* exp2perm, const void* wts, const void* residual, void* out, int T,
+                                  int cols, int topk, void* stream) {
+  K3G_REQUIRE_PTR(fc2); K3G_REQUIRE_PTR(exp2perm); K3G_REQUIRE_PTR(wts); K3G_REQUIRE_PTR(residual); K3G_REQUIRE_PTR(out);
+  K3G_REQUIRE_ALIGNED(fc2); K3G_REQUIRE_ALIGNED(out); K3G_REQUIRE_ALIGNED(residual);
+  K3G_REQUIRE(T >= 0 && cols > 0 && cols % 8 == 0 && topk > 0 && topk <= kMaxTopk, K3G_ESHAPE);
+  if (T == 0) return K3G_OK;
+  finalize_kernel<true><<<T, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)fc2, (const int*)exp2perm, (const float*)wts,
+                                                          (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, T, cols, topk);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_permute_gather(const void* q, const void* sf, const void* route_map, long long rows, int cols, void* out_q,
+                               void* out_sf, void* stream) {
+  K3G_REQUIRE_PTR(q); K3G_REQUIRE_PTR(sf); K3G_REQUIRE_PTR(route_map); K3G_REQUIRE_PTR(out_q); K3G_REQUIRE_PTR(out_sf);
+  K3G_REQUIRE_ALIGNED(q); K3G_REQUIRE_ALIGNED(out_q);
+  K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
+  if ((cols >> 5) % 16 == 0) { K3G_REQUIRE_ALIGNED(sf); K3G_REQUIRE_ALIGNED(out_sf); }
+  if (rows == 0) return K3G_OK;
+  const long long grid = rows < 0x7fffffffLL ? rows : 0x7fffffffLL;
+  permute_gather_kernel<<<(unsigned)grid, 128, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
+                                                                       cols, (uint8_t*)out_q, (uint8_t*)out_sf);
+  return k3g_launch_status();
+}
+#endif

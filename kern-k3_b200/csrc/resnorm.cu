@@ -211,7 +211,7 @@ __device__ __forceinline__ void attnres_rms_body(const __nv_bfloat16* __restrict
 }
 
 // ---- K1b ----------------------------------------------------------------------------------
-template <int VPT, bool LAND_BF16>
+template <int VPT, bool LB16>
 __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix,
                                                           const __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
                                                           const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,
@@ -228,7 +228,7 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
     for (int v = 0; v < VPT; ++v) {
       const size_t off = base + (t + v * kTeam) * 8;
       V8 p;
-      if (LAND_BF16) {
+      if (LB16) {
         p = ld_stream((const __nv_bfloat16*)partial + off);
       } else {
         const V8 f0 = ld_stream((const float*)partial + off), f1 = ld_stream((const float*)partial + off + 4);
@@ -252,7 +252,7 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
 }
 
 // ---- K1c ----------------------------------------------------------------------------------
-template <int VPT, bool LAND_BF16>
+template <int VPT, bool LB16>
 __device__ __forceinline__ void land_add2_body(const void* __restrict__ p1, const void* __restrict__ p2,
                                                const __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ hidden,
                                                int two, int B) {
@@ -264,7 +264,7 @@ __device__ __forceinline__ void land_add2_body(const void* __restrict__ p1, cons
       const size_t off = (size_t)b * H + (t + v * kTeam) * 8;
       const V8 pr = ld_stream(prefix2 + off);
       float l1[8], l2[8];
-      if (LAND_BF16) {
+      if (LB16) {
         const V8 a = ld_stream((const __nv_bfloat16*)p1 + off);
 #pragma unroll
         for (int j = 0; j < 4; ++j) { l1[2 * j] = bf_lo(a.w[j]); l1[2 * j + 1] = bf_hi(a.w[j]); }

@@ -76,6 +76,10 @@ def _ptr(x):
         return ctypes.c_void_p(x)
     if hasattr(x, "ctypes"):          # numpy array (host_ arguments)
         return ctypes.c_void_p(x.ctypes.data)
+    if isinstance(x, (ctypes._SimpleCData, ctypes.Array)):   # host out-parameters
+        return ctypes.cast(ctypes.pointer(x) if isinstance(x, ctypes._SimpleCData) else x, ctypes.c_void_p)
+    if isinstance(x, (bytes, bytearray)):
+        return ctypes.cast(ctypes.c_char_p(bytes(x)), ctypes.c_void_p)
     raise TypeError("cannot pass %r as a pointer" % type(x))
 
 

@@ -1,0 +1,86 @@
+"""World-2 gloo rank for tests/test_host_cpu.py: the peer-table exchange and the row sharding with a
+fake allocator (no CUDA), and the sharded oracle pipeline reassembled across ranks."""
+import os
+import sys
+
+import numpy as np
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in ("kern-k3_b200", "oracle", "tests"):
+    sys.path.insert(0, os.path.join(ROOT, p))
+import k3o  # noqa: E402
+from k3g.peer import PeerGroup, collective_units, shard_rows  # noqa: E402
+from util import normal_bf16, rng  # noqa: E402
+
+
+class FakeAllocator:
+    """Addresses are (rank << 40) | serial; a handle is the address as 64 bytes; opening a handle maps
+    it at (1 << 60) | address, so own and opened addresses are distinguishable."""
+
+    def __init__(self, rank):
+        self.rank, self.n, self.closed, self.freed = rank, 0, [], []
+
+    def alloc(self, nbytes):
+        self.n += 1
+        return (self.rank << 40) | (self.n << 12)
+
+    def export(self, ptr):
+        return int(ptr).to_bytes(64, "little")
+
+    def open(self, handle):
+        return (1 << 60) | int.from_bytes(handle, "little")
+
+    def close(self, ptr):
+        self.closed.append(ptr)
+
+    def free(self, ptr):
+        self.freed.append(ptr)
+
+    def upload_table(self, addrs):
+        return list(addrs)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo")
+    alloc = FakeAllocator(rank)
+    pg = PeerGroup(rank, world, allocator=alloc)
+    a = pg.symmetric("partial", 1000)
+    b = pg.symmetric("flags", 64)
+    for buf in (a, b):
+        assert buf.nbytes % 256 == 0 and len(buf.table) == world
+        for r in range(world):
+            if r == rank:
+                assert buf.table[r] == buf.ptr and (buf.ptr >> 40) == rank
+            else:
+                assert buf.table[r] >> 60 == 1 and ((buf.table[r] & ((1 << 60) - 1)) >> 40) == r
+    pg.release()
+    assert len(alloc.closed) == 2 * (world - 1) and len(alloc.freed) == 2
+
+    # sharding: rows in block order, one collective grid width for the whole replay
+    T, H = 64, 1024
+    rows = shard_rows(T, world)
+    assert rows == 32 and shard_rows(16384, 4) == 4096 and shard_rows(5, 4) == 2
+    assert collective_units(16384, 4) == 896 and collective_units(16384, 8) == 448 and collective_units(1, 4) == 1
+    # each rank reduces and normalises its own shard; gathering the shards over gloo reproduces the
+    # single-process result
+    partials = [normal_bf16(rng(10 + r), (T * H,), std=0.5 / world) for r in range(world)]
+    residual = normal_bf16(rng(20), (T, H)); gamma = normal_bf16(rng(21), (H,), mean=1.0, std=0.02)
+    delta = k3o.rs_pull(partials, rank, 2 * (world - 1)).reshape(rows, H)
+    _, q, sf, _ = k3o.resnorm_mxfp8(residual[rank * rows:(rank + 1) * rows], delta, gamma, 1e-6, want_normed=False)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (q, sf))
+    q_all = np.concatenate([x[0] for x in gathered]); sf_all = np.concatenate([x[1] for x in gathered])
+    total = sum(k3o.bf16_to_f32(p).astype(np.float64) for p in partials).reshape(T, H)
+    full_delta = np.concatenate([k3o.rs_pull(partials, r, 2 * (world - 1)).reshape(rows, H) for r in range(world)])
+    assert np.allclose(k3o.bf16_to_f32(full_delta), total, rtol=2e-2, atol=1e-2)
+    _, q_ref, sf_ref, _ = k3o.resnorm_mxfp8(residual, full_delta, gamma, 1e-6, want_normed=False)
+    assert np.array_equal(q_all, q_ref) and np.array_equal(sf_all, sf_ref)
+    dist.barrier()
+    print("GLOO_OK rank %d" % rank)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

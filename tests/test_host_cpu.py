@@ -1,0 +1,92 @@
+"""CPU-only checks: the oracle's collective semantics, the simulated flag protocol (including a rank
+that never arrives), the library's exported symbols, and the peer-table exchange with gloo ranks."""
+import ctypes
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+import k3o
+from util import normal_bf16, rng
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_rs_sequence_matches_ring_orders():
+    assert list(k3o.rs_sequence(1, 4, 6)) == [2, 3, 0, 1]       # peers ascending, own last (the NCCL ring)
+    assert list(k3o.rs_sequence(1, 4, 0)) == [1, 2, 3, 0]       # own first
+    assert list(k3o.rs_sequence(1, 4, 7)) == [0, 3, 2, 1]       # descending, own last
+    assert list(k3o.rs_sequence(0, 1, 0)) == [0]
+    for W in (2, 4, 8):
+        for order in range(2 * W):
+            for r in range(W):
+                assert sorted(k3o.rs_sequence(r, W, order)) == list(range(W))
+
+
+def test_rs_pull_oracle_against_numpy_chain():
+    g = rng(11)
+    W, count = 4, 4096
+    partials = [normal_bf16(g, (W * count,)) for _ in range(W)]
+    for rank in range(W):
+        seq = k3o.rs_sequence(rank, W, 6)
+        a = k3o.bf16_to_f32(partials[seq[0]][rank * count:(rank + 1) * count])
+        for k in seq[1:]:
+            a = k3o.bf16_to_f32(k3o.f32_to_bf16(a + k3o.bf16_to_f32(partials[k][rank * count:(rank + 1) * count])))
+        assert np.array_equal(k3o.rs_pull(partials, rank, 6), k3o.f32_to_bf16(a))
+
+
+def test_simulated_flag_protocol():
+    bad, status = k3o.sim_barrier(4, slots=6, replays=50, units=896)
+    assert bad == 0 and not status.any()
+    bad, status = k3o.sim_barrier(8, slots=3, replays=20, units=1)
+    assert bad == 0
+
+
+def test_simulated_flag_protocol_absent_rank_times_out_and_reports():
+    bad, status = k3o.sim_barrier(4, slots=2, replays=3, units=896, absent_rank=2, timeout_us=20000)
+    assert bad == 3
+    assert status[2] == 0 and all(status[r] == 1 + 2 for r in (0, 1, 3))    # every waiter names peer 2
+
+
+def test_library_exports_every_declared_symbol():
+    sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
+    lib = os.path.join(ROOT, "kern-k3_b200", "lib", "libk3g.so")
+    if not os.path.exists(lib):
+        import build
+        build.build()
+    import k3g
+    assert len(k3g.PROTOTYPES) >= 30
+    handle = ctypes.CDLL(lib)
+    for name in k3g.PROTOTYPES:
+        assert hasattr(handle, name), name
+    # argument checks run before any CUDA call, so they work without a GPU
+    assert k3g.raw("k3g_resnorm_mxfp8", None, None, None, None, None, None, None, 1, 7168, 1e-6, 0, None) == -1
+    assert k3g.raw("k3g_rs_pull", 16, 16, 16, 12, 0, 0, 1, 1, None) == -2
+    assert k3g.raw("k3g_router_topk", 16, 16, 16, 16, 16, 4, 200, 8, None) == -2
+
+
+def test_dropin_cubins_export_reference_entry_names():
+    """Every cubin built for a reference module name contains the entry names the manifest launches."""
+    cdir = os.path.join(ROOT, "kern-k3_b200", "lib", "cubin")
+    want = {
+        "k3_residual_v2+LAND_BF16=1": ["kern_k3_attnres_rms", "kern_k3_land_add_attnres_rms", "kern_k3_land_add2"],
+        "k3_quant_fp8_pair_v2": ["kern_quant_fp8_amax_v2", "kern_quant_fp8_apply_v2", "kern_k3_moe_quant"],
+        "k3_router_argmax": ["kern_k3_router_topk"],
+        "k3_reducescatter_pull_nr4": ["kern_k3_rs_pull", "kern_k3_rs_arrive1", "kern_k3_allgather4_push", "kern_k3_epoch_bump", "kern_k3_flags_init"],
+        "k3_mla_prep_v2+INNER=3072+MLA_FUSED=5184": ["kern_k3_mla_prep_head", "kern_k3_mla_prep_gate"],
+        "k3_span_gather_v3+HEADS=24": ["kern_k3_span_gather", "kern_k3_kda_out_gate"],
+    }
+    for mod, entries in want.items():
+        path = os.path.join(cdir, mod + ".cubin")
+        assert os.path.exists(path), path
+        blob = open(path, "rb").read()
+        for e in entries:
+            assert e.encode() in blob, (mod, e)
+
+
+def test_peer_group_exchange_with_gloo_ranks():
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29533", os.path.join(ROOT, "tests", "gloo_worker.py")], capture_output=True, text=True, timeout=300)
+    sys.stdout.write(r.stdout[-3000:]); sys.stderr.write(r.stderr[-3000:])
+    assert r.returncode == 0 and r.stdout.count("GLOO_OK") == 2

@@ -1,0 +1,321 @@
+"""Benchmark of the K3 prefill glue path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-ops]
+
+One "step" is benchmark configuration 1 at world N over T = 16384 tokens x d = 7168:
+each rank holds a bf16 partial-sum matrix [T, d]; the step reduce-scatters it into T/N-row shards
+(in-kernel NVLink pull, ring-order bf16 chain), applies residual add + RMSNorm + MXFP8 to the shard
+and all-gathers codes and scales back to every rank (in-kernel push), bracketed by the two
+arrive/poll barriers.  Metric: microseconds per step ("per-layer glue us at 16k tokens"; lower is
+better; total work is fixed as N grows, i.e. strong scaling).  Inputs are synthetic and seeded,
+larger than the 126 MB L2 (470 MB read per step at N = 1), so no L2 flush is needed.
+
+Rank 0 prints ONE JSON line.  `value` is timed with inputs resident in HBM; `e2e` is the same step
+through host (pinned) buffers with the H2D / D2H copies inside the timed region.  `roofline`
+describes the fused kernel; `cpu_baseline` is the CPU oracle (test infrastructure, oracle/) timed on
+this box's host cores on a bounded sample.  `--impl reference` times that CPU oracle as the
+reference arm (the reference project has no CPU path and no host API of its own).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
+
+TOKENS, HIDDEN, EPS = 16384, 7168, 1e-6
+METRIC, UNIT = "per-layer glue us at 16k tokens", "us"
+CPU_SAMPLE_ROWS = 2048
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+    BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+
+    def __init__(self, index, period=0.001):
+        super().__init__(daemon=True)
+        self.index, self.period, self.samples, self.reasons, self.max_mhz = index, period, [], set(), None
+        self._halt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        while self.nv is not None and not self._halt.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                r = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.BITS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def finish(self):
+        self._halt.set()
+        self.join(timeout=1.0)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "samples": len(s), "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def cpu_oracle_us(steps, warmup, rows=CPU_SAMPLE_ROWS):
+    """The CPU oracle's version of the step (W = 1) on `rows` rows, scaled to 16384 tokens."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import k3o
+    g = np.random.Generator(np.random.Philox(7))
+    partial = k3o.f32_to_bf16(g.standard_normal((rows, HIDDEN), dtype=np.float32) * np.float32(0.5))
+    residual = k3o.f32_to_bf16(g.standard_normal((rows, HIDDEN), dtype=np.float32))
+    gamma = k3o.f32_to_bf16((1 + 0.02 * g.standard_normal(HIDDEN, dtype=np.float32)).astype(np.float32))
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        delta = k3o.rs_pull([partial.reshape(-1)], 0, 0).reshape(rows, HIDDEN)
+        k3o.resnorm_mxfp8(residual, delta, gamma, EPS, want_normed=False)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    per_step = sum(times) / len(times) * (TOKENS / rows)
+    return per_step * 1e6, k3o.num_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    us, cores = cpu_oracle_us(steps, min(args.warmup, 2))
+    sample = "%d of %d rows per step (time scaled by %d), C++/OpenMP oracle of the same semantics" % (CPU_SAMPLE_ROWS, TOKENS, TOKENS // CPU_SAMPLE_ROWS)
+    line = {"impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2),
+            "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config1: RS -> residual+RMSNorm+MXFP8 -> AG, T=16384 d=7168, CPU oracle at world 1", "tokens": TOKENS, "d": HIDDEN},
+            "cpu_baseline": {"value": us, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def time_us(fn, iters, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
+def bench_ops(k3g, dev, peak_gbs, iters=20):
+    """Per-op device times of the other benchmark configurations at their 16k-token shapes (N = 1),
+    each with its algorithmic bytes (unique bytes that must cross HBM once)."""
+    import torch
+    T, H = TOKENS, HIDDEN
+    s = k3g.current_stream()
+    g = torch.Generator(device=dev); g.manual_seed(3)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev).to(torch.bfloat16)
+    out = []
+
+    def add(name, fn, nbytes):
+        us = time_us(fn, iters)
+        out.append({"op": name, "us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_measured": round(nbytes / us / 1e3 / peak_gbs, 3),
+                    "frac_8tbs": round(nbytes / us / 1e3 / 8000.0, 3)})
+
+    E = T * H
+    res, dl, gm = rnd(T, H), rnd(T, H), (1 + 0.02 * torch.randn(H, generator=g, device=dev)).to(torch.bfloat16)
+    o16 = torch.empty_like(res); q8 = torch.empty((T, H), dtype=torch.uint8, device=dev); sf8 = torch.empty((T, H // 32), dtype=torch.uint8, device=dev)
+    add("config0 resnorm_mxfp8 16384x7168", lambda: k3g.call("k3g_resnorm_mxfp8", res, dl, gm, o16, q8, sf8, None, T, H, EPS, 0, s), 7 * E + E // 32)
+    n16 = torch.empty_like(res)
+    add("land_add_attnres_rms nb=0 16384x7168", lambda: k3g.call("k3g_land_add_attnres_rms", dl, 1, res, None, None, gm, o16, n16, 0, 0, T, H, 1e-5, s), 8 * E)
+    add("land_add2 two 16384x7168", lambda: k3g.call("k3g_land_add2", dl, res, 1, o16, n16, 1, T, H, s), 8 * E)
+    del n16
+    add("moe_quant 32768x3584", lambda: k3g.call("k3g_moe_quant", res, q8, sf8, 2 * T, 3584, 0, s), 3 * E + E // 32)
+    part = torch.empty(2048, device=dev); sc = torch.empty(1, device=dev)
+    add("quant_fp8_tensor 16384x7168", lambda: k3g.call("k3g_quant_fp8_tensor", res, q8, sc, part, E, 2048, s), 3 * E)
+    # config 2: router, routing tables, dispatch gather, combine
+    S = torch.randn((T, 224), generator=g, device=dev); bias = 0.1 * torch.randn(224, generator=g, device=dev)
+    rs = torch.ones(1, dtype=torch.bfloat16, device=dev)
+    idx = torch.empty((T, 8), dtype=torch.int32, device=dev); wts = torch.empty((T, 8), dtype=torch.float32, device=dev)
+    add("config2 router_topk 16384x224 k=8", lambda: k3g.call("k3g_router_topk", S, bias, rs, idx, wts, T, 224, 8, s), T * 224 * 4 + T * 8 * 8)
+    torch.cuda.synchronize()
+    ids64 = (idx % 64).contiguous()     # one rank's 64 local experts stand in for EP = 1 (tables are per rank)
+    blocks = T // 256
+    bc = torch.zeros((blocks, 64), dtype=torch.int32, device=dev); bo = torch.zeros_like(bc)
+    tile = 128                         # the reference's CTA tile: offsets padded to 128 rows per expert
+    nct = T * 8 // tile + 64
+    cb = torch.zeros(nct, dtype=torch.int32, device=dev); cl = torch.zeros_like(cb); nne = torch.zeros(1, dtype=torch.int32, device=dev)
+    tot = torch.zeros(1, dtype=torch.int32, device=dev); rm = torch.zeros(nct * tile, dtype=torch.int32, device=dev)
+    e2p = torch.zeros((T, 8), dtype=torch.int32, device=dev)
+
+    def route():
+        k3g.call("k3g_moe_route_count", ids64, T, 0, 64, 8, 1, 0, bc, s)
+        k3g.call("k3g_moe_route_tables", bc, blocks, 64, tile, bo, cb, cl, nne, tot, rm, s)
+        k3g.call("k3g_moe_route_scatter", ids64, bo, T, 0, 64, 8, 1, 0, rm, e2p, s)
+    add("config2 route count+tables+scatter (3 launches)", route, T * 8 * 4 * 4)
+    torch.cuda.synchronize()
+    rows = int(tot.item())             # tile-padded permuted rows (padding rows route token 0)
+    pq = torch.empty((rows, H), dtype=torch.uint8, device=dev); psf = torch.empty((rows, H // 32), dtype=torch.uint8, device=dev)
+    add("config2 permute_gather %dx7168 mxfp8" % rows, lambda: k3g.call("k3g_permute_gather", q8, sf8, rm, rows, H, pq, psf, s), (T + rows) * (H + H // 32))
+    del pq, psf
+    fc2 = torch.randn((rows, H), generator=g, device=dev, dtype=torch.bfloat16)
+    add("config2 finalize_residual 16384x8x7168", lambda: k3g.call("k3g_finalize_residual", fc2, e2p, wts, res, o16, T, H, 8, s), T * 8 * H * 2 + 4 * E)
+    del fc2
+    # config 3
+    kv = rnd(T, 576); qq = rnd(T, 16, 192); gkv = gm[:512].contiguous(); tab = rnd(T, 64)
+    qo = torch.empty_like(qq); ko = torch.empty_like(qq); lat = torch.empty((T, 512), dtype=torch.bfloat16, device=dev)
+    add("config3 mla_prep_rope_pack 16 heads", lambda: k3g.call("k3g_mla_prep_rope_pack", kv, qq, gkv, tab, qo, ko, lat, T, 16, EPS, s),
+        T * (576 * 2 + 64 * 2 + 16 * 192 * 2 * 2 + 16 * 64 * 2 + 512 * 2))
+    # config 4
+    inner = 3072
+    x = rnd(T, 3 * inner); cw = (0.5 * torch.randn((3, 4, inner), generator=g, device=dev)).to(torch.bfloat16)
+    win = torch.zeros((3, 3, inner), dtype=torch.bfloat16, device=dev)
+    oq, ok, ov = (torch.empty((T, inner), dtype=torch.bfloat16, device=dev) for _ in range(3))
+    add("config4 span conv+SiLU 16384x3x3072", lambda: k3g.call("k3g_span_gather", x, 3 * inner, cw, 1, win, None, oq, ok, ov, None, None, 24, 0, T, 0, s),
+        2 * T * 3 * inner * 2)
+    gate = rnd(T, inner); gamma_o = torch.ones(128, device=dev)
+    gq = torch.empty((T, inner), dtype=torch.uint8, device=dev); gsf = torch.empty((T, inner // 32), dtype=torch.uint8, device=dev)
+    add("config4 kda_out_gate+mxfp8 16384x3072", lambda: k3g.call("k3g_kda_out_gate", oq, gate, inner, 0, gamma_o, None, gq, gsf, 24, 0, T, EPS, s),
+        T * inner * (2 + 2 + 1) + T * inner // 32)
+    return out
+
+
+def run_gpu(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import k3g
+    from k3g.pipeline import LAUNCHES_PER_STEP, TpGlue
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda")
+    if world > 1:
+        dist.init_process_group("nccl")
+    peak_gbs, peak_kind = measured_peaks()
+    glue = TpGlue(rank, world, TOKENS, HIDDEN, EPS)
+    g = torch.Generator(device=dev); g.manual_seed(0x5EED ^ rank)
+    glue.partial.copy_((torch.randn((TOKENS, HIDDEN), generator=g, device=dev) * (0.5 / world)).to(torch.bfloat16))
+    glue.residual.copy_(torch.randn((glue.rows, HIDDEN), generator=g, device=dev).to(torch.bfloat16))
+    g2 = torch.Generator(device=dev); g2.manual_seed(99)
+    glue.gamma.copy_((1 + 0.02 * torch.randn(HIDDEN, generator=g2, device=dev)).to(torch.bfloat16))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, sampler=None):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        if sampler:
+            sampler.start()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / steps * 1e3
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    glue.kernel_events = []
+    warm = max(args.warmup, 3)
+    step_us = timed(glue.step, args.steps, warm, sampler)
+    clocks = sampler.finish()
+    ev = glue.kernel_events[-args.steps:]
+    glue.kernel_events = None
+    kern_us = sum(a.elapsed_time(b) for a, b in ev) / len(ev) * 1e3
+    glue.check_status()
+
+    # end to end: pinned host buffers in, results out, every step
+    hp = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory(); hp.copy_(glue.partial)
+    hr = torch.empty((glue.rows, HIDDEN), dtype=torch.bfloat16).pin_memory(); hr.copy_(glue.residual)
+    ho = torch.empty((glue.rows, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    hq = torch.empty((TOKENS, HIDDEN), dtype=torch.uint8).pin_memory()
+    hs = torch.empty((TOKENS, HIDDEN // 32), dtype=torch.uint8).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_us = timed(lambda: glue.step_host(hp, hr, ho, hq, hs), e2e_steps, 3)
+    glue.check_status()
+
+    W, E = world, TOKENS * HIDDEN
+    alg_hbm = (7 * E + E // 32) // W if W == 1 else (2 * E // W) * 3 + (W - 1) * 2 * E // W + E + E // 32   # per rank, incl. serving peers' pulls
+    roof = {"bound": "hbm", "kernel": "rs_resnorm_mxfp8_ag_kernel", "achieved": round(alg_hbm / kern_us / 1e3, 1), "peak": peak_gbs, "unit": "GB/s",
+            "frac": round(alg_hbm / kern_us / 1e3 / peak_gbs, 4), "peak_kind": peak_kind, "traffic": None, "kernel_us": round(kern_us, 2),
+            "algorithmic_bytes_per_launch": alg_hbm}
+    nv = None
+    if W > 1:
+        nin, nout = (W - 1) * 2 * E // W, (W - 1) * (E + E // 32) // W
+        nv = {"in_bytes": nin, "out_bytes": nout, "in_gbs": round(nin / kern_us / 1e3, 1), "out_gbs": round(nout / kern_us / 1e3, 1),
+              "frac_of_900": round(nin / kern_us / 1e3 / 900.0, 3), "frac_of_measured_770": round(nin / kern_us / 1e3 / 770.0, 3)}
+    line = {"metric": METRIC, "value": round(step_us, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": round(step_us / 1e3, 5), "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config1: TP reduce-scatter -> residual add + RMSNorm + MXFP8 -> all-gather, T=16384 d=7168, world=%d" % W,
+                       "tokens": TOKENS, "d": HIDDEN, "world": W, "l2": "inputs (470 MB read per step at world 1) exceed the 126 MB L2; no flush"},
+            "clocks": clocks, "roofline": roof, "nvlink": nv,
+            "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps},
+            "gpu_launches": LAUNCHES_PER_STEP * args.steps, "tokens_per_s": round(TOKENS / step_us * 1e6)}
+    if rank == 0 and world == 1:
+        us, cores = cpu_oracle_us(3, 1)
+        line["cpu_baseline"] = {"value": round(us, 1), "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": "%d of %d rows (time scaled by %d), best-effort mean of 3" % (CPU_SAMPLE_ROWS, TOKENS, TOKENS // CPU_SAMPLE_ROWS)}
+        if not args.no_ops:
+            glue.close(); glue = None
+            line["ops"] = bench_ops(k3g, dev, peak_gbs)
+    if glue is not None:
+        glue.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="k3g", choices=["k3g", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configurations")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            sys.exit("bench.py --gpus %d must be launched with torch.distributed.run --nproc-per-node %d" % (args.gpus, args.gpus))
+        args.gpus = world
+    run_gpu(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -232,9 +232,14 @@ __global__ void __launch_bounds__(128) permute_gather_kernel(const uint8_t* __re
     const long long t = route_map[r];
     const uint4* src = reinterpret_cast<const uint4*>(q + t * cols);
     uint4* dst = reinterpret_cast<uint4*>(out_q + r * cols);
-    for (int v = threadIdx.x; v < qv; v += blockDim.x) {
-      const uint4 x = __ldg(src + v);       // a token row is read once per expert it routes to: keep it cached
-      __stcs(dst + v, x);
+    for (int v0 = threadIdx.x; v0 < qv; v0 += 4 * blockDim.x) {      // four loads in flight per thread
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * blockDim.x < qv) x[u] = __ldg(src + v0 + u * blockDim.x);   // a token row is read once per expert it routes to: keep it cached
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * blockDim.x < qv) __stcs(dst + v0 + u * blockDim.x, x[u]);
     }
     if ((sfb & 15) == 0) {
       const int sv = sfb >> 4;

@@ -23,29 +23,38 @@ extern "C" __global__ void __launch_bounds__(256) kern_k3_moe_quant(const __nv_b
   const long long nvec = (long long)rows * cols / 8;           // cols % 32 == 0: groups never straddle rows
   const long long stride = (long long)gridDim.x * blockDim.x;  // a multiple of 32: groups stay lane-aligned
   const int lane = threadIdx.x & 31;
-  for (long long i0 = (long long)blockIdx.x * blockDim.x; i0 < nvec; i0 += stride) {
-    const long long i = i0 + threadIdx.x;
-    const bool live = i < nvec;                                // nvec % 4 == 0: a group is live or dead as a whole
-    V8 v = {{0u, 0u, 0u, 0u}};
-    if (live) v = ld_stream(x + i * 8);
-    unsigned am = absmax8(v);
-    am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
-    am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
-    const int e = ue8m0_exp_from_bf16(am);
-    unsigned q0, q1;
-    quant8(v, pow2_neg(e), q0, q1);
-    unsigned sfb = (unsigned)(e + 127);
-    sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
-    sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
-    if (live) {
-      st_stream8(q + i * 8, q0, q1);
-      if ((lane & 15) == 0) {
-        // four scale bytes; the tail of the tensor may hold fewer than four groups
-        const long long g = i >> 2, ng = nvec >> 2;
-        if (g + 4 <= ng && ((reinterpret_cast<uintptr_t>(sf) + g) & 3) == 0) {
-          *reinterpret_cast<unsigned*>(sf + g) = sfb;
-        } else {
-          for (int k = 0; k < 4 && g + k < ng; ++k) sf[g + k] = (uint8_t)(sfb >> (8 * k));
+  constexpr int U = 4;                                         // vectors per thread in flight
+  for (long long i0 = (long long)blockIdx.x * blockDim.x; i0 < nvec; i0 += U * stride) {
+    V8 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride + threadIdx.x;
+      v[u] = V8{{0u, 0u, 0u, 0u}};
+      if (i < nvec) v[u] = ld_stream(x + i * 8);                // nvec % 4 == 0: a group is live or dead as a whole
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride + threadIdx.x;
+      const bool live = i < nvec;
+      unsigned am = absmax8(v[u]);
+      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
+      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
+      const int e = ue8m0_exp_from_bf16(am);
+      unsigned q0, q1;
+      quant8(v[u], pow2_neg(e), q0, q1);
+      unsigned sfb = (unsigned)(e + 127);
+      sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+      sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+      if (live) {
+        st_stream8(q + i * 8, q0, q1);
+        if ((lane & 15) == 0) {
+          // four scale bytes; the tail of the tensor may hold fewer than four groups
+          const long long g = i >> 2, ng = nvec >> 2;
+          if (g + 4 <= ng && ((reinterpret_cast<uintptr_t>(sf) + g) & 3) == 0) {
+            *reinterpret_cast<unsigned*>(sf + g) = sfb;
+          } else {
+            for (int k = 0; k < 4 && g + k < ng; ++k) sf[g + k] = (uint8_t)(sfb >> (8 * k));
+          }
         }
       }
     }
@@ -119,7 +128,7 @@ K3G_API int k3g_moe_quant(const void* x, void* q, void* sf, int rows, int cols, 
   K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
   const long long nvec = (long long)rows * cols / 8;
   if (nvec == 0) return K3G_OK;
-  long long grid = (nvec + 255) / 256;
+  long long grid = (nvec + 1023) / 1024;     // four vectors per thread
   if (grid_hint > 0 && grid_hint < grid) grid = grid_hint;
   K3G_REQUIRE(grid <= 0x7fffffffLL, K3G_ELIMIT);
   kern_k3_moe_quant<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)sf, rows, cols);

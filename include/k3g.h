@@ -64,6 +64,15 @@ int k3g_moe_quant(const void* x, void* q, void* sf, int rows, int cols, int grid
  * (op quant_fp8_tensor): per-tensor E4M3; partials holds `grid` floats. */
 int k3g_quant_fp8_tensor(const void* x, void* y, void* scale_out, void* partials, int n, int grid, void* stream);
 
+/* No counterpart in the reference.  k3g_quant_fp8_tensor for hosts that cannot allocate or pass a
+ * workspace at call time (a runtime whose memory was all handed out at load, a server that bans
+ * cudaMalloc after start-up because it synchronises the device): the block maxima live in a static
+ * 8 KB device array inside the library, so grid is limited to 2048 (K3G_ELIMIT beyond), each GPU that
+ * loads the library holds the array until exit, calls that overlap on one GPU race on it, and the
+ * first call on a device does a one-time host-side address lookup (make it before any stream
+ * capture).  Results equal k3g_quant_fp8_tensor's for the same grid. */
+int k3g_quant_fp8_tensor_noalloc(const void* x, void* y, void* scale_out, int n, int grid, void* stream);
+
 /* ---- router and MoE routing ------------------------------------------------------------------ */
 
 /* kern_k3_router_topk, source/k3_router_argmax.cu:87 (op router_topk).  experts must be 224; topk 8 or

@@ -24,7 +24,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr"]
 
 SOURCES = ["resnorm.cu", "quant.cu", "router.cu", "moe_route.cu", "collectives.cu", "mla_prep.cu", "kda.cu",
-           "peer.cu"]
+           "peer.cu", "quant_noalloc.cu"]
 
 # reference module name -> (source, defines).  Names follow kernels.toml of the reference.
 CUBINS = {

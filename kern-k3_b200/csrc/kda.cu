@@ -6,8 +6,8 @@
 //   kern_k3_kda_out_gate   source/k3_kda_out_gate_v3.cu:36-118
 //
 // span conv.  Stream s in {q,k,v}; x_i[c] = partial[(at + i) * row_stride + s * inner + c], rows
-// i < 0 come from the stored 3-row window; y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-2}, w1,
-// x_{i-3} * w0))); sb = bf16(y); out = bf16(sb * sigmoid(sb)); the new window is the last three
+// i < 0 come from the stored 3-row window; y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-3}, w0,
+// x_{i-2} * w1))) (the reference build's contraction of its four-term sum); sb = bf16(y); out = bf16(sb * sigmoid(sb)); the new window is the last three
 // INPUT rows.  A thread owns 8 consecutive columns (one 16-byte vector) and walks a run of rows
 // with the three previous inputs sliding in registers, four row loads in flight at a time;
 // rows per block = ceil(span / gridDim.z), so the reference launch (16 rows) and a coarser one
@@ -48,8 +48,8 @@ __device__ __forceinline__ V8 conv_silu_row(const float* t0, const float* t1, co
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int k = 2 * j + h;
-      float a = __fmul_rn(t0[k], w[0][k]);
-      a = __fmaf_rn(t1[k], w[1][k], a);
+      float a = __fmul_rn(t1[k], w[1][k]);
+      a = __fmaf_rn(t0[k], w[0][k], a);
       a = __fmaf_rn(t2[k], w[2][k], a);
       y[h] = __fmaf_rn(x[k], w[3][k], a);
     }

@@ -567,7 +567,9 @@ K3O_API void k3o_mla_prep_rope_pack(const u16* kv, const u16* q, const u16* gamm
 // kern_k3_span_gather (source/k3_span_gather_v3.cu:251-293; row math :131-142; window
 // :236-248).  Streams s in {q, k, v}; input row i column c of stream s = partial[(at + i) *
 // row_stride + s * inner + c]; x_{i<0} comes from the 3-row window; taps cw[s][t][c] (f32, or
-// bf16 when taps_bf16).  y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-2}, w1, x_{i-3} * w0)));
+// bf16 when taps_bf16).  y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-3}, w0, x_{i-2} * w1))) -- the
+// contraction the reference build produces for `t0*w0 + t1*w1 + t2*w2 + x*w3` (:134), established
+// against the reference kernel's own outputs (tests/golden);
 // sb = bf16(y); out = bf16(sb * sigmoid(sb)); new window = the last three inputs.
 K3O_API void k3o_span_conv_silu(const u16* partial, long long row_stride, const void* cw, int taps_bf16,
                                 u16* win /* [3][3][inner] */, u16* out_q, u16* out_k, u16* out_v, int inner,
@@ -587,8 +589,8 @@ K3O_API void k3o_span_conv_silu(const u16* partial, long long row_stride, const 
 #pragma omp parallel for schedule(static)
     for (int i = 0; i < span; ++i)
       for (int c = 0; c < inner; ++c) {
-        float y = xin(i - 3, c) * tap(0, c);
-        y = std::fmaf(xin(i - 2, c), tap(1, c), y);
+        float y = xin(i - 2, c) * tap(1, c);             // nvcc contracts t0*w0 + t1*w1 as fma(t0, w0, t1*w1)
+        y = std::fmaf(xin(i - 3, c), tap(0, c), y);
         y = std::fmaf(xin(i - 1, c), tap(2, c), y);
         y = std::fmaf(xin(i, c), tap(3, c), y);
         const float sb = land(y);

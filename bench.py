@@ -133,7 +133,7 @@ def time_us(fn, iters, warmup=3):
     return a.elapsed_time(b) * 1e3 / iters
 
 
-def bench_ops(k3g, dev, peak_gbs, iters=20):
+def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     """Per-op device times of the other benchmark configurations at their 16k-token shapes (N = 1),
     each with its algorithmic bytes (unique bytes that must cross HBM once)."""
     import torch
@@ -144,6 +144,8 @@ def bench_ops(k3g, dev, peak_gbs, iters=20):
     out = []
 
     def add(name, fn, nbytes):
+        if only and only not in name:
+            return
         us = time_us(fn, iters)
         out.append({"op": name, "us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_measured": round(nbytes / us / 1e3 / peak_gbs, 3),
                     "frac_8tbs": round(nbytes / us / 1e3 / 8000.0, 3)})
@@ -178,6 +180,7 @@ def bench_ops(k3g, dev, peak_gbs, iters=20):
         k3g.call("k3g_moe_route_count", ids64, T, 0, 64, 8, 1, 0, bc, s)
         k3g.call("k3g_moe_route_tables", bc, blocks, 64, tile, bo, cb, cl, nne, tot, rm, s)
         k3g.call("k3g_moe_route_scatter", ids64, bo, T, 0, 64, 8, 1, 0, rm, e2p, s)
+    route()
     add("config2 route count+tables+scatter (3 launches)", route, T * 8 * 4 * 4)
     torch.cuda.synchronize()
     rows = int(tot.item())             # tile-padded permuted rows (padding rows route token 0)
@@ -245,11 +248,16 @@ def run_gpu(args, rank, world, local_rank):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item()) / steps * 1e3
 
+    # headline: the step replayed as a CUDA graph (how the reference's runtime runs its program)
     sampler = ClockSampler(physical_gpu_index(local_rank))
-    glue.kernel_events = []
     warm = max(args.warmup, 3)
-    step_us = timed(glue.step, args.steps, warm, sampler)
+    glue.capture()
+    step_us = timed(glue.replay, args.steps, warm, sampler)
     clocks = sampler.finish()
+    glue.check_status()
+    # the same K steps launched eagerly with an event pair around the fused kernel: its duration
+    glue.kernel_events = []
+    eager_us = timed(glue.step, args.steps, 3)
     ev = glue.kernel_events[-args.steps:]
     glue.kernel_events = None
     kern_us = sum(a.elapsed_time(b) for a, b in ev) / len(ev) * 1e3
@@ -279,9 +287,9 @@ def run_gpu(args, rank, world, local_rank):
             "ms_per_step": round(step_us / 1e3, 5), "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "config1: TP reduce-scatter -> residual add + RMSNorm + MXFP8 -> all-gather, T=16384 d=7168, world=%d" % W,
                        "tokens": TOKENS, "d": HIDDEN, "world": W, "l2": "inputs (470 MB read per step at world 1) exceed the 126 MB L2; no flush"},
-            "clocks": clocks, "roofline": roof, "nvlink": nv,
+            "clocks": clocks, "roofline": roof, "nvlink": nv, "launch_mode": "cuda graph replay of 4 kernels per step (epoch bump, arrive, fused kernel, arrive)",
             "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps},
-            "gpu_launches": LAUNCHES_PER_STEP * args.steps, "tokens_per_s": round(TOKENS / step_us * 1e6)}
+            "gpu_launches": LAUNCHES_PER_STEP * args.steps, "eager_step_us": round(eager_us, 2), "tokens_per_s": round(TOKENS / step_us * 1e6)}
     if rank == 0 and world == 1:
         us, cores = cpu_oracle_us(3, 1)
         line["cpu_baseline"] = {"value": round(us, 1), "unit": UNIT, "cores": cores, "kind": "port",
@@ -304,11 +312,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="k3g", choices=["k3g", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configurations")
+    ap.add_argument("--ops-only", default=None, metavar="SUBSTR", help="run only the per-op microbenchmarks whose name contains SUBSTR "
+                    "('' = all) and print their table; for profiling a single kernel")
+    ap.add_argument("--op-iters", type=int, default=20)
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.ops_only is not None:
+        import torch
+        import k3g
+        torch.cuda.set_device(local_rank)
+        for row in bench_ops(k3g, torch.device("cuda"), measured_peaks()[0], iters=args.op_iters, only=args.ops_only or None):
+            print(json.dumps(row), flush=True)
         return
     if world != args.gpus:
         if world == 1 and args.gpus > 1:

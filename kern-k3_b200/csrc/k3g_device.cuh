@@ -62,6 +62,29 @@ __device__ __forceinline__ unsigned absmax_bf2(unsigned m, unsigned x) {
 }
 __device__ __forceinline__ float land_bf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// ---- packed f32x2 arithmetic (sm_100: one instruction for two IEEE round-to-nearest results) ----
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) { f32x2 r; asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0,%1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 f2_splat(float a) { return f2_pack(a, a); }
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+// a bf16 pair widened to an f32 pair, and an f32 pair rounded (RNE) to a bf16 pair
+__device__ __forceinline__ f32x2 f2_from_bf2(unsigned u) { return f2_pack(bf_lo(u), bf_hi(u)); }
+__device__ __forceinline__ unsigned f2_to_bf2(f32x2 v) { float lo, hi; f2_unpack(v, lo, hi); return pack_bf2(lo, hi); }
+// sigmoid of a pair: packed scale and add, one ex2.approx and one rcp.approx per element
+__device__ __forceinline__ f32x2 f2_fast_sigmoid(f32x2 x) {
+  float a, b, ea, eb, ra, rb;
+  f2_unpack(f2_mul(x, f2_splat(-1.4426950408889634f)), a, b);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ea) : "f"(a));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(eb) : "f"(b));
+  f2_unpack(f2_add(f2_pack(ea, eb), f2_splat(1.0f)), a, b);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ra) : "f"(a));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rb) : "f"(b));
+  return f2_pack(ra, rb);
+}
+
 // ---- fixed-order reductions --------------------------------------------------------------
 template <int LANES>
 __device__ __forceinline__ float butterfly_sum(float v) {

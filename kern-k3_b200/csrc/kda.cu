@@ -8,8 +8,8 @@
 // span conv.  Stream s in {q,k,v}; x_i[c] = partial[(at + i) * row_stride + s * inner + c], rows
 // i < 0 come from the stored 3-row window; y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-3}, w0,
 // x_{i-2} * w1))) (the reference build's contraction of its four-term sum); sb = bf16(y); out = bf16(sb * sigmoid(sb)); the new window is the last three
-// INPUT rows.  A thread owns 8 consecutive columns (one 16-byte vector) and walks a run of rows
-// with the three previous inputs sliding in registers, four row loads in flight at a time;
+// INPUT rows.  A thread owns 4 consecutive columns (8 bytes) and walks a run of rows with the three
+// previous inputs sliding in registers, four row loads in flight at a time, eight blocks per SM;
 // rows per block = ceil(span / gridDim.z), so the reference launch (16 rows) and a coarser one
 // (fewer halo re-reads) are both valid.  The sigmoid is ex2.approx + rcp.approx, as in the
 // reference: two MUFU ops per element is what a 6.5 TB/s stream leaves room for.
@@ -24,105 +24,125 @@ using namespace k3g;
 
 namespace {
 
-__device__ __forceinline__ void unpack8(const V8& v, float* x) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) { x[2 * j] = bf_lo(v.w[j]); x[2 * j + 1] = bf_hi(v.w[j]); }
-}
+// A thread owns kVec = 4 consecutive columns (8 bytes): small register footprint (the three sliding
+// taps, one chunk of rows and 16 tap weights), so eight 128-thread blocks stay resident per SM.
+#ifndef K3G_SPAN_CHUNK
+#define K3G_SPAN_CHUNK 4
+#endif
+#ifndef K3G_SPAN_MINB
+#define K3G_SPAN_MINB 8
+#endif
+#ifndef K3G_SPAN_PACKED
+#define K3G_SPAN_PACKED 0   /* packed f32x2 conv math measured no faster than scalar on B200 */
+#endif
+constexpr int kVec = 4;
+constexpr int kChunk = K3G_SPAN_CHUNK;
 
+__device__ __forceinline__ uint2 ld8_stream(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+// taps of this thread's 4 columns as two f32 pairs per tap
 template <bool TAPS_BF16>
-__device__ __forceinline__ void load_taps(const void* cw, size_t off, float* w) {
+__device__ __forceinline__ void load_taps(const void* cw, size_t off, f32x2* w) {
   if (TAPS_BF16) {
-    unpack8(ld_keep(reinterpret_cast<const __nv_bfloat16*>(cw) + off), w);
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(cw) + off));
+    w[0] = f2_from_bf2(v.x); w[1] = f2_from_bf2(v.y);
   } else {
     const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(cw) + off));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(cw) + off + 4));
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    w[0] = f2_pack(a.x, a.y); w[1] = f2_pack(a.z, a.w);
   }
 }
 
-__device__ __forceinline__ V8 conv_silu_row(const float* t0, const float* t1, const float* t2, const float* x, const float (*w)[8]) {
-  V8 o;
+// One output row of 4 columns.  Rows are held as two f32 pairs; every arithmetic step is the packed
+// form of the scalar recipe (same roundings): y = fma(x, w3, fma(t2, w2, fma(t0, w0, t1 * w1))).
+__device__ __forceinline__ uint2 conv_silu_row(const f32x2* t0, const f32x2* t1, const f32x2* t2, const f32x2* x, const f32x2 (*w)[2]) {
+  unsigned o[2];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float y[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int k = 2 * j + h;
-      float a = __fmul_rn(t1[k], w[1][k]);
-      a = __fmaf_rn(t0[k], w[0][k], a);
-      a = __fmaf_rn(t2[k], w[2][k], a);
-      y[h] = __fmaf_rn(x[k], w[3][k], a);
-    }
-    const unsigned sbp = pack_bf2(y[0], y[1]);
+  for (int j = 0; j < 2; ++j) {
+#if K3G_SPAN_PACKED
+    f32x2 a = f2_mul(t1[j], w[1][j]);
+    a = f2_fma(t0[j], w[0][j], a);
+    a = f2_fma(t2[j], w[2][j], a);
+    a = f2_fma(x[j], w[3][j], a);
+    const f32x2 sb = f2_from_bf2(f2_to_bf2(a));
+    o[j] = f2_to_bf2(f2_mul(sb, f2_fast_sigmoid(sb)));
+#else
+    float t0a, t0b, t1a, t1b, t2a, t2b, xa, xb, w0a, w0b, w1a, w1b, w2a, w2b, w3a, w3b;
+    f2_unpack(t0[j], t0a, t0b); f2_unpack(t1[j], t1a, t1b); f2_unpack(t2[j], t2a, t2b); f2_unpack(x[j], xa, xb);
+    f2_unpack(w[0][j], w0a, w0b); f2_unpack(w[1][j], w1a, w1b); f2_unpack(w[2][j], w2a, w2b); f2_unpack(w[3][j], w3a, w3b);
+    const float ya = __fmaf_rn(xa, w3a, __fmaf_rn(t2a, w2a, __fmaf_rn(t0a, w0a, __fmul_rn(t1a, w1a))));
+    const float yb = __fmaf_rn(xb, w3b, __fmaf_rn(t2b, w2b, __fmaf_rn(t0b, w0b, __fmul_rn(t1b, w1b))));
+    const unsigned sbp = pack_bf2(ya, yb);
     const float s0 = bf_lo(sbp), s1 = bf_hi(sbp);
-    o.w[j] = pack_bf2(s0 * fast_sigmoid(s0), s1 * fast_sigmoid(s1));
+    o[j] = pack_bf2(s0 * fast_sigmoid(s0), s1 * fast_sigmoid(s1));
+#endif
   }
-  return o;
+  return make_uint2(o[0], o[1]);
 }
-
-constexpr int kChunk = 4;
 
 template <bool TAPS_BF16>
 __device__ __forceinline__ void span_stream(const __nv_bfloat16* __restrict__ partial, long long row_stride, const void* __restrict__ cw,
                                             __nv_bfloat16* win, __nv_bfloat16* __restrict__ out, int inner, int s, int c, int row0,
                                             int row1, int span) {
-  float w[4][8];
+  f32x2 w[4][2];
 #pragma unroll
   for (int t = 0; t < 4; ++t) load_taps<TAPS_BF16>(cw, ((size_t)s * 4 + t) * inner + c, w[t]);
   const __nv_bfloat16* col = partial + (size_t)s * inner + c;
   const bool first = row0 == 0;
-  float x[kChunk + 3][8];
+  f32x2 x[kChunk + 3][2];
 #pragma unroll
   for (int t = 0; t < 3; ++t) {
     const int i = row0 - 3 + t;
-    unpack8(i < 0 ? ld_plain(win + (size_t)(i + 3) * inner + c) : ld_stream(col + (size_t)i * row_stride), x[t]);
+    const uint2 v = i < 0 ? *reinterpret_cast<const uint2*>(win + (size_t)(i + 3) * inner + c) : ld8_stream(col + (size_t)i * row_stride);
+    x[t][0] = f2_from_bf2(v.x); x[t][1] = f2_from_bf2(v.y);
   }
   for (int r0 = row0; r0 < row1; r0 += kChunk) {
-    V8 raw[kChunk];
+    uint2 raw[kChunk];
 #pragma unroll
     for (int r = 0; r < kChunk; ++r)
-      if (r0 + r < row1) raw[r] = ld_stream(col + (size_t)(r0 + r) * row_stride);
+      if (r0 + r < row1) raw[r] = ld8_stream(col + (size_t)(r0 + r) * row_stride);
 #pragma unroll
     for (int r = 0; r < kChunk; ++r)
-      if (r0 + r < row1) unpack8(raw[r], x[3 + r]);
+      if (r0 + r < row1) { x[3 + r][0] = f2_from_bf2(raw[r].x); x[3 + r][1] = f2_from_bf2(raw[r].y); }
 #pragma unroll
     for (int r = 0; r < kChunk; ++r)
-      if (r0 + r < row1) st_stream(out + (size_t)(r0 + r) * inner + c, conv_silu_row(x[r], x[r + 1], x[r + 2], x[r + 3], w));
+      if (r0 + r < row1) __stcs(reinterpret_cast<uint2*>(out + (size_t)(r0 + r) * inner + c), conv_silu_row(x[r], x[r + 1], x[r + 2], x[r + 3], w));
 #pragma unroll
-    for (int t = 0; t < 3; ++t)
-#pragma unroll
-      for (int k = 0; k < 8; ++k) x[t][k] = x[kChunk + t][k];
+    for (int t = 0; t < 3; ++t) { x[t][0] = x[kChunk + t][0]; x[t][1] = x[kChunk + t][1]; }
   }
   if (first) {
     // new window = inputs span-3 .. span-1 (old window rows when span < 3); this thread has
     // already read every old tap it needs, and no other thread touches these columns
-    V8 nw[3];
+    uint2 nw[3];
 #pragma unroll
     for (int t = 0; t < 3; ++t) {
       const int i = span - 3 + t;
-      nw[t] = i < 0 ? ld_plain(win + (size_t)(i + 3) * inner + c) : ld_stream(col + (size_t)i * row_stride);
+      nw[t] = i < 0 ? *reinterpret_cast<const uint2*>(win + (size_t)(i + 3) * inner + c) : ld8_stream(col + (size_t)i * row_stride);
     }
 #pragma unroll
-    for (int t = 0; t < 3; ++t) st_plain(win + (size_t)t * inner + c, nw[t]);
+    for (int t = 0; t < 3; ++t) *reinterpret_cast<uint2*>(win + (size_t)t * inner + c) = nw[t];
   }
 }
 
-// beta transpose + flow landing for the rows of one block
+// beta transpose + flow landing: the rows of one z-chunk are dealt round-robin to the chunk's x-blocks
 __device__ __forceinline__ void span_beta_flow(const float* __restrict__ wsm, int heads, __nv_bfloat16* __restrict__ span_beta,
                                                __nv_bfloat16* __restrict__ span_flow, int row0, int row1, int span) {
-  const int R = row1 - row0;
+  const int R = (row1 - row0 - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // rows row0 + blockIdx.x + k * gridDim.x
+  if (R <= 0) return;
   for (int idx = threadIdx.x; idx < R * heads; idx += blockDim.x) {
-    const int h = idx / R, i = row0 + idx % R;
-    span_beta[(size_t)h * span + i] = __float2bfloat16_rn(wsm[(size_t)i * 256 + h]);
+    const int h = idx / R, i = row0 + (int)blockIdx.x + (idx % R) * (int)gridDim.x;
+    span_beta[(size_t)h * span + i] = __float2bfloat16_rn(__ldg(wsm + (size_t)i * 256 + h));
   }
   for (int idx = threadIdx.x; idx < R * 32; idx += blockDim.x) {
-    const int i = row0 + idx / 32, c4 = (idx % 32) * 4;
+    const int i = row0 + (int)blockIdx.x + (idx / 32) * (int)gridDim.x, c4 = (idx % 32) * 4;
     const float4 v = __ldcs(reinterpret_cast<const float4*>(wsm + (size_t)i * 256 + 96 + c4));
     *reinterpret_cast<uint2*>(span_flow + (size_t)i * 128 + c4) = make_uint2(pack_bf2(v.x, v.y), pack_bf2(v.z, v.w));
   }
 }
 
-// grid (ceil(inner / 1024), 4, row chunks), block 128: y < 3 = stream, y == 3 = beta/flow (optional)
+// grid (ceil(inner / 512), 4, row chunks), block 128: y < 3 = stream, y == 3 = beta/flow (optional)
 template <bool TAPS_BF16>
 __device__ __forceinline__ void span_gather_body(const __nv_bfloat16* __restrict__ partial, long long row_stride, const void* __restrict__ cw,
                                                  __nv_bfloat16* win_base, const float* __restrict__ wsm_partial, __nv_bfloat16* span_q,
@@ -133,11 +153,11 @@ __device__ __forceinline__ void span_gather_body(const __nv_bfloat16* __restrict
   const int row0 = blockIdx.z * rpb, row1 = min(span, row0 + rpb);
   if (row0 >= span) return;
   if (blockIdx.y == 3) {
-    if (blockIdx.x == 0 && wsm_partial) span_beta_flow(wsm_partial + (size_t)at * 256, heads, span_beta, span_flow, row0, row1, span);
+    if (wsm_partial) span_beta_flow(wsm_partial + (size_t)at * 256, heads, span_beta, span_flow, row0, row1, span);
     return;
   }
   const int s = blockIdx.y;
-  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * kVec;
   if (c >= inner) return;
   __nv_bfloat16* out = s == 0 ? span_q : s == 1 ? span_k : span_v;
   span_stream<TAPS_BF16>(partial + (size_t)at * row_stride, row_stride, cw, win_base + (size_t)s * 3 * inner, out, inner, s, c, row0, row1,
@@ -145,7 +165,7 @@ __device__ __forceinline__ void span_gather_body(const __nv_bfloat16* __restrict
 }
 
 template <bool TAPS_BF16>
-__global__ void __launch_bounds__(128) span_conv_kernel(const __nv_bfloat16* partial, long long row_stride, const void* cw, __nv_bfloat16* win,
+__global__ void __launch_bounds__(128, K3G_SPAN_MINB) span_conv_kernel(const __nv_bfloat16* partial, long long row_stride, const void* cw, __nv_bfloat16* win,
                                                         const float* wsm_partial, __nv_bfloat16* span_q, __nv_bfloat16* span_k,
                                                         __nv_bfloat16* span_v, __nv_bfloat16* span_beta, __nv_bfloat16* span_flow,
                                                         int heads, int at, int span) {
@@ -153,44 +173,45 @@ __global__ void __launch_bounds__(128) span_conv_kernel(const __nv_bfloat16* par
 }
 
 // ---- output gate -----------------------------------------------------------------------------------
+// grid (rows, ceil(heads * 16 / blockDim.x)): blockIdx.x walks rows (grid-stride), blockIdx.y * blockDim.x
+// + threadIdx.x is the thread's 8-column vector inside the row -- no integer division anywhere.
 template <bool STORE_GATED, bool QUANT>
 __device__ __forceinline__ void out_gate_body(const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ gate,
                                               long long gate_stride, long long gate_off, const float* __restrict__ gamma_o,
                                               __nv_bfloat16* __restrict__ gated, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                               int heads, int at, int span, float eps) {
   const int inner = heads * 128;
-  const int tpr = heads * 16;                                  // threads per row
-  const long long total = (long long)span * tpr;
-  const long long nthreads = (long long)gridDim.x * gridDim.y * blockDim.x;
+  const int vec = blockIdx.y * blockDim.x + threadIdx.x;
+  const int col = vec * 8;
+  const bool live = col < inner;                               // heads * 16 is a multiple of 16: half-warps are live or dead whole
   const int lane = threadIdx.x & 31;
-  const long long first = ((long long)blockIdx.x * gridDim.y + blockIdx.y) * blockDim.x;
-  for (long long base = first; base < total; base += nthreads) {   // block-uniform trip count; tpr % 32 == 0 keeps warps whole
-    const long long g = base + threadIdx.x;
-    const bool live = g < total;
-    const long long i = live ? g / tpr : 0;
-    const int col = live ? (int)(g - i * tpr) * 8 : 0;
+  const int d0 = col & 127;
+  f32x2 gm[4];
+  {
+    const float4 m0 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0)), m1 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0 + 4));
+    gm[0] = f2_pack(m0.x, m0.y); gm[1] = f2_pack(m0.z, m0.w); gm[2] = f2_pack(m1.x, m1.y); gm[3] = f2_pack(m1.z, m1.w);
+  }
+  for (int i = blockIdx.x; i < span; i += gridDim.x) {
     const long long b = at + i;
     V8 av = {{0u, 0u, 0u, 0u}}, gv = {{0u, 0u, 0u, 0u}};
     if (live) {
       av = ld_stream(attn + (size_t)i * inner + col);
       gv = ld_stream(gate + (size_t)b * gate_stride + gate_off + col);
     }
-    float a[8], gg[8], gm[8];
-    unpack8(av, a);
-    unpack8(gv, gg);
-    const int d0 = col & 127;
-    const float4 m0 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0)), m1 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0 + 4));
-    gm[0] = m0.x; gm[1] = m0.y; gm[2] = m0.z; gm[3] = m0.w; gm[4] = m1.x; gm[5] = m1.y; gm[6] = m1.z; gm[7] = m1.w;
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) ss = __fmaf_rn(a[k], a[k], ss);
+    for (int j = 0; j < 4; ++j) {
+      const float lo = bf_lo(av.w[j]), hi = bf_hi(av.w[j]);
+      ss = __fmaf_rn(lo, lo, ss);
+      ss = __fmaf_rn(hi, hi, ss);
+    }
     ss = butterfly_sum<16>(ss);
-    const float r = __frsqrt_rn(__fmaf_rn(ss, 1.0f / 128.0f, eps));
+    const f32x2 r2 = f2_splat(__frsqrt_rn(__fmaf_rn(ss, 1.0f / 128.0f, eps)));
     V8 o;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const unsigned ov = pack_bf2(__fmul_rn(__fmul_rn(a[2 * j], r), gm[2 * j]), __fmul_rn(__fmul_rn(a[2 * j + 1], r), gm[2 * j + 1]));
-      const unsigned gt = pack_bf2(fast_sigmoid(gg[2 * j]), fast_sigmoid(gg[2 * j + 1]));
+      const unsigned ov = f2_to_bf2(f2_mul(f2_mul(f2_from_bf2(av.w[j]), r2), gm[j]));
+      const unsigned gt = f2_to_bf2(f2_fast_sigmoid(f2_from_bf2(gv.w[j])));
       o.w[j] = mul_bf2(ov, gt);
     }
     if (STORE_GATED && live) st_stream(gated + (size_t)b * inner + col, o);
@@ -213,7 +234,7 @@ __device__ __forceinline__ void out_gate_body(const __nv_bfloat16* __restrict__ 
 }
 
 template <bool STORE_GATED, bool QUANT>
-__global__ void __launch_bounds__(256) out_gate_kernel(const __nv_bfloat16* attn, const __nv_bfloat16* gate, long long gate_stride,
+__global__ void __launch_bounds__(128) out_gate_kernel(const __nv_bfloat16* attn, const __nv_bfloat16* gate, long long gate_stride,
                                                        long long gate_off, const float* gamma_o, __nv_bfloat16* gated, uint8_t* q,
                                                        uint8_t* sf, int heads, int at, int span, float eps) {
   out_gate_body<STORE_GATED, QUANT>(attn, gate, gate_stride, gate_off, gamma_o, gated, q, sf, heads, at, span, eps);
@@ -228,7 +249,7 @@ __global__ void __launch_bounds__(256) out_gate_kernel(const __nv_bfloat16* attn
 #define K3G_KDA_INNER (HEADS * 128)
 #define K3G_KDA_REC_BYTES ((long long)HEADS * 128 * 128 * 4)
 
-extern "C" __global__ void __launch_bounds__(128) kern_k3_span_gather(
+extern "C" __global__ void __launch_bounds__(128, K3G_SPAN_MINB) kern_k3_span_gather(
     const __nv_bfloat16* __restrict__ partial, const float* __restrict__ cw, void* __restrict__ kda_base, const int* __restrict__ line_index,
     long long line_bytes, const float* __restrict__ wsm_partial, __nv_bfloat16* __restrict__ span_q, __nv_bfloat16* __restrict__ span_k,
     __nv_bfloat16* __restrict__ span_v, __nv_bfloat16* __restrict__ span_beta, __nv_bfloat16* __restrict__ span_flow,
@@ -250,7 +271,7 @@ extern "C" __global__ void __launch_bounds__(128) kern_k3_kda_out_gate(const __n
 // Conv + SiLU on the three streams.  win: [3 streams][3 rows][inner] bf16, read as the initial
 // state and overwritten with the final one (zero-fill it for a zero initial state).  cw:
 // [3][4][inner] taps, f32 or bf16.  wsm_partial (f32 [rows, 256]) may be null: then span_beta /
-// span_flow are not produced.  rows_per_block <= 0 selects 32.
+// span_flow are not produced.  rows_per_block <= 0 selects 64.
 K3G_API int k3g_span_gather(const void* partial, long long row_stride, const void* cw, int taps_bf16, void* win, const void* wsm_partial,
                             void* span_q, void* span_k, void* span_v, void* span_beta, void* span_flow, int heads, int at, int span,
                             int rows_per_block, void* stream) {
@@ -260,9 +281,9 @@ K3G_API int k3g_span_gather(const void* partial, long long row_stride, const voi
   K3G_REQUIRE_ALIGNED(span_v);
   K3G_REQUIRE(heads > 0 && heads <= 512 && span >= 0 && at >= 0 && row_stride >= 3LL * heads * 128 && row_stride % 8 == 0, K3G_ESHAPE);
   if (span == 0) return K3G_OK;
-  const int rpb = rows_per_block > 0 ? rows_per_block : 32;
+  const int rpb = rows_per_block > 0 ? rows_per_block : 64;
   const int inner = heads * 128;
-  const dim3 grid((inner + 1023) / 1024, wsm_partial ? 4 : 3, (span + rpb - 1) / rpb);
+  const dim3 grid((inner + 511) / 512, wsm_partial ? 4 : 3, (span + rpb - 1) / rpb);
   K3G_REQUIRE(grid.z <= 65535, K3G_ELIMIT);
   if (taps_bf16)
     span_conv_kernel<true><<<grid, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)partial, row_stride, cw, (__nv_bfloat16*)win,
@@ -288,16 +309,13 @@ K3G_API int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_
   K3G_REQUIRE(((uintptr_t)q & 7) == 0 && ((uintptr_t)sf & 3) == 0, K3G_EALIGN);
   K3G_REQUIRE(heads > 0 && heads % 2 == 0 && span >= 0 && at >= 0 && gate_stride % 8 == 0 && gate_off % 8 == 0, K3G_ESHAPE);
   if (span == 0) return K3G_OK;
-  const long long total = (long long)span * heads * 16;
-  const long long blocks = (total + 255) / 256;
-  K3G_REQUIRE(blocks <= 0x7fffffffLL, K3G_ELIMIT);
-  const dim3 grid((unsigned)blocks, 1, 1);
+  const dim3 grid((unsigned)span, (unsigned)((heads * 16 + 127) / 128), 1);
   cudaStream_t st = k3g_stream(stream);
 #define K3G_OG_ARGS (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, gate_stride, gate_off, (const float*)gamma_o, \
     (__nv_bfloat16*)gated, (uint8_t*)q, (uint8_t*)sf, heads, at, span, eps
-  if (gated && q) out_gate_kernel<true, true><<<grid, 256, 0, st>>>(K3G_OG_ARGS);
-  else if (gated) out_gate_kernel<true, false><<<grid, 256, 0, st>>>(K3G_OG_ARGS);
-  else out_gate_kernel<false, true><<<grid, 256, 0, st>>>(K3G_OG_ARGS);
+  if (gated && q) out_gate_kernel<true, true><<<grid, 128, 0, st>>>(K3G_OG_ARGS);
+  else if (gated) out_gate_kernel<true, false><<<grid, 128, 0, st>>>(K3G_OG_ARGS);
+  else out_gate_kernel<false, true><<<grid, 128, 0, st>>>(K3G_OG_ARGS);
 #undef K3G_OG_ARGS
   return k3g_launch_status();
 }

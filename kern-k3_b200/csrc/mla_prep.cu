@@ -150,24 +150,44 @@ __global__ void __launch_bounds__(128) mla_rope_pack_kernel(const __nv_bfloat16*
     const V8 cs = ld_plain(rope_tab + (size_t)t * 64 + 8 * c), sn = ld_plain(rope_tab + (size_t)t * 64 + 32 + 8 * c);
     V8 k1, k2;
     rope8(ld_plain(kvr + kKV + 8 * c), ld_plain(kvr + kKV + 32 + 8 * c), cs, sn, k1, k2);
-    for (int h0 = 0; h0 < heads; h0 += 8) {
-      const int h = h0 + (lane >> 2);
-      if (h < heads) {
-        const size_t o = ((size_t)t * heads + h) * 192 + 128;
-        V8 o1, o2;
-        rope8(ld_stream(q + o + 8 * c), ld_stream(q + o + 32 + 8 * c), cs, sn, o1, o2);
-        st_stream(q_out + o + 8 * c, o1);
-        st_stream(q_out + o + 32 + 8 * c, o2);
-        st_stream(k_out + o + 8 * c, k1);
-        st_stream(k_out + o + 32 + 8 * c, k2);
+    // all loads of a batch are issued before its first store (a store orders later loads behind it)
+    for (int h0 = 0; h0 < heads; h0 += 16) {                  // two rope passes (8 heads each) per batch
+      V8 a1[2], a2[2];
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        const int h = h0 + 8 * p + (lane >> 2);
+        if (h < heads) {
+          const size_t o = ((size_t)t * heads + h) * 192 + 128;
+          a1[p] = ld_stream(q + o + 8 * c);
+          a2[p] = ld_stream(q + o + 32 + 8 * c);
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        const int h = h0 + 8 * p + (lane >> 2);
+        if (h < heads) {
+          const size_t o = ((size_t)t * heads + h) * 192 + 128;
+          V8 o1, o2;
+          rope8(a1[p], a2[p], cs, sn, o1, o2);
+          st_stream(q_out + o + 8 * c, o1);
+          st_stream(q_out + o + 32 + 8 * c, o2);
+          st_stream(k_out + o + 8 * c, k1);
+          st_stream(k_out + o + 32 + 8 * c, k2);
+        }
       }
     }
-    // nope copy: 16 vectors per head, two heads per pass
-    for (int h0 = 0; h0 < heads; h0 += 2) {
-      const int h = h0 + (lane >> 4);
-      if (h < heads) {
-        const size_t o = ((size_t)t * heads + h) * 192 + 8 * (lane & 15);
-        st_stream(q_out + o, ld_stream(q + o));
+    // nope copy: 16 vectors per head, two heads per pass, eight passes per batch
+    for (int h0 = 0; h0 < heads; h0 += 16) {
+      V8 n8[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const int h = h0 + 2 * p + (lane >> 4);
+        if (h < heads) n8[p] = ld_stream(q + ((size_t)t * heads + h) * 192 + 8 * (lane & 15));
+      }
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const int h = h0 + 2 * p + (lane >> 4);
+        if (h < heads) st_stream(q_out + ((size_t)t * heads + h) * 192 + 8 * (lane & 15), n8[p]);
       }
     }
   }

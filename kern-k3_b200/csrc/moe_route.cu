@@ -182,43 +182,54 @@ __device__ __forceinline__ void finalize_body(const __nv_bfloat16* __restrict__ 
     }
     __syncthreads();
     const int n = s_n[buf];
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-      float acc[8];
+    // two 16-byte column vectors per thread at a time, rows in chunks of four: eight loads in flight
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 2 * blockDim.x) {
+      const int v1 = v0 + blockDim.x;
+      const bool two = v1 < nvec;
+      float acc0[8], acc1[8];
 #pragma unroll
-      for (int l = 0; l < 8; ++l) acc[l] = 0.f;
-      int i = 0;
-      for (; i + 4 <= n; i += 4) {           // four row loads in flight
-        V8 x[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) x[u] = ld_stream(fc2 + (size_t)s_row[buf][i + u] * cols + v * 8);
+      for (int l = 0; l < 8; ++l) { acc0[l] = 0.f; acc1[l] = 0.f; }
+      for (int i = 0; i < n; i += 4) {
+        V8 x0[4], x1[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const float w = s_w[buf][i + u];
+          if (i + u < n) {
+            const __nv_bfloat16* rowp = fc2 + (size_t)s_row[buf][i + u] * cols;
+            x0[u] = ld_stream(rowp + v0 * 8);
+            if (two) x1[u] = ld_stream(rowp + v1 * 8);
+          }
+        }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] = __fmaf_rn(w, bf_lo(x[u].w[j]), acc[2 * j]);
-            acc[2 * j + 1] = __fmaf_rn(w, bf_hi(x[u].w[j]), acc[2 * j + 1]);
+        for (int u = 0; u < 4; ++u) {
+          if (i + u < n) {
+            const float w = s_w[buf][i + u];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              acc0[2 * j] = __fmaf_rn(w, bf_lo(x0[u].w[j]), acc0[2 * j]);
+              acc0[2 * j + 1] = __fmaf_rn(w, bf_hi(x0[u].w[j]), acc0[2 * j + 1]);
+              if (two) {
+                acc1[2 * j] = __fmaf_rn(w, bf_lo(x1[u].w[j]), acc1[2 * j]);
+                acc1[2 * j + 1] = __fmaf_rn(w, bf_hi(x1[u].w[j]), acc1[2 * j + 1]);
+              }
+            }
           }
         }
       }
-      for (; i < n; ++i) {
-        const V8 x = ld_stream(fc2 + (size_t)s_row[buf][i] * cols + v * 8);
-        const float w = s_w[buf][i];
+      V8 o0, o1;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          acc[2 * j] = __fmaf_rn(w, bf_lo(x.w[j]), acc[2 * j]);
-          acc[2 * j + 1] = __fmaf_rn(w, bf_hi(x.w[j]), acc[2 * j + 1]);
+      for (int j = 0; j < 4; ++j) { o0.w[j] = pack_bf2(acc0[2 * j], acc0[2 * j + 1]); o1.w[j] = pack_bf2(acc1[2 * j], acc1[2 * j + 1]); }
+      if (RESIDUAL) {
+        const V8 r0 = ld_stream(residual + (size_t)t * cols + v0 * 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o0.w[j] = add_bf2(r0.w[j], o0.w[j]);
+        if (two) {
+          const V8 r1 = ld_stream(residual + (size_t)t * cols + v1 * 8);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o1.w[j] = add_bf2(r1.w[j], o1.w[j]);
         }
       }
-      V8 o;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) o.w[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
-      if (RESIDUAL) {
-        const V8 r = ld_stream(residual + (size_t)t * cols + v * 8);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o.w[j] = add_bf2(r.w[j], o.w[j]);
-      }
-      st_stream(out + (size_t)t * cols + v * 8, o);
+      st_stream(out + (size_t)t * cols + v0 * 8, o0);
+      if (two) st_stream(out + (size_t)t * cols + v1 * 8, o1);
     }
   }
 }

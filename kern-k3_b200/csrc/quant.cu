@@ -5,10 +5,9 @@
 //   kern_quant_fp8_amax_v2   per-tensor pair: partial |max| per block            (replaces
 //   kern_quant_fp8_apply_v2  scale = amax / 448, y = e4m3(x / scale)              source/k3_quant_fp8_pair_v2.cu:42-95)
 //
-// MXFP8 layout: a thread owns one 16-byte vector (8 elements); the four threads of a group
-// are adjacent lanes, so the group amax is two xor-shuffles, every load is a coalesced 16 B
-// and every code store a coalesced 8 B.  The exponent is computed on the bf16 bits of amax
-// (exact integer arithmetic, no log2).
+// MXFP8 layout: a thread owns one 32-element group (64 contiguous input bytes): four 16-byte
+// loads in flight, the amax taken in registers, 32 code bytes out as two 16-byte stores.  The
+// exponent is computed on the bf16 bits of amax (exact integer arithmetic, no log2).
 //
 // Per-tensor pair: the amax pass walks the tensor forwards with ordinary (L2-allocating)
 // loads and the apply pass walks it backwards, so the tail the first pass left in the 126 MB
@@ -20,44 +19,27 @@ using namespace k3g;
 
 extern "C" __global__ void __launch_bounds__(256) kern_k3_moe_quant(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                                                    uint8_t* __restrict__ sf, int rows, int cols) {
-  const long long nvec = (long long)rows * cols / 8;           // cols % 32 == 0: groups never straddle rows
-  const long long stride = (long long)gridDim.x * blockDim.x;  // a multiple of 32: groups stay lane-aligned
-  const int lane = threadIdx.x & 31;
-  constexpr int U = 4;                                         // vectors per thread in flight
-  for (long long i0 = (long long)blockIdx.x * blockDim.x; i0 < nvec; i0 += U * stride) {
-    V8 v[U];
+  // One thread per 32-element group: four 16-byte loads in flight, amax in registers (no
+  // shuffles), two 16-byte code stores and one scale byte (a warp's 32 scale bytes are contiguous).
+  const long long ngroups = (long long)rows * cols / 32;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < ngroups; g += (long long)gridDim.x * blockDim.x) {
+    const __nv_bfloat16* src = x + g * 32;
+    V8 v[4];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long i = i0 + u * stride + threadIdx.x;
-      v[u] = V8{{0u, 0u, 0u, 0u}};
-      if (i < nvec) v[u] = ld_stream(x + i * 8);                // nvec % 4 == 0: a group is live or dead as a whole
-    }
+    for (int j = 0; j < 4; ++j) v[j] = ld_plain(src + 8 * j);   // through L1: the warp's four loads share their sectors
+    unsigned am = absmax8(v[0]);
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long i = i0 + u * stride + threadIdx.x;
-      const bool live = i < nvec;
-      unsigned am = absmax8(v[u]);
-      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
-      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
-      const int e = ue8m0_exp_from_bf16(am);
-      unsigned q0, q1;
-      quant8(v[u], pow2_neg(e), q0, q1);
-      unsigned sfb = (unsigned)(e + 127);
-      sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
-      sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
-      if (live) {
-        st_stream8(q + i * 8, q0, q1);
-        if ((lane & 15) == 0) {
-          // four scale bytes; the tail of the tensor may hold fewer than four groups
-          const long long g = i >> 2, ng = nvec >> 2;
-          if (g + 4 <= ng && ((reinterpret_cast<uintptr_t>(sf) + g) & 3) == 0) {
-            *reinterpret_cast<unsigned*>(sf + g) = sfb;
-          } else {
-            for (int k = 0; k < 4 && g + k < ng; ++k) sf[g + k] = (uint8_t)(sfb >> (8 * k));
-          }
-        }
-      }
-    }
+    for (int j = 1; j < 4; ++j) am = max_bf16_bits(am, absmax8(v[j]));
+    const int e = ue8m0_exp_from_bf16(am);
+    const float sc = pow2_neg(e);
+    V8 o0, o1;
+    quant8(v[0], sc, o0.w[0], o0.w[1]);
+    quant8(v[1], sc, o0.w[2], o0.w[3]);
+    quant8(v[2], sc, o1.w[0], o1.w[1]);
+    quant8(v[3], sc, o1.w[2], o1.w[3]);
+    st_stream(q + g * 32, o0);
+    st_stream(q + g * 32 + 16, o1);
+    sf[g] = (uint8_t)(e + 127);
   }
 }
 
@@ -124,11 +106,11 @@ extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_apply_v2(con
 #ifndef K3G_CUBIN_ONLY
 K3G_API int k3g_moe_quant(const void* x, void* q, void* sf, int rows, int cols, int grid_hint, void* stream) {
   K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(q); K3G_REQUIRE_PTR(sf);
-  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE(((uintptr_t)q & 7) == 0, K3G_EALIGN);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE_ALIGNED(q);
   K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
-  const long long nvec = (long long)rows * cols / 8;
+  const long long nvec = (long long)rows * cols / 32;
   if (nvec == 0) return K3G_OK;
-  long long grid = (nvec + 1023) / 1024;     // four vectors per thread
+  long long grid = (nvec + 255) / 256;       // one group per thread
   if (grid_hint > 0 && grid_hint < grid) grid = grid_hint;
   K3G_REQUIRE(grid <= 0x7fffffffLL, K3G_ELIMIT);
   kern_k3_moe_quant<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (uint8_t*)q, (uint8_t*)sf, rows, cols);

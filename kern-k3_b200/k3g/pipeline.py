@@ -59,11 +59,29 @@ class TpGlue:
             self.kernel_events.append((e0, e1))
         call("k3g_rs_arrive", self.flags, self._b_flags.table, self.units, SLOT_PUSH_LANDED, self.world, self.timeout_us, self.status, s)
 
+    def capture(self):
+        """Capture step() into a CUDA graph (the reference replays its whole program as one graph per
+        rank); collective on every rank, because the warm-up step runs the flag protocol."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        keep, self.kernel_events = self.kernel_events, None
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step()
+        self.kernel_events = keep
+
+    def replay(self):
+        self.graph.replay()
+
     def step_host(self, host_partial, host_residual, host_residual_out, host_q_all, host_sf_all):
         """The same step with HOST (pinned) inputs and outputs: copies in, step, copies out."""
         self.partial.copy_(host_partial, non_blocking=True)
         self.residual.copy_(host_residual, non_blocking=True)
-        self.step()
+        self.replay() if getattr(self, "graph", None) is not None else self.step()
         host_residual_out.copy_(self.residual_out, non_blocking=True)
         host_q_all.copy_(self.q_all, non_blocking=True)
         host_sf_all.copy_(self.sf_all, non_blocking=True)

@@ -75,6 +75,21 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "samples": len(s), "reasons": sorted(self.reasons)}
 
 
+class quiet_stdout:
+    """Route the process's fd 1 to stderr while libraries that print banners initialise (NCCL prints its
+    version on stdout), so that the only thing on stdout is the JSON line."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def __exit__(self, *a):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def physical_gpu_index(local_rank):
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -217,7 +232,10 @@ def run_gpu(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda")
     if world > 1:
-        dist.init_process_group("nccl")
+        with quiet_stdout():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+            torch.cuda.synchronize()
     peak_gbs, peak_kind = measured_peaks()
     glue = TpGlue(rank, world, TOKENS, HIDDEN, EPS)
     g = torch.Generator(device=dev); g.manual_seed(0x5EED ^ rank)
@@ -273,6 +291,38 @@ def run_gpu(args, rank, world, local_rank):
     e2e_us = timed(lambda: glue.step_host(hp, hr, ho, hq, hs), e2e_steps, 3)
     glue.check_status()
 
+    coll = None
+    if world > 1:
+        # the collectives on their own, and NCCL on the same payloads as a comparison line
+        s = k3g.current_stream()
+        count = glue.rows * HIDDEN
+        dst = torch.empty(count, dtype=torch.bfloat16, device=dev)
+        pull_us = timed(lambda: k3g.call("k3g_rs_pull", glue.partial, dst, glue._b_partial.table, count, 2 * (world - 1), rank, world, glue.units, s), 20, 3)
+        q_sh = glue.q_all[rank * glue.rows:(rank + 1) * glue.rows].clone(); sf_sh = glue.sf_all[rank * glue.rows:(rank + 1) * glue.rows].clone()
+
+        # its own flag table: a slot must see exactly one call per epoch, and the step's table has moved on
+        b_f2 = glue.pg.symmetric("flags_ag", 64)
+        flags2 = b_f2.tensor(torch.int64, (8,))
+        k3g.call("k3g_flags_init", flags2, 8, s)
+        barrier()
+
+        def ag_push():
+            k3g.call("k3g_epoch_bump", flags2, glue.units, s)
+            k3g.call("k3g_allgather4_push", q_sh, glue.q_all, glue._b_q.table, q_sh.numel(), sf_sh, glue.sf_all, glue._b_sf.table, sf_sh.numel(),
+                     None, None, None, 0, None, None, None, 0, flags2, b_f2.table, 1, rank, world, glue.units, 200_000, glue.status, s)
+        push_us = timed(ag_push, 20, 3)
+        glue.check_status()
+        rs_out = torch.empty((glue.rows, HIDDEN), dtype=torch.bfloat16, device=dev)
+        with quiet_stdout():
+            nccl_rs_us = timed(lambda: dist.reduce_scatter_tensor(rs_out, glue.partial), 20, 3)
+            nccl_ag_us = timed(lambda: (dist.all_gather_into_tensor(glue.q_all, q_sh), dist.all_gather_into_tensor(glue.sf_all, sf_sh)), 20, 3)
+        Ew = TOKENS * HIDDEN
+        rs_in = (world - 1) * 2 * Ew // world; ag_out = (world - 1) * (Ew + Ew // 32) // world
+        coll = {"rs_pull_us": round(pull_us, 1), "rs_pull_in_gbs": round(rs_in / pull_us / 1e3, 1), "ag_push_us": round(push_us, 1),
+                "ag_push_out_gbs": round(ag_out / push_us / 1e3, 1), "nccl_reduce_scatter_us": round(nccl_rs_us, 1),
+                "nccl_all_gather_us": round(nccl_ag_us, 1), "rs_in_bytes": rs_in, "ag_out_bytes": ag_out,
+                "note": "per rank; NVLink nominal 900 GB/s per direction, measured peer copy 770 GB/s; NCCL is the comparison line only"}
+
     W, E = world, TOKENS * HIDDEN
     alg_hbm = (7 * E + E // 32) // W if W == 1 else (2 * E // W) * 3 + (W - 1) * 2 * E // W + E + E // 32   # per rank, incl. serving peers' pulls
     roof = {"bound": "hbm", "kernel": "rs_resnorm_mxfp8_ag_kernel", "achieved": round(alg_hbm / kern_us / 1e3, 1), "peak": peak_gbs, "unit": "GB/s",
@@ -280,14 +330,19 @@ def run_gpu(args, rank, world, local_rank):
             "algorithmic_bytes_per_launch": alg_hbm}
     nv = None
     if W > 1:
-        nin, nout = (W - 1) * 2 * E // W, (W - 1) * (E + E // 32) // W
-        nv = {"in_bytes": nin, "out_bytes": nout, "in_gbs": round(nin / kern_us / 1e3, 1), "out_gbs": round(nout / kern_us / 1e3, 1),
-              "frac_of_900": round(nin / kern_us / 1e3 / 900.0, 3), "frac_of_measured_770": round(nin / kern_us / 1e3 / 770.0, 3)}
+        # per rank and per direction the fused kernel moves: reduce-scatter responses (W-1)/W * 2E plus the
+        # peers' all-gather stores (W-1)/W * (E + E/32) -- both arrive on this GPU's NVLink ingress, and the
+        # same two amounts leave on its egress
+        rs_b, ag_b = (W - 1) * 2 * E // W, (W - 1) * (E + E // 32) // W
+        tot = rs_b + ag_b
+        nv = {"bytes_per_direction": tot, "rs_bytes": rs_b, "ag_bytes": ag_b, "gbs_per_direction": round(tot / kern_us / 1e3, 1),
+              "frac_of_900": round(tot / kern_us / 1e3 / 900.0, 3), "frac_of_measured_770": round(tot / kern_us / 1e3 / 770.0, 3),
+              "target_us_at_770": round(tot / 770e3, 1)}
     line = {"metric": METRIC, "value": round(step_us, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": round(step_us / 1e3, 5), "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "config1: TP reduce-scatter -> residual add + RMSNorm + MXFP8 -> all-gather, T=16384 d=7168, world=%d" % W,
                        "tokens": TOKENS, "d": HIDDEN, "world": W, "l2": "inputs (470 MB read per step at world 1) exceed the 126 MB L2; no flush"},
-            "clocks": clocks, "roofline": roof, "nvlink": nv, "launch_mode": "cuda graph replay of 4 kernels per step (epoch bump, arrive, fused kernel, arrive)",
+            "clocks": clocks, "roofline": roof, "nvlink": nv, "collectives": coll, "launch_mode": "cuda graph replay of 4 kernels per step (epoch bump, arrive, fused kernel, arrive)",
             "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps, "eager_step_us": round(eager_us, 2), "tokens_per_s": round(TOKENS / step_us * 1e6)}
     if rank == 0 and world == 1:

@@ -242,43 +242,50 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
     qdst[r] = (r == rank ? q_all : reinterpret_cast<uint8_t*>(q_all_peer[r])) + (size_t)rank * rows * H;
     sfdst[r] = (r == rank ? sf_all : reinterpret_cast<uint8_t*>(sf_all_peer[r])) + (size_t)rank * rows * (H / 32);
   }
-  // loads of a chunk of vectors are all issued before the first dependent instruction: the chunk is
-  // sized so that (NR partials + 1 residual) x chunk stays near 14 vectors in flight per thread
-  constexpr int CH = NR == 1 ? VPT : NR == 2 ? 4 : NR == 4 ? 2 : 1;
+  // Phase A pulls the W partial rows chunk by chunk -- every load of a chunk is issued before the
+  // first dependent instruction, W x CH 16-byte loads in flight per thread (the NVLink round trip is
+  // what has to be covered) -- and lands the ring-order chain; phase B adds the residual.
+  constexpr int CH = NR == 1 ? VPT : NR == 2 ? VPT : NR == 4 ? 4 : 2;
   int it = 0;
   for (int b = blockIdx.x; b < rows; b += gridDim.x, ++it) {
     const size_t rowoff = (size_t)b * H;
     V8 x[VPT];
 #pragma unroll
     for (int v0 = 0; v0 < VPT; v0 += CH) {
-      V8 p[CH][NR], r[CH];
+      V8 p[CH][NR];
 #pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        if (v0 + c < VPT) {
-          const long long vi = (long long)((rowoff + (t + (v0 + c) * kTeam) * 8) >> 3);
+      for (int k = 0; k < NR; ++k) {
 #pragma unroll
-          for (int k = 0; k < NR; ++k) p[c][k] = NR == 1 ? ld_stream(base[k] + vi) : ld_plain(base[k] + vi);
+        for (int c = 0; c < CH; ++c) {
+          if (v0 + c < VPT) {
+            const long long vi = (long long)((rowoff + (t + (v0 + c) * kTeam) * 8) >> 3);
+            p[c][k] = NR == 1 ? ld_stream(base[k] + vi) : ld_plain(base[k] + vi);
+          }
         }
       }
 #pragma unroll
-      for (int c = 0; c < CH; ++c)
-        if (v0 + c < VPT) r[c] = ld_stream(residual + rowoff + (t + (v0 + c) * kTeam) * 8);
-#pragma unroll
       for (int c = 0; c < CH; ++c) {
         if (v0 + c < VPT) {
-          V8 d = p[c][0];
+          x[v0 + c] = p[c][0];
 #pragma unroll
           for (int k = 1; k < NR; ++k) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) d.w[j] = add_bf2(d.w[j], p[c][k].w[j]);
+            for (int j = 0; j < 4; ++j) x[v0 + c].w[j] = add_bf2(x[v0 + c].w[j], p[c][k].w[j]);
           }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) x[v0 + c].w[j] = add_bf2(r[c].w[j], d.w[j]);
         }
       }
+    }
+    {
+      V8 r[VPT];
 #pragma unroll
-      for (int c = 0; c < CH; ++c)
-        if (v0 + c < VPT) st_stream(residual_out + rowoff + (t + (v0 + c) * kTeam) * 8, x[v0 + c]);
+      for (int v = 0; v < VPT; ++v) r[v] = ld_stream(residual + rowoff + (t + v * kTeam) * 8);
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(r[v].w[j], x[v].w[j]);
+      }
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) st_stream(residual_out + rowoff + (t + v * kTeam) * 8, x[v]);
     }
     // sum of squares in the fixed order, then the normed row + quant epilogue
     float sq = 0.f;

@@ -124,18 +124,50 @@ __device__ __forceinline__ void rope8(const V8& x1, const V8& x2, const V8& cs, 
   }
 }
 
-// Config-level prep: one warp per token.  kv [T,576], q [T,heads,192], rope_tab [T,64] = cos|sin.
+// Config-level prep.  kv [T,576], q [T,heads,192], rope_tab [T,64] = cos|sin.  Flat thread mapping:
+// item = (token, head, c) with c = 0..3 one 8-pair chunk of the rope slice; the thread rotates that
+// chunk of q, writes the rotated k_rope chunk into the head's k slots and copies four of the head's
+// sixteen nope vectors -- six independent 16-byte loads in flight, no shared memory.  The latent
+// RMSNorm needs a whole warp per token: global warp w also normalises token w (there are at least as
+// many warps as tokens when heads >= 8; otherwise warps stride over tokens).
 __global__ void __launch_bounds__(128) mla_rope_pack_kernel(const __nv_bfloat16* __restrict__ kv, const __nv_bfloat16* __restrict__ q,
                                                             const __nv_bfloat16* __restrict__ gamma_kv, const __nv_bfloat16* __restrict__ rope_tab,
                                                             __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
                                                             __nv_bfloat16* __restrict__ latent_out, int T, int heads, float eps) {
-  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
-  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
+  const int lane = threadIdx.x & 31;
+  const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long items = (long long)T * heads * 4;
+  for (long long it = gtid; it < items; it += nthreads) {
+    const int c = (int)(it & 3);
+    const long long th = it >> 2;                      // token * heads + head
+    const int t = (int)(th / heads);
+    const size_t o = (size_t)th * 192;
+    const __nv_bfloat16* kvr = kv + (size_t)t * kKVA + kKV;
+    const __nv_bfloat16* tab = rope_tab + (size_t)t * 64;
+    const V8 a1 = ld_stream(q + o + 128 + 8 * c), a2 = ld_stream(q + o + 160 + 8 * c);
+    V8 n4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) n4[j] = ld_stream(q + o + 8 * (4 * j + c));
+    const V8 cs = ld_keep(tab + 8 * c), sn = ld_keep(tab + 32 + 8 * c);
+    const V8 b1 = ld_keep(kvr + 8 * c), b2 = ld_keep(kvr + 32 + 8 * c);
+    V8 o1, o2, k1, k2;
+    rope8(a1, a2, cs, sn, o1, o2);
+    rope8(b1, b2, cs, sn, k1, k2);
+    st_stream(q_out + o + 128 + 8 * c, o1);
+    st_stream(q_out + o + 160 + 8 * c, o2);
+    st_stream(k_out + o + 128 + 8 * c, k1);
+    st_stream(k_out + o + 160 + 8 * c, k2);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) st_stream(q_out + o + 8 * (4 * j + c), n4[j]);
+  }
+  // latent RMSNorm (kv groups' reduction order), one warp per token
+  const long long nwarps = nthreads >> 5;
+  for (long long t = gtid >> 5; t < T; t += nwarps) {
     const __nv_bfloat16* kvr = kv + (size_t)t * kKVA;
-    // latent RMSNorm (kv groups' reduction order)
     uint2 uk[kKG];
 #pragma unroll
-    for (int g = 0; g < kKG; ++g) uk[g] = __ldcs(reinterpret_cast<const uint2*>(kvr) + 32 * g + lane);
+    for (int g = 0; g < kKG; ++g) uk[g] = __ldg(reinterpret_cast<const uint2*>(kvr) + 32 * g + lane);
     float tk = 0.f;
 #pragma unroll
     for (int g = 0; g < kKG; ++g) tk = __fadd_rn(tk, butterfly_sum<32>(unit_sumsq(uk[g])));
@@ -144,51 +176,6 @@ __global__ void __launch_bounds__(128) mla_rope_pack_kernel(const __nv_bfloat16*
     for (int g = 0; g < kKG; ++g) {
       const int u = 32 * g + lane;
       __stcs(reinterpret_cast<uint2*>(latent_out + (size_t)t * kKV) + u, unit_norm(uk[g], sck, __ldg(reinterpret_cast<const uint2*>(gamma_kv) + u)));
-    }
-    // rope: lane = (head slot, c) with c = lane & 3 the 8-pair chunk; 8 heads per pass
-    const int c = lane & 3;
-    const V8 cs = ld_plain(rope_tab + (size_t)t * 64 + 8 * c), sn = ld_plain(rope_tab + (size_t)t * 64 + 32 + 8 * c);
-    V8 k1, k2;
-    rope8(ld_plain(kvr + kKV + 8 * c), ld_plain(kvr + kKV + 32 + 8 * c), cs, sn, k1, k2);
-    // all loads of a batch are issued before its first store (a store orders later loads behind it)
-    for (int h0 = 0; h0 < heads; h0 += 16) {                  // two rope passes (8 heads each) per batch
-      V8 a1[2], a2[2];
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        const int h = h0 + 8 * p + (lane >> 2);
-        if (h < heads) {
-          const size_t o = ((size_t)t * heads + h) * 192 + 128;
-          a1[p] = ld_stream(q + o + 8 * c);
-          a2[p] = ld_stream(q + o + 32 + 8 * c);
-        }
-      }
-#pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        const int h = h0 + 8 * p + (lane >> 2);
-        if (h < heads) {
-          const size_t o = ((size_t)t * heads + h) * 192 + 128;
-          V8 o1, o2;
-          rope8(a1[p], a2[p], cs, sn, o1, o2);
-          st_stream(q_out + o + 8 * c, o1);
-          st_stream(q_out + o + 32 + 8 * c, o2);
-          st_stream(k_out + o + 8 * c, k1);
-          st_stream(k_out + o + 32 + 8 * c, k2);
-        }
-      }
-    }
-    // nope copy: 16 vectors per head, two heads per pass, eight passes per batch
-    for (int h0 = 0; h0 < heads; h0 += 16) {
-      V8 n8[8];
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        const int h = h0 + 2 * p + (lane >> 4);
-        if (h < heads) n8[p] = ld_stream(q + ((size_t)t * heads + h) * 192 + 8 * (lane & 15));
-      }
-#pragma unroll
-      for (int p = 0; p < 8; ++p) {
-        const int h = h0 + 2 * p + (lane >> 4);
-        if (h < heads) st_stream(q_out + ((size_t)t * heads + h) * 192 + 8 * (lane & 15), n8[p]);
-      }
     }
   }
 }
@@ -270,7 +257,11 @@ K3G_API int k3g_mla_prep_rope_pack(const void* kv, const void* q, const void* ga
   K3G_REQUIRE_ALIGNED(latent_out); K3G_REQUIRE_ALIGNED(gamma_kv);
   K3G_REQUIRE(T >= 0 && heads > 0 && heads <= 128, K3G_ESHAPE);
   if (T == 0) return K3G_OK;
-  mla_rope_pack_kernel<<<(T + 3) / 4, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)kv, (const __nv_bfloat16*)q,
+  const long long items = (long long)T * heads * 4;
+  long long grid = (items + 127) / 128;
+  if (grid < (T + 3) / 4) grid = (T + 3) / 4;      // at least one warp per token for the latent norm
+  K3G_REQUIRE(grid <= 0x7fffffffLL, K3G_ELIMIT);
+  mla_rope_pack_kernel<<<(unsigned)grid, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)kv, (const __nv_bfloat16*)q,
                                                                    (const __nv_bfloat16*)gamma_kv, (const __nv_bfloat16*)rope_tab,
                                                                    (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)latent_out,
                                                                    T, heads, eps);

@@ -140,10 +140,12 @@ int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long long n0, 
 /* Fused reduce-scatter -> residual add -> RMSNorm -> MXFP8 -> all-gather (benchmark configuration 1):
  * kern_k3_rs_pull + kern_k3_land_add_attnres_rms (nb = 0) + kern_k3_moe_quant + the all-gather push of
  * kern_k3_attnres_rms_push (source/k3_residual_push_add2.cu:356-360) in one kernel.  Bracket it with
- * k3g_rs_arrive before (partials ready) and after (pushes landed). */
+ * k3g_rs_arrive before (partials ready) and after (pushes landed).  Processes rows
+ * [row_begin, row_begin + rows) of a shard of shard_rows rows (shard_rows <= 0: shard = rows). */
 int k3g_rs_resnorm_mxfp8_ag(const void* partial, const void* partial_peer, const void* residual, const void* gamma,
                             void* residual_out, void* q_all, const void* q_all_peer, void* sf_all, const void* sf_all_peer,
-                            int rows, int H, float eps, int rank, int nranks, int grid_hint, void* stream);
+                            int rows, int H, float eps, int rank, int nranks, int grid_hint, int row_begin, int shard_rows,
+                            void* stream);
 
 /* Status of the last expired wait of a launch that had no status pointer (host_status: 4 x u32). */
 int k3g_wait_status(void* host_status, int clear, void* stream);

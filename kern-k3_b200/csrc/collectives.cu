@@ -229,25 +229,25 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
     const __nv_bfloat16* __restrict__ partial, const unsigned long long* __restrict__ partial_peer,
     const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ residual_out,
     uint8_t* __restrict__ q_all, const unsigned long long* __restrict__ q_all_peer, uint8_t* __restrict__ sf_all,
-    const unsigned long long* __restrict__ sf_all_peer, int rows, int rank, float eps) {
+    const unsigned long long* __restrict__ sf_all_peer, int rows, int rank, float eps, int row_begin, int shard_rows) {
   constexpr int H = VPT * 1024;
   __shared__ float s_red[2][kTeam / 32];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const uint4* base[NR];
-  rs_bases<NR, NR - 1, 0>(partial, partial_peer, (long long)rank * rows * H, rank, base);
+  rs_bases<NR, NR - 1, 0>(partial, partial_peer, (long long)rank * shard_rows * H, rank, base);
   uint8_t* qdst[NR];
   uint8_t* sfdst[NR];
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
-    qdst[r] = (r == rank ? q_all : reinterpret_cast<uint8_t*>(q_all_peer[r])) + (size_t)rank * rows * H;
-    sfdst[r] = (r == rank ? sf_all : reinterpret_cast<uint8_t*>(sf_all_peer[r])) + (size_t)rank * rows * (H / 32);
+    qdst[r] = (r == rank ? q_all : reinterpret_cast<uint8_t*>(q_all_peer[r])) + (size_t)rank * shard_rows * H;
+    sfdst[r] = (r == rank ? sf_all : reinterpret_cast<uint8_t*>(sf_all_peer[r])) + (size_t)rank * shard_rows * (H / 32);
   }
   // Phase A pulls the W partial rows chunk by chunk -- every load of a chunk is issued before the
   // first dependent instruction, W x CH 16-byte loads in flight per thread (the NVLink round trip is
   // what has to be covered) -- and lands the ring-order chain; phase B adds the residual.
   constexpr int CH = NR == 1 ? VPT : NR == 2 ? VPT : NR == 4 ? 4 : 2;
   int it = 0;
-  for (int b = blockIdx.x; b < rows; b += gridDim.x, ++it) {
+  for (int b = row_begin + blockIdx.x; b < row_begin + rows; b += gridDim.x, ++it) {
     const size_t rowoff = (size_t)b * H;
     V8 x[VPT];
 #pragma unroll
@@ -474,11 +474,11 @@ template <int NR>
 static int launch_fused(int H, int grid, cudaStream_t st, const __nv_bfloat16* partial, const unsigned long long* partial_peer,
                         const __nv_bfloat16* residual, const __nv_bfloat16* gamma, __nv_bfloat16* residual_out, uint8_t* q_all,
                         const unsigned long long* q_all_peer, uint8_t* sf_all, const unsigned long long* sf_all_peer, int rows, int rank,
-                        float eps) {
+                        float eps, int row_begin, int shard_rows) {
   switch (H / 1024) {
-    case 1: rs_resnorm_mxfp8_ag_kernel<1, NR><<<grid, kTeam, 0, st>>>(partial, partial_peer, residual, gamma, residual_out, q_all, q_all_peer, sf_all, sf_all_peer, rows, rank, eps); break;
-    case 2: rs_resnorm_mxfp8_ag_kernel<2, NR><<<grid, kTeam, 0, st>>>(partial, partial_peer, residual, gamma, residual_out, q_all, q_all_peer, sf_all, sf_all_peer, rows, rank, eps); break;
-    case 7: rs_resnorm_mxfp8_ag_kernel<7, NR><<<grid, kTeam, 0, st>>>(partial, partial_peer, residual, gamma, residual_out, q_all, q_all_peer, sf_all, sf_all_peer, rows, rank, eps); break;
+    case 1: rs_resnorm_mxfp8_ag_kernel<1, NR><<<grid, kTeam, 0, st>>>(partial, partial_peer, residual, gamma, residual_out, q_all, q_all_peer, sf_all, sf_all_peer, rows, rank, eps, row_begin, shard_rows); break;
+    case 2: rs_resnorm_mxfp8_ag_kernel<2, NR><<<grid, kTeam, 0, st>>>(partial, partial_peer, residual, gamma, residual_out, q_all, q_all_peer, sf_all, sf_all_peer, rows, rank, eps, row_begin, shard_rows); break;
+    case 7: rs_resnorm_mxfp8_ag_kernel<7, NR><<<grid, kTeam, 0, st>>>(partial, partial_peer, residual, gamma, residual_out, q_all, q_all_peer, sf_all, sf_all_peer, rows, rank, eps, row_begin, shard_rows); break;
     default: return K3G_ESHAPE;
   }
   return k3g_launch_status();
@@ -489,21 +489,27 @@ static int launch_fused(int H, int grid, cudaStream_t st, const __nv_bfloat16* p
 // residual / residual_out: this rank's [rows, H] shard.  q_all [nranks * rows, H] u8 and
 // sf_all [nranks * rows, H / 32] u8 are every rank's gathered outputs (q_all_peer / sf_all_peer
 // the peer tables).  Bracket with k3g_rs_arrive before (partials ready) and after (pushes landed).
+// The call processes rows [row_begin, row_begin + rows) of the rank's shard of shard_rows rows
+// (shard_rows <= 0: the shard has exactly `rows` rows and row_begin must be 0), so a host can
+// pipeline a shard in row chunks; residual / residual_out are indexed by shard row.
 K3G_API int k3g_rs_resnorm_mxfp8_ag(const void* partial, const void* partial_peer, const void* residual, const void* gamma,
                                     void* residual_out, void* q_all, const void* q_all_peer, void* sf_all, const void* sf_all_peer,
-                                    int rows, int H, float eps, int rank, int nranks, int grid_hint, void* stream) {
+                                    int rows, int H, float eps, int rank, int nranks, int grid_hint, int row_begin, int shard_rows,
+                                    void* stream) {
   K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(partial_peer); K3G_REQUIRE_PTR(residual); K3G_REQUIRE_PTR(gamma);
   K3G_REQUIRE_PTR(residual_out); K3G_REQUIRE_PTR(q_all); K3G_REQUIRE_PTR(q_all_peer); K3G_REQUIRE_PTR(sf_all); K3G_REQUIRE_PTR(sf_all_peer);
   K3G_REQUIRE_ALIGNED(partial); K3G_REQUIRE_ALIGNED(residual); K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(residual_out);
   K3G_REQUIRE_ALIGNED(q_all); K3G_REQUIRE_ALIGNED(sf_all);
   if (int rc = check_world(rank, nranks)) return rc;
   K3G_REQUIRE(rows >= 0 && (H == 1024 || H == 2048 || H == 7168), K3G_ESHAPE);
+  if (shard_rows <= 0) shard_rows = rows;                       // whole shard in one call
+  K3G_REQUIRE(row_begin >= 0 && row_begin + rows <= shard_rows, K3G_ERANGE);
   if (rows == 0) return K3G_OK;
   const int grid = grid_hint > 0 && grid_hint < rows ? grid_hint : rows;
   cudaStream_t st = k3g_stream(stream);
 #define K3G_FUSED_ARGS H, grid, st, (const __nv_bfloat16*)partial, (const unsigned long long*)partial_peer, (const __nv_bfloat16*)residual, \
     (const __nv_bfloat16*)gamma, (__nv_bfloat16*)residual_out, (uint8_t*)q_all, (const unsigned long long*)q_all_peer, (uint8_t*)sf_all, \
-    (const unsigned long long*)sf_all_peer, rows, rank, eps
+    (const unsigned long long*)sf_all_peer, rows, rank, eps, row_begin, shard_rows
   switch (nranks) {
     case 1: return launch_fused<1>(K3G_FUSED_ARGS);
     case 2: return launch_fused<2>(K3G_FUSED_ARGS);

@@ -44,16 +44,18 @@ class TpGlue:
         torch.cuda.synchronize()
         self.kernel_events = None      # set to a list to collect (start, end) events around the fused kernel
 
-    def step(self, grid_hint=0):
-        """One glue step on device-resident inputs (self.partial, self.residual, self.gamma)."""
+    def step(self, grid_hint=0, row_begin=0, rows=None):
+        """One glue step on device-resident inputs (self.partial, self.residual, self.gamma); with
+        row_begin / rows, one protocol round over that row chunk of every rank's shard."""
         s = current_stream()
+        rows = self.rows if rows is None else rows
         call("k3g_epoch_bump", self.flags, self.units, s)
         call("k3g_rs_arrive", self.flags, self._b_flags.table, self.units, SLOT_PARTIALS_READY, self.world, self.timeout_us, self.status, s)
         if self.kernel_events is not None:
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
             e0.record()
         call("k3g_rs_resnorm_mxfp8_ag", self.partial, self._b_partial.table, self.residual, self.gamma, self.residual_out, self.q_all,
-             self._b_q.table, self.sf_all, self._b_sf.table, self.rows, self.H, self.eps, self.rank, self.world, grid_hint, s)
+             self._b_q.table, self.sf_all, self._b_sf.table, rows, self.H, self.eps, self.rank, self.world, grid_hint, row_begin, self.rows, s)
         if self.kernel_events is not None:
             e1.record()
             self.kernel_events.append((e0, e1))
@@ -85,6 +87,39 @@ class TpGlue:
         host_residual_out.copy_(self.residual_out, non_blocking=True)
         host_q_all.copy_(self.q_all, non_blocking=True)
         host_sf_all.copy_(self.sf_all, non_blocking=True)
+
+    def step_host_pipelined(self, host_partial, host_residual, host_residual_out, host_q_all, host_sf_all, chunks=8):
+        """step_host with the shard cut into row chunks and three streams: while chunk c is reduced,
+        normalised and gathered, chunk c + 1 is on its way in and chunk c - 1 on its way out, so the
+        host link is busy in both directions at once.  Each chunk is a full protocol round (epoch bump,
+        arrive, fused kernel over rows [r0, r1) of every shard, arrive)."""
+        if not hasattr(self, "_s_in"):
+            self._s_in, self._s_cmp, self._s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        cur = torch.cuda.current_stream()
+        start = torch.cuda.Event(); start.record(cur)
+        for st in (self._s_in, self._s_cmp, self._s_out):
+            st.wait_event(start)
+        R, W = self.rows, self.world
+        step_rows = (R + chunks - 1) // chunks
+        for r0 in range(0, R, step_rows):
+            r1 = min(R, r0 + step_rows)
+            with torch.cuda.stream(self._s_in):
+                for q in range(W):
+                    self.partial[q * R + r0:q * R + r1].copy_(host_partial[q * R + r0:q * R + r1], non_blocking=True)
+                self.residual[r0:r1].copy_(host_residual[r0:r1], non_blocking=True)
+                ev_in = torch.cuda.Event(); ev_in.record(self._s_in)
+            with torch.cuda.stream(self._s_cmp):
+                self._s_cmp.wait_event(ev_in)
+                self.step(row_begin=r0, rows=r1 - r0)
+                ev_done = torch.cuda.Event(); ev_done.record(self._s_cmp)
+            with torch.cuda.stream(self._s_out):
+                self._s_out.wait_event(ev_done)
+                host_residual_out[r0:r1].copy_(self.residual_out[r0:r1], non_blocking=True)
+                for q in range(W):
+                    host_q_all[q * R + r0:q * R + r1].copy_(self.q_all[q * R + r0:q * R + r1], non_blocking=True)
+                    host_sf_all[q * R + r0:q * R + r1].copy_(self.sf_all[q * R + r0:q * R + r1], non_blocking=True)
+        end = torch.cuda.Event(); end.record(self._s_out)
+        cur.wait_event(end)
 
     def h2d_bytes(self):
         return self.tokens * self.H * 2 + self.rows * self.H * 2

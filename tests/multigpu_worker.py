@@ -64,7 +64,7 @@ def main():
         k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 2, world, 5_000_000, status, s)
         res_out = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
         k3g.call("k3g_rs_resnorm_mxfp8_ag", part, b_part.table, to_dev_bf16(residual[rank], dev), to_dev_bf16(gamma, dev), res_out, q_all,
-                 b_q.table, sf_all, b_sf.table, rows, H, 1e-6, rank, world, 0, s)
+                 b_q.table, sf_all, b_sf.table, rows, H, 1e-6, rank, world, 0, 0, 0, s)
         k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 3, world, 5_000_000, status, s)
         torch.cuda.synchronize()
         assert not status.cpu().numpy().any(), status

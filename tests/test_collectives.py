@@ -153,12 +153,40 @@ def test_fused_rs_resnorm_ag_emulated(k3g, dev, W, H, rows):
     for r in range(W):
         res_out = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
         k3g.call("k3g_rs_resnorm_mxfp8_ag", d_part[r], ptab, to_dev_bf16(residual[r], dev), d_gamma, res_out, q_all[r], qtab, sf_all[r],
-                 sftab, rows, H, 1e-6, r, W, 0, k3g.current_stream())
+                 sftab, rows, H, 1e-6, r, W, 0, 0, 0, k3g.current_stream())
         torch.cuda.synchronize()
         assert np.array_equal(bf16_bits(res_out), want_res[r])
     for r in range(W):
         assert np.array_equal(sf_all[r].cpu().numpy(), want_sf)
         assert np.array_equal(q_all[r].cpu().numpy(), want_q)
+
+
+def test_fused_kernel_in_row_chunks_equals_one_call(k3g, dev):
+    """A shard processed as three row chunks (row_begin / rows / shard_rows) gives the same bytes as
+    one call -- what the host-side copy/compute pipeline relies on."""
+    import torch
+    g = rng(31)
+    W, H, rows = 2, 7168, 21
+    T = W * rows
+    partials = [to_dev_bf16(normal_bf16(g, (T * H,), std=0.25), dev) for _ in range(W)]
+    ptab = _table(partials, dev)
+    residual = to_dev_bf16(normal_bf16(g, (rows, H)), dev); gamma = to_dev_bf16(normal_bf16(g, (H,), mean=1.0, std=0.02), dev)
+    outs = []
+    for chunks in ([(0, rows)], [(0, 8), (8, 8), (16, 5)]):
+        q_all = [torch.zeros((T, H), dtype=torch.uint8, device=dev) for _ in range(W)]
+        sf_all = [torch.zeros((T, H // 32), dtype=torch.uint8, device=dev) for _ in range(W)]
+        qtab, sftab = _table(q_all, dev), _table(sf_all, dev)
+        res_out = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for r0, n in chunks:
+            k3g.call("k3g_rs_resnorm_mxfp8_ag", partials[1], ptab, residual, gamma, res_out, q_all[1], qtab, sf_all[1], sftab, n, H, 1e-6, 1, W, 0,
+                     r0, rows, k3g.current_stream())
+        torch.cuda.synchronize()
+        outs.append((res_out, q_all[0], q_all[1], sf_all[0], sf_all[1]))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert int(outs[0][1][rows:].max()) > 0 and int(outs[0][1][:rows].max()) == 0     # rank 1's rows landed in its slice only
+    s = k3g.current_stream()
+    assert k3g.raw("k3g_rs_resnorm_mxfp8_ag", partials[1], ptab, residual, gamma, res_out, q_all[1], qtab, sf_all[1], sftab, 8, H, 1e-6, 1, W, 0, 16, rows, s) == -4
 
 
 def test_collective_argument_errors(k3g, dev):
@@ -169,4 +197,33 @@ def test_collective_argument_errors(k3g, dev):
     assert k3g.raw("k3g_rs_pull", x, x, tab, 16, 0, 2, 2, 1, s) == -4          # rank out of range
     assert k3g.raw("k3g_rs_pull", x, x, None, 16, 0, 0, 1, 1, s) == -1
     assert k3g.raw("k3g_rs_arrive", f, tab, 4, 0, 1, 1000, None, s) == -4      # slot 0 is the epoch
-    assert k3g.raw("k3g_rs_resnorm_mxfp8_ag", x, tab, x, x, x, x, tab, x, tab, 1, 7168, 1e-6, 0, 3, 0, s) == -2
+    assert k3g.raw("k3g_rs_resnorm_mxfp8_ag", x, tab, x, x, x, x, tab, x, tab, 1, 7168, 1e-6, 0, 3, 0, 0, 0, s) == -2
+
+
+def test_glue_step_host_paths_agree(k3g, dev):
+    """World-1 glue step three ways -- device-resident step, CUDA-graph replay through pinned host
+    buffers, and the row-chunked three-stream pipeline -- all bit-identical to the CPU oracle."""
+    import torch
+    from k3g.pipeline import TpGlue
+    T, H = 96, 7168
+    g = rng(91)
+    partial, residual = normal_bf16(g, (T, H), std=0.5), normal_bf16(g, (T, H))
+    gamma = normal_bf16(g, (H,), mean=1.0, std=0.02)
+    want_res, want_q, want_sf, _ = k3o.resnorm_mxfp8(residual, partial, gamma, 1e-6, want_normed=False)
+    glue = TpGlue(0, 1, T, H, 1e-6)
+    glue.gamma.copy_(to_dev_bf16(gamma, dev))
+    hp = to_dev_bf16(partial, "cpu").pin_memory(); hr = to_dev_bf16(residual, "cpu").pin_memory()
+    for mode in ("serial", "graph", "pipelined"):
+        ho = torch.zeros((T, H), dtype=torch.bfloat16).pin_memory()
+        hq = torch.zeros((T, H), dtype=torch.uint8).pin_memory(); hs = torch.zeros((T, H // 32), dtype=torch.uint8).pin_memory()
+        if mode == "graph":
+            glue.capture()
+        if mode == "pipelined":
+            glue.step_host_pipelined(hp, hr, ho, hq, hs, chunks=5)
+        else:
+            glue.step_host(hp, hr, ho, hq, hs)
+        torch.cuda.synchronize()
+        glue.check_status()
+        assert np.array_equal(bf16_bits(ho), want_res), mode
+        assert np.array_equal(hq.numpy(), want_q) and np.array_equal(hs.numpy(), want_sf), mode
+    glue.close()

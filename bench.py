@@ -205,6 +205,9 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     fc2 = torch.randn((rows, H), generator=g, device=dev, dtype=torch.bfloat16)
     add("config2 finalize_residual 16384x8x7168", lambda: k3g.call("k3g_finalize_residual", fc2, e2p, wts, res, o16, T, H, 8, s), T * 8 * H * 2 + 4 * E)
     del fc2
+    big = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
+    add("context: write-only fill of 1 GiB (torch zero_)", lambda: big.zero_(), big.numel())
+    del big
     # config 3
     kv = rnd(T, 576); qq = rnd(T, 16, 192); gkv = gm[:512].contiguous(); tab = rnd(T, 64)
     qo = torch.empty_like(qq); ko = torch.empty_like(qq); lat = torch.empty((T, 512), dtype=torch.bfloat16, device=dev)

@@ -50,6 +50,22 @@ int k3g_land_add_attnres_rms(const void* partial, int partial_is_bf16, const voi
                              const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
                              int B, int H, float eps, void* stream);
 
+/* kern_k3_land_add_attnres_rms_nb1..8, source/k3_residual_nb_stats.cu:366-842 (ops
+ * land_add_attnres_rms_bf16_v2_nb{1..8}): the same kernel with the statistics hand-off -- stats [B, 8, 2]
+ * f32 = (sum x^2, sum x * sw) of the snapshot candidates c < nb_stats, written by k3g_attnres_rms_push. */
+int k3g_land_add_attnres_rms_stats(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+                                   const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
+                                   int B, int H, float eps, const void* stats, int nb_stats, void* stream);
+
+/* kern_k3_attnres_rms_push, source/k3_residual_push_add2.cu:369 (op attnres_rms_push_add2): landing add
+ * (hidden = bf16(prefix2 + p1 (+ p2))), optional snapshot, attention-residual mix, RMSNorm, and the normed
+ * row pushed into this rank's slice of every rank's normed_all [nranks * B, H] (dst_peer = peer table of
+ * normed_all).  stats (may be null) receives (sum x^2, sum x * sw_mlp) per snapshot candidate.  The
+ * all-gather's barrier is a separate k3g_rs_arrive. */
+int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
+                         int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
+                         const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream);
+
 /* kern_k3_land_add2, source/k3_residual_v2.cu:349 (op land_add2_v2; bf16 partials as in
  * source/k3_land_bf16.cu:96). */
 int k3g_land_add2(const void* p1, const void* p2, int partial_is_bf16, const void* prefix2, void* hidden, int two,

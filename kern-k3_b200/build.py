@@ -30,6 +30,9 @@ SOURCES = ["resnorm.cu", "quant.cu", "router.cu", "moe_route.cu", "collectives.c
 CUBINS = {
     "k3_residual_v2": ("resnorm.cu", []),
     "k3_residual_v2+LAND_BF16=1": ("resnorm.cu", ["-DLAND_BF16=1"]),
+    "k3_residual_nb+LAND_BF16=1": ("resnorm.cu", ["-DLAND_BF16=1"]),
+    "k3_residual_nb_stats": ("resnorm.cu", ["-DLAND_BF16=1"]),
+    "k3_residual_push_add2": ("resnorm.cu", ["-DLAND_BF16=1"]),
     "k3_quant_fp8_pair_v2": ("quant.cu", []),
     "k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16":
         ("moe_route.cu", ["-DEP_RANKS=4", "-DEP_STRIDED=1", "-DTILE_SHIFT=7"]),

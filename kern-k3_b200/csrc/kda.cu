@@ -26,58 +26,49 @@ namespace {
 
 // A thread owns kVec = 4 consecutive columns (8 bytes): small register footprint (the three sliding
 // taps, one chunk of rows and 16 tap weights), so eight 128-thread blocks stay resident per SM.
-#ifndef K3G_SPAN_CHUNK
-#define K3G_SPAN_CHUNK 4
-#endif
 #ifndef K3G_SPAN_MINB
 #define K3G_SPAN_MINB 8
 #endif
-#ifndef K3G_SPAN_PACKED
-#define K3G_SPAN_PACKED 0   /* packed f32x2 conv math measured no faster than scalar on B200 */
-#endif
 constexpr int kVec = 4;
-constexpr int kChunk = K3G_SPAN_CHUNK;
+constexpr int kChunk = 4;
 
 __device__ __forceinline__ uint2 ld8_stream(const void* p) {
   uint2 v;
   asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
   return v;
 }
-// taps of this thread's 4 columns as two f32 pairs per tap
+__device__ __forceinline__ void unpack4(uint2 v, float* x) {
+  x[0] = bf_lo(v.x); x[1] = bf_hi(v.x); x[2] = bf_lo(v.y); x[3] = bf_hi(v.y);
+}
+
 template <bool TAPS_BF16>
-__device__ __forceinline__ void load_taps(const void* cw, size_t off, f32x2* w) {
+__device__ __forceinline__ void load_taps(const void* cw, size_t off, float* w) {
   if (TAPS_BF16) {
-    const uint2 v = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(cw) + off));
-    w[0] = f2_from_bf2(v.x); w[1] = f2_from_bf2(v.y);
+    unpack4(__ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(cw) + off)), w);
   } else {
     const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(cw) + off));
-    w[0] = f2_pack(a.x, a.y); w[1] = f2_pack(a.z, a.w);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
   }
 }
 
-// One output row of 4 columns.  Rows are held as two f32 pairs; every arithmetic step is the packed
-// form of the scalar recipe (same roundings): y = fma(x, w3, fma(t2, w2, fma(t0, w0, t1 * w1))).
-__device__ __forceinline__ uint2 conv_silu_row(const f32x2* t0, const f32x2* t1, const f32x2* t2, const f32x2* x, const f32x2 (*w)[2]) {
+// One output row of 4 columns: y = fma(x, w3, fma(t2, w2, fma(t0, w0, t1 * w1))), sb = bf16(y),
+// out = bf16(sb * sigmoid(sb)).
+__device__ __forceinline__ uint2 conv_silu_row(const float* t0, const float* t1, const float* t2, const float* x, const float (*w)[kVec]) {
   unsigned o[2];
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-#if K3G_SPAN_PACKED
-    f32x2 a = f2_mul(t1[j], w[1][j]);
-    a = f2_fma(t0[j], w[0][j], a);
-    a = f2_fma(t2[j], w[2][j], a);
-    a = f2_fma(x[j], w[3][j], a);
-    const f32x2 sb = f2_from_bf2(f2_to_bf2(a));
-    o[j] = f2_to_bf2(f2_mul(sb, f2_fast_sigmoid(sb)));
-#else
-    float t0a, t0b, t1a, t1b, t2a, t2b, xa, xb, w0a, w0b, w1a, w1b, w2a, w2b, w3a, w3b;
-    f2_unpack(t0[j], t0a, t0b); f2_unpack(t1[j], t1a, t1b); f2_unpack(t2[j], t2a, t2b); f2_unpack(x[j], xa, xb);
-    f2_unpack(w[0][j], w0a, w0b); f2_unpack(w[1][j], w1a, w1b); f2_unpack(w[2][j], w2a, w2b); f2_unpack(w[3][j], w3a, w3b);
-    const float ya = __fmaf_rn(xa, w3a, __fmaf_rn(t2a, w2a, __fmaf_rn(t0a, w0a, __fmul_rn(t1a, w1a))));
-    const float yb = __fmaf_rn(xb, w3b, __fmaf_rn(t2b, w2b, __fmaf_rn(t0b, w0b, __fmul_rn(t1b, w1b))));
-    const unsigned sbp = pack_bf2(ya, yb);
+    float y[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int k = 2 * j + h;
+      float a = __fmul_rn(t1[k], w[1][k]);
+      a = __fmaf_rn(t0[k], w[0][k], a);
+      a = __fmaf_rn(t2[k], w[2][k], a);
+      y[h] = __fmaf_rn(x[k], w[3][k], a);
+    }
+    const unsigned sbp = pack_bf2(y[0], y[1]);
     const float s0 = bf_lo(sbp), s1 = bf_hi(sbp);
     o[j] = pack_bf2(s0 * fast_sigmoid(s0), s1 * fast_sigmoid(s1));
-#endif
   }
   return make_uint2(o[0], o[1]);
 }
@@ -86,33 +77,46 @@ template <bool TAPS_BF16>
 __device__ __forceinline__ void span_stream(const __nv_bfloat16* __restrict__ partial, long long row_stride, const void* __restrict__ cw,
                                             __nv_bfloat16* win, __nv_bfloat16* __restrict__ out, int inner, int s, int c, int row0,
                                             int row1, int span) {
-  f32x2 w[4][2];
+  float w[4][kVec];
 #pragma unroll
   for (int t = 0; t < 4; ++t) load_taps<TAPS_BF16>(cw, ((size_t)s * 4 + t) * inner + c, w[t]);
   const __nv_bfloat16* col = partial + (size_t)s * inner + c;
-  const bool first = row0 == 0;
-  f32x2 x[kChunk + 3][2];
+  float x[kChunk + 3][kVec];
 #pragma unroll
   for (int t = 0; t < 3; ++t) {
     const int i = row0 - 3 + t;
-    const uint2 v = i < 0 ? *reinterpret_cast<const uint2*>(win + (size_t)(i + 3) * inner + c) : ld8_stream(col + (size_t)i * row_stride);
-    x[t][0] = f2_from_bf2(v.x); x[t][1] = f2_from_bf2(v.y);
+    unpack4(i < 0 ? *reinterpret_cast<const uint2*>(win + (size_t)(i + 3) * inner + c) : ld8_stream(col + (size_t)i * row_stride), x[t]);
   }
-  for (int r0 = row0; r0 < row1; r0 += kChunk) {
+  // full chunks: no per-row predicates, pointers advance by constant strides
+  const __nv_bfloat16* pin = col + (size_t)row0 * row_stride;
+  __nv_bfloat16* pout = out + (size_t)row0 * inner + c;
+  int r = row0;
+  for (; r + kChunk <= row1; r += kChunk) {
     uint2 raw[kChunk];
 #pragma unroll
-    for (int r = 0; r < kChunk; ++r)
-      if (r0 + r < row1) raw[r] = ld8_stream(col + (size_t)(r0 + r) * row_stride);
+    for (int k = 0; k < kChunk; ++k) raw[k] = ld8_stream(pin + k * row_stride);
 #pragma unroll
-    for (int r = 0; r < kChunk; ++r)
-      if (r0 + r < row1) { x[3 + r][0] = f2_from_bf2(raw[r].x); x[3 + r][1] = f2_from_bf2(raw[r].y); }
+    for (int k = 0; k < kChunk; ++k) unpack4(raw[k], x[3 + k]);
 #pragma unroll
-    for (int r = 0; r < kChunk; ++r)
-      if (r0 + r < row1) __stcs(reinterpret_cast<uint2*>(out + (size_t)(r0 + r) * inner + c), conv_silu_row(x[r], x[r + 1], x[r + 2], x[r + 3], w));
+    for (int k = 0; k < kChunk; ++k) __stcs(reinterpret_cast<uint2*>(pout + (size_t)k * inner), conv_silu_row(x[k], x[k + 1], x[k + 2], x[k + 3], w));
 #pragma unroll
-    for (int t = 0; t < 3; ++t) { x[t][0] = x[kChunk + t][0]; x[t][1] = x[kChunk + t][1]; }
+    for (int t = 0; t < 3; ++t)
+#pragma unroll
+      for (int k = 0; k < kVec; ++k) x[t][k] = x[kChunk + t][k];
+    pin += kChunk * row_stride;
+    pout += (size_t)kChunk * inner;
   }
-  if (first) {
+  for (; r < row1; ++r) {                                   // ragged tail, one row at a time
+    unpack4(ld8_stream(pin), x[3]);
+    __stcs(reinterpret_cast<uint2*>(pout), conv_silu_row(x[0], x[1], x[2], x[3], w));
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+#pragma unroll
+      for (int k = 0; k < kVec; ++k) x[t][k] = x[t + 1][k];
+    pin += row_stride;
+    pout += inner;
+  }
+  if (row0 == 0) {
     // new window = inputs span-3 .. span-1 (old window rows when span < 3); this thread has
     // already read every old tap it needs, and no other thread touches these columns
     uint2 nw[3];
@@ -126,17 +130,20 @@ __device__ __forceinline__ void span_stream(const __nv_bfloat16* __restrict__ pa
   }
 }
 
-// beta transpose + flow landing: the rows of one z-chunk are dealt round-robin to the chunk's x-blocks
+// beta transpose + flow landing for one z-chunk of rows, shared by the chunk's x-blocks: block x takes
+// the heads h = x, x + gridDim.x, ... (stores along i stay contiguous) and the rows i = x mod gridDim.x
+// of the flow band (256 contiguous bytes per row).
 __device__ __forceinline__ void span_beta_flow(const float* __restrict__ wsm, int heads, __nv_bfloat16* __restrict__ span_beta,
                                                __nv_bfloat16* __restrict__ span_flow, int row0, int row1, int span) {
-  const int R = (row1 - row0 - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // rows row0 + blockIdx.x + k * gridDim.x
-  if (R <= 0) return;
-  for (int idx = threadIdx.x; idx < R * heads; idx += blockDim.x) {
-    const int h = idx / R, i = row0 + (int)blockIdx.x + (idx % R) * (int)gridDim.x;
+  const int R = row1 - row0, gx = (int)gridDim.x, bx = (int)blockIdx.x;
+  const int nh = (heads - bx + gx - 1) / gx;
+  for (int idx = threadIdx.x; idx < R * nh; idx += blockDim.x) {
+    const int h = bx + (idx / R) * gx, i = row0 + idx % R;
     span_beta[(size_t)h * span + i] = __float2bfloat16_rn(__ldg(wsm + (size_t)i * 256 + h));
   }
-  for (int idx = threadIdx.x; idx < R * 32; idx += blockDim.x) {
-    const int i = row0 + (int)blockIdx.x + (idx / 32) * (int)gridDim.x, c4 = (idx % 32) * 4;
+  const int nr = (R - bx + gx - 1) / gx;
+  for (int idx = threadIdx.x; idx < nr * 32; idx += blockDim.x) {
+    const int i = row0 + bx + (idx / 32) * gx, c4 = (idx % 32) * 4;
     const float4 v = __ldcs(reinterpret_cast<const float4*>(wsm + (size_t)i * 256 + 96 + c4));
     *reinterpret_cast<uint2*>(span_flow + (size_t)i * 128 + c4) = make_uint2(pack_bf2(v.x, v.y), pack_bf2(v.z, v.w));
   }
@@ -191,43 +198,52 @@ __device__ __forceinline__ void out_gate_body(const __nv_bfloat16* __restrict__ 
     const float4 m0 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0)), m1 = __ldg(reinterpret_cast<const float4*>(gamma_o + d0 + 4));
     gm[0] = f2_pack(m0.x, m0.y); gm[1] = f2_pack(m0.z, m0.w); gm[2] = f2_pack(m1.x, m1.y); gm[3] = f2_pack(m1.z, m1.w);
   }
-  for (int i = blockIdx.x; i < span; i += gridDim.x) {
-    const long long b = at + i;
-    V8 av = {{0u, 0u, 0u, 0u}}, gv = {{0u, 0u, 0u, 0u}};
-    if (live) {
-      av = ld_stream(attn + (size_t)i * inner + col);
-      gv = ld_stream(gate + (size_t)b * gate_stride + gate_off + col);
-    }
-    float ss = 0.f;
+  // two rows per pass: four 16-byte loads in flight per thread before the first dependent instruction
+  for (int i0 = 2 * blockIdx.x; i0 < span; i0 += 2 * gridDim.x) {
+    V8 av[2], gv[2];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float lo = bf_lo(av.w[j]), hi = bf_hi(av.w[j]);
-      ss = __fmaf_rn(lo, lo, ss);
-      ss = __fmaf_rn(hi, hi, ss);
+    for (int k = 0; k < 2; ++k) {
+      av[k] = V8{{0u, 0u, 0u, 0u}}; gv[k] = V8{{0u, 0u, 0u, 0u}};
+      if (live && i0 + k < span) {
+        av[k] = ld_stream(attn + (size_t)(i0 + k) * inner + col);
+        gv[k] = ld_stream(gate + (size_t)(at + i0 + k) * gate_stride + gate_off + col);
+      }
     }
-    ss = butterfly_sum<16>(ss);
-    const f32x2 r2 = f2_splat(__frsqrt_rn(__fmaf_rn(ss, 1.0f / 128.0f, eps)));
-    V8 o;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const unsigned ov = f2_to_bf2(f2_mul(f2_mul(f2_from_bf2(av.w[j]), r2), gm[j]));
-      const unsigned gt = f2_to_bf2(f2_fast_sigmoid(f2_from_bf2(gv.w[j])));
-      o.w[j] = mul_bf2(ov, gt);
-    }
-    if (STORE_GATED && live) st_stream(gated + (size_t)b * inner + col, o);
-    if (QUANT) {
-      unsigned am = absmax8(o);
-      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
-      am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
-      const int e = ue8m0_exp_from_bf16(am);
-      unsigned q0, q1;
-      quant8(o, pow2_neg(e), q0, q1);
-      unsigned sfb = (unsigned)(e + 127);
-      sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
-      sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
-      if (live) {
-        st_stream8(q + (size_t)b * inner + col, q0, q1);
-        if ((lane & 15) == 0) *reinterpret_cast<unsigned*>(sf + (((size_t)b * inner + col) >> 5)) = sfb;
+    for (int k = 0; k < 2; ++k) {
+      const bool on = live && i0 + k < span;
+      const long long b = at + i0 + k;
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf_lo(av[k].w[j]), hi = bf_hi(av[k].w[j]);
+        ss = __fmaf_rn(lo, lo, ss);
+        ss = __fmaf_rn(hi, hi, ss);
+      }
+      ss = butterfly_sum<16>(ss);
+      const f32x2 r2 = f2_splat(__frsqrt_rn(__fmaf_rn(ss, 1.0f / 128.0f, eps)));
+      V8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned ov = f2_to_bf2(f2_mul(f2_mul(f2_from_bf2(av[k].w[j]), r2), gm[j]));
+        const unsigned gt = f2_to_bf2(f2_fast_sigmoid(f2_from_bf2(gv[k].w[j])));
+        o.w[j] = mul_bf2(ov, gt);
+      }
+      if (STORE_GATED && on) st_stream(gated + (size_t)b * inner + col, o);
+      if (QUANT) {
+        unsigned am = absmax8(o);
+        am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = max_bf16_bits(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        const int e = ue8m0_exp_from_bf16(am);
+        unsigned q0, q1;
+        quant8(o, pow2_neg(e), q0, q1);
+        unsigned sfb = (unsigned)(e + 127);
+        sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
+        sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+        if (on) {
+          st_stream8(q + (size_t)b * inner + col, q0, q1);
+          if ((lane & 15) == 0) *reinterpret_cast<unsigned*>(sf + (((size_t)b * inner + col) >> 5)) = sfb;
+        }
       }
     }
   }
@@ -309,7 +325,7 @@ K3G_API int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_
   K3G_REQUIRE(((uintptr_t)q & 7) == 0 && ((uintptr_t)sf & 3) == 0, K3G_EALIGN);
   K3G_REQUIRE(heads > 0 && heads % 2 == 0 && span >= 0 && at >= 0 && gate_stride % 8 == 0 && gate_off % 8 == 0, K3G_ESHAPE);
   if (span == 0) return K3G_OK;
-  const dim3 grid((unsigned)span, (unsigned)((heads * 16 + 127) / 128), 1);
+  const dim3 grid((unsigned)((span + 1) / 2), (unsigned)((heads * 16 + 127) / 128), 1);
   cudaStream_t st = k3g_stream(stream);
 #define K3G_OG_ARGS (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, gate_stride, gate_off, (const float*)gamma_o, \
     (__nv_bfloat16*)gated, (uint8_t*)q, (uint8_t*)sf, heads, at, span, eps

@@ -235,30 +235,38 @@ __device__ __forceinline__ void finalize_body(const __nv_bfloat16* __restrict__ 
 }
 
 // dst row r = src row route_map[r]: `cols` code bytes and cols / 32 scale bytes per row.
-__global__ void __launch_bounds__(128) permute_gather_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+// One WARP per destination row: a lane issues up to eight 16-byte loads before its first store,
+// rows are walked with a warp stride, and the token id of the next row is fetched one row ahead.
+__global__ void __launch_bounds__(256) permute_gather_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
                                                              const int* __restrict__ route_map, long long rows, int cols,
                                                              uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int qv = cols >> 4, sfb = cols >> 5;
-  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
-    const long long t = route_map[r];
+  const bool sf_vec = (sfb & 15) == 0;
+  long long r = warp;
+  long long t = r < rows ? route_map[r] : 0;
+  while (r < rows) {
+    const long long rn = r + nwarps;
+    const long long tn = rn < rows ? route_map[rn] : 0;
     const uint4* src = reinterpret_cast<const uint4*>(q + t * cols);
     uint4* dst = reinterpret_cast<uint4*>(out_q + r * cols);
-    for (int v0 = threadIdx.x; v0 < qv; v0 += 4 * blockDim.x) {      // four loads in flight per thread
-      uint4 x[4];
+    for (int v0 = lane; v0 < qv; v0 += 8 * 32) {
+      uint4 x[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + u * blockDim.x < qv) x[u] = __ldg(src + v0 + u * blockDim.x);   // a token row is read once per expert it routes to: keep it cached
+      for (int u = 0; u < 8; ++u)
+        if (v0 + 32 * u < qv) x[u] = __ldg(src + v0 + 32 * u);      // a token row is read once per expert it routes to: keep it cached
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + u * blockDim.x < qv) __stcs(dst + v0 + u * blockDim.x, x[u]);
+      for (int u = 0; u < 8; ++u)
+        if (v0 + 32 * u < qv) __stcs(dst + v0 + 32 * u, x[u]);
     }
-    if ((sfb & 15) == 0) {
-      const int sv = sfb >> 4;
-      if ((int)threadIdx.x < sv)
-        __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + threadIdx.x, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + threadIdx.x));
+    if (sf_vec) {
+      if (lane < (sfb >> 4)) __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + lane, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + lane));
     } else {
-      for (int b = threadIdx.x; b < sfb; b += blockDim.x) out_sf[r * sfb + b] = sf[t * sfb + b];
+      for (int b = lane; b < sfb; b += 32) out_sf[r * sfb + b] = sf[t * sfb + b];
     }
+    r = rn; t = tn;
   }
 }
 
@@ -383,8 +391,9 @@ K3G_API int k3g_permute_gather(const void* q, const void* sf, const void* route_
   K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
   if ((cols >> 5) % 16 == 0) { K3G_REQUIRE_ALIGNED(sf); K3G_REQUIRE_ALIGNED(out_sf); }
   if (rows == 0) return K3G_OK;
-  const long long grid = rows < 0x7fffffffLL ? rows : 0x7fffffffLL;
-  permute_gather_kernel<<<(unsigned)grid, 128, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
+  long long grid = (rows + 7) / 8;                 // eight warps per block, one row per warp pass
+  if (grid > 148 * 64) grid = 148 * 64;            // then rows are walked with a warp stride
+  permute_gather_kernel<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
                                                                        cols, (uint8_t*)out_q, (uint8_t*)out_sf);
   return k3g_launch_status();
 }

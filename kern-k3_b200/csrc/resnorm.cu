@@ -87,16 +87,28 @@ __device__ __forceinline__ void team_rms_store(const V8 (&x)[VPT], const __nv_bf
 
 // Attention-residual mix of source/k3_residual_v2.cu:122-223: candidates 0..nb-1 are the
 // snapshot rows, candidate nb is the prefix row held in x (overwritten with the mix).
+//
+// Statistics hand-off (source/k3_residual_push_add2.cu:273-279, source/k3_residual_nb_stats.cu:254-258):
+//   producer  (sw_other != nullptr): also accumulates dp'_c = sum x_c * sw_other for the snapshot
+//             candidates and stores (sq_c, dp'_c) to stats_out[c] -- the numbers the NEXT residual
+//             kernel of the layer would compute for the same rows with its own scoring vector;
+//   consumer  (nb_stats > 0): takes (sq_c, dp_c) of candidates c < nb_stats from stats_in instead of
+//             reading those rows in pass 1.  Same summation order on both sides, so the value read
+//             is bit-identical to the value recomputed.
 template <int VPT>
 __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat16* __restrict__ blk_row,
-                                                 const float* __restrict__ sw, int nb, float eps, float* s_mix, int t) {
+                                                 const float* __restrict__ sw, int nb, float eps, float* s_mix, int t,
+                                                 const float* __restrict__ sw_other = nullptr, float* __restrict__ stats_out = nullptr,
+                                                 const float* __restrict__ stats_in = nullptr, int nb_stats = 0) {
   constexpr int H = VPT * 1024;
   constexpr int NW = kTeam / 32;
   const int lane = t & 31, warp = t >> 5;
   const int ncand = nb + 1;
+  float* s_oth = s_mix + (kNbMax + 1) * 2 * NW;       // dp' warp partials (producer only)
   // pass 1: (sum x^2, sum x*sw) per candidate, candidate by candidate (same per-thread order)
-  for (int c = 0; c < ncand; ++c) {
-    float sq = 0.f, dp = 0.f;
+  for (int c = (nb_stats < nb ? nb_stats : nb); c < ncand; ++c) {
+    float sq = 0.f, dp = 0.f, dq = 0.f;
+    const bool other = sw_other != nullptr && c < nb;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int u = (t + v * kTeam) * 8;
@@ -109,21 +121,45 @@ __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat
         sq = __fmaf_rn(lo, lo, sq);  sq = __fmaf_rn(hi, hi, sq);
         dp = __fmaf_rn(lo, s8[2 * j], dp);  dp = __fmaf_rn(hi, s8[2 * j + 1], dp);
       }
+      if (other) {
+        const float4 c0 = __ldg((const float4*)(sw_other + u)), c1 = __ldg((const float4*)(sw_other + u + 4));
+        const float o8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dq = __fmaf_rn(bf_lo(cv.w[j]), o8[2 * j], dq);  dq = __fmaf_rn(bf_hi(cv.w[j]), o8[2 * j + 1], dq);
+        }
+      }
     }
     sq = butterfly_sum<32>(sq);
     dp = butterfly_sum<32>(dp);
     if (lane == 0) { s_mix[(2 * c) * NW + warp] = sq; s_mix[(2 * c + 1) * NW + warp] = dp; }
+    if (other) {
+      dq = butterfly_sum<32>(dq);
+      if (lane == 0) s_oth[c * NW + warp] = dq;
+    }
   }
   __syncthreads();
   float sc = -3.0e38f;
   if (lane < ncand) {
     float sqv = 0.f, dpv = 0.f;
+    if (lane < nb_stats && lane < nb) {
+      sqv = __ldg(stats_in + 2 * lane);
+      dpv = __ldg(stats_in + 2 * lane + 1);
+    } else {
 #pragma unroll
-    for (int w = 0; w < NW; ++w) {
-      sqv = __fadd_rn(sqv, s_mix[(2 * lane) * NW + w]);
-      dpv = __fadd_rn(dpv, s_mix[(2 * lane + 1) * NW + w]);
+      for (int w = 0; w < NW; ++w) {
+        sqv = __fadd_rn(sqv, s_mix[(2 * lane) * NW + w]);
+        dpv = __fadd_rn(dpv, s_mix[(2 * lane + 1) * NW + w]);
+      }
     }
     sc = __fmul_rn(dpv, __frsqrt_rn(__fmaf_rn(sqv, 1.0f / (float)H, eps)));
+    if (stats_out != nullptr && lane < nb && warp == 0) {
+      float dqv = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) dqv = __fadd_rn(dqv, s_oth[lane * NW + w]);
+      stats_out[2 * lane] = sqv;
+      stats_out[2 * lane + 1] = dqv;
+    }
   }
   float mx = sc;
 #pragma unroll
@@ -156,6 +192,8 @@ __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat
     for (int j = 0; j < 4; ++j) x[v].w[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
   }
 }
+
+constexpr int kMixSmem = (kNbMax + 1) * 3 * (kTeam / 32);   // sq, dp and dp' warp partials
 
 // ---- fused residual add + RMSNorm + MXFP8 ------------------------------------------------
 template <int VPT, bool STORE_NORMED>
@@ -192,7 +230,7 @@ __device__ __forceinline__ void attnres_rms_body(const __nv_bfloat16* __restrict
                                                  __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps) {
   constexpr int H = VPT * 1024;
   __shared__ float s_red[2][kTeam / 32];
-  __shared__ float s_mix[(kNbMax + 1) * 2 * (kTeam / 32)];
+  __shared__ float s_mix[kMixSmem];
   const int t = threadIdx.x;
   int it = 0;
   for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
@@ -215,11 +253,13 @@ template <int VPT, bool LB16>
 __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix,
                                                           const __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
                                                           const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,
-                                                          __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps) {
+                                                          __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps,
+                                                          const float* __restrict__ stats = nullptr, int nb_stats = 0) {
   constexpr int H = VPT * 1024;
   __shared__ float s_red[2][kTeam / 32];
-  __shared__ float s_mix[(kNbMax + 1) * 2 * (kTeam / 32)];
+  __shared__ float s_mix[kMixSmem];
   const int t = threadIdx.x;
+  if (stats == nullptr) nb_stats = 0;
   int it = 0;
   for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
     const size_t base = (size_t)b * H;
@@ -246,8 +286,88 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
       }
       st_stream(prefix2 + off, x[v]);
     }
-    if (nb > 0) team_attnres_mix<VPT>(x, blocks + (size_t)b * kNbMax * H, sw, nb, eps, s_mix, t);
+    if (nb > 0)
+      team_attnres_mix<VPT>(x, blocks + (size_t)b * kNbMax * H, sw, nb, eps, s_mix, t, nullptr, nullptr,
+                            nb_stats > 0 ? stats + (size_t)b * kNbMax * 2 : nullptr, nb_stats);
     team_rms_store<VPT, true, false>(x, gamma, normed + base, nullptr, nullptr, eps, s_red[it & 1], t);
+  }
+}
+
+// ---- K1a fused with the preceding landing add and the following all-gather ---------------------
+// kern_k3_attnres_rms_push of source/k3_residual_push_add2.cu:369-444: hidden = bf16(prefix2 + p1 (+ p2))
+// (the K1c expression, f32 adds in that order, one rounding), optional snapshot, attention-residual
+// mix with the statistics hand-off, RMSNorm, and the normed row stored to this rank's slice of every
+// rank's normed_all (own copy write-back, peer copies streaming).  The barrier is a separate launch.
+template <int VPT>
+__device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
+                                                      const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ normed_all,
+                                                      const unsigned long long* __restrict__ dst_peer, int nb, int snapshot, int B, int rank,
+                                                      int nranks, const float* __restrict__ sw_mlp, float* __restrict__ stats,
+                                                      const __nv_bfloat16* __restrict__ p1, const __nv_bfloat16* __restrict__ p2,
+                                                      const __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ hidden, int two,
+                                                      float eps) {
+  constexpr int H = VPT * 1024;
+  __shared__ float s_red[2][kTeam / 32];
+  __shared__ float s_mix[kMixSmem];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int nr = nranks < 8 ? nranks : 8;
+  __nv_bfloat16* peer[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) peer[q] = (q < nr && q != rank) ? reinterpret_cast<__nv_bfloat16*>(dst_peer[q]) : nullptr;
+  int it = 0;
+  for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
+    const size_t base = (size_t)b * H;
+    V8 x[VPT];
+    {
+      V8 a[VPT], c[VPT];
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) a[v] = ld_stream(prefix2 + base + (t + v * kTeam) * 8);
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) c[v] = ld_stream(p1 + base + (t + v * kTeam) * 8);
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          f[2 * j] = __fadd_rn(bf_lo(a[v].w[j]), bf_lo(c[v].w[j]));
+          f[2 * j + 1] = __fadd_rn(bf_hi(a[v].w[j]), bf_hi(c[v].w[j]));
+        }
+        if (two) {
+          const V8 e = ld_stream(p2 + base + (t + v * kTeam) * 8);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            f[2 * j] = __fadd_rn(f[2 * j], bf_lo(e.w[j]));
+            f[2 * j + 1] = __fadd_rn(f[2 * j + 1], bf_hi(e.w[j]));
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[v].w[j] = pack_bf2(f[2 * j], f[2 * j + 1]);
+        st_plain(hidden + base + (t + v * kTeam) * 8, x[v]);
+      }
+    }
+    __nv_bfloat16* blk_row = blocks + (size_t)b * kNbMax * H;
+    if (snapshot && nb < kNbMax) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) st_plain(blk_row + (size_t)nb * H + (t + v * kTeam) * 8, x[v]);
+    }
+    if (nb > 0)
+      team_attnres_mix<VPT>(x, blk_row, sw, nb, eps, s_mix, t, stats ? sw_mlp : nullptr, stats ? stats + (size_t)b * kNbMax * 2 : nullptr);
+    const float tot = team_sumsq<VPT>(x, s_red[it & 1], lane, warp);
+    const float r = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
+    const size_t dst_off = ((size_t)rank * B + b) * H;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      const int u = (t + v * kTeam) * 8;
+      const V8 g = ld_keep(gamma + u);
+      V8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(x[v].w[j]), r), __fmul_rn(bf_hi(x[v].w[j]), r)), g.w[j]);
+      st_plain(normed_all + dst_off + u, o);            // own slice: the next GEMM reads it, keep it in L2
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (peer[q] != nullptr) st_stream(peer[q] + dst_off + u, o);
+    }
   }
 }
 
@@ -314,6 +434,16 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms(
   attnres_rms_body<K3G_RES_VPT>(prefix, blocks, sw, gamma, normed, nb, snapshot, B, K3G_RES_EPS);
 }
 
+// op attnres_rms_push_add2 (module k3_residual_push_add2): 17 kernel parameters, reference order.
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms_push(
+    __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma,
+    __nv_bfloat16* __restrict__ normed_all, const unsigned long long* __restrict__ dst_peer, int nb, int snapshot, int B, int rank,
+    int nranks, const float* __restrict__ sw_mlp, float* __restrict__ stats, const __nv_bfloat16* __restrict__ p1,
+    const __nv_bfloat16* __restrict__ p2, const __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ hidden, int two) {
+  attnres_rms_push_body<K3G_RES_VPT>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2,
+                                     hidden, two, K3G_RES_EPS);
+}
+
 #if defined(K3G_CUBIN_ONLY)
 // one landing dtype per module, as in the reference (-DLAND_BF16 selects bf16)
 #ifdef LAND_BF16
@@ -329,6 +459,19 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rm
     __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B) {
   land_add_attnres_rms_body<K3G_RES_VPT, K3G_LAND_IS_BF16>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, K3G_RES_EPS);
 }
+// ops land_add_attnres_rms_bf16_v2_nb{1..8} (modules k3_residual_nb, k3_residual_nb_stats): one entry per
+// candidate count in the reference; the count is a run-time argument here, the entries share one body.
+#define K3G_NB_ENTRY(K)                                                                                                          \
+  extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rms_nb##K(                                       \
+      const k3g_land_t* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix, const __nv_bfloat16* __restrict__ blocks, \
+      const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,                \
+      __nv_bfloat16* __restrict__ normed, int nb_in, int snapshot, int B, const float* __restrict__ stats, int nb_stats) {        \
+    if (nb_in != K) return;                                                                                                      \
+    land_add_attnres_rms_body<K3G_RES_VPT, K3G_LAND_IS_BF16>(partial, prefix, blocks, sw, gamma, prefix2, normed, K, snapshot, B, \
+                                                             K3G_RES_EPS, stats, nb_stats);                                      \
+  }
+K3G_NB_ENTRY(1) K3G_NB_ENTRY(2) K3G_NB_ENTRY(3) K3G_NB_ENTRY(4) K3G_NB_ENTRY(5) K3G_NB_ENTRY(6) K3G_NB_ENTRY(7) K3G_NB_ENTRY(8)
+
 extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add2(
     const k3g_land_t* __restrict__ p1, const k3g_land_t* __restrict__ p2, const __nv_bfloat16* __restrict__ prefix2,
     __nv_bfloat16* __restrict__ hidden, int two, int B) {
@@ -345,8 +488,17 @@ __global__ void __launch_bounds__(128, 4) attnres_rms_kernel(const __nv_bfloat16
 template <int VPT, bool LB>
 __global__ void __launch_bounds__(128, 4) land_add_attnres_rms_kernel(const void* partial, const __nv_bfloat16* prefix, const __nv_bfloat16* blocks,
                                                                      const float* sw, const __nv_bfloat16* gamma, __nv_bfloat16* prefix2,
-                                                                     __nv_bfloat16* normed, int nb, int snapshot, int B, float eps) {
-  land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps);
+                                                                     __nv_bfloat16* normed, int nb, int snapshot, int B, float eps,
+                                                                     const float* stats, int nb_stats) {
+  land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps, stats, nb_stats);
+}
+template <int VPT>
+__global__ void __launch_bounds__(128, 4) attnres_rms_push_kernel(__nv_bfloat16* blocks, const float* sw, const __nv_bfloat16* gamma,
+                                                                 __nv_bfloat16* normed_all, const unsigned long long* dst_peer, int nb,
+                                                                 int snapshot, int B, int rank, int nranks, const float* sw_mlp, float* stats,
+                                                                 const __nv_bfloat16* p1, const __nv_bfloat16* p2, const __nv_bfloat16* prefix2,
+                                                                 __nv_bfloat16* hidden, int two, float eps) {
+  attnres_rms_push_body<VPT>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two, eps);
 }
 template <int VPT, bool LB>
 __global__ void __launch_bounds__(128, 4) land_add2_kernel(const void* p1, const void* p2, const __nv_bfloat16* prefix2,
@@ -403,9 +555,9 @@ K3G_API int k3g_attnres_rms(const void* prefix, void* blocks, const void* sw, co
   return k3g_launch_status();
 }
 
-K3G_API int k3g_land_add_attnres_rms(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+static int land_add_attnres_rms_impl(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
                                      const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
-                                     int B, int H, float eps, void* stream) {
+                                     int B, int H, float eps, const void* stats, int nb_stats, void* stream) {
   K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(prefix2); K3G_REQUIRE_PTR(normed);
   if (!snapshot) K3G_REQUIRE_PTR(prefix);
   K3G_REQUIRE(nb >= 0 && nb <= kNbMax, K3G_ERANGE);
@@ -417,12 +569,55 @@ K3G_API int k3g_land_add_attnres_rms(const void* partial, int partial_is_bf16, c
   if (partial_is_bf16) {
     K3G_DISPATCH_VPT(H, (land_add_attnres_rms_kernel<VPT, true><<<B, kTeam, 0, k3g_stream(stream)>>>(
         partial, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma,
-        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps)));
+        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats, nb_stats)));
   } else {
     K3G_DISPATCH_VPT(H, (land_add_attnres_rms_kernel<VPT, false><<<B, kTeam, 0, k3g_stream(stream)>>>(
         partial, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma,
-        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps)));
+        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats, nb_stats)));
   }
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_land_add_attnres_rms(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+                                     const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
+                                     int B, int H, float eps, void* stream) {
+  return land_add_attnres_rms_impl(partial, partial_is_bf16, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, H, eps, nullptr, 0,
+                                   stream);
+}
+
+// The per-candidate-count entries of the reference (kern_k3_land_add_attnres_rms_nb1..8) with the
+// statistics hand-off: stats [B, 8, 2] = (sum x^2, sum x * sw) of snapshot candidates c < nb_stats, as
+// written by k3g_attnres_rms_push; those candidates are not re-read in the scoring pass.
+K3G_API int k3g_land_add_attnres_rms_stats(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+                                           const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
+                                           int B, int H, float eps, const void* stats, int nb_stats, void* stream) {
+  K3G_REQUIRE(nb_stats >= 0 && nb_stats <= nb, K3G_ERANGE);
+  if (nb_stats > 0) K3G_REQUIRE_PTR(stats);
+  return land_add_attnres_rms_impl(partial, partial_is_bf16, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, H, eps, stats,
+                                   nb_stats, stream);
+}
+
+// kern_k3_attnres_rms_push (op attnres_rms_push_add2): landing add + snapshot + mix + RMSNorm + push of the
+// normed row into every rank's normed_all [nranks * B, H]; stats (may be null) receives the hand-off.
+K3G_API int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
+                                 int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
+                                 const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream) {
+  K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(normed_all); K3G_REQUIRE_PTR(dst_peer); K3G_REQUIRE_PTR(p1); K3G_REQUIRE_PTR(prefix2);
+  K3G_REQUIRE_PTR(hidden);
+  if (two) K3G_REQUIRE_PTR(p2);
+  K3G_REQUIRE(nb >= 0 && nb <= kNbMax, K3G_ERANGE);
+  if (nb > 0 || snapshot) K3G_REQUIRE_PTR(blocks);
+  if (nb > 0) K3G_REQUIRE_PTR(sw);
+  if (stats) K3G_REQUIRE_PTR(sw_mlp);
+  K3G_REQUIRE(nranks >= 1 && nranks <= 8 && B >= 0 && H > 0 && H % 1024 == 0, K3G_ESHAPE);
+  K3G_REQUIRE(rank >= 0 && rank < nranks, K3G_ERANGE);
+  K3G_REQUIRE_ALIGNED(blocks); K3G_REQUIRE_ALIGNED(sw); K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(normed_all); K3G_REQUIRE_ALIGNED(sw_mlp);
+  K3G_REQUIRE_ALIGNED(p1); K3G_REQUIRE_ALIGNED(p2); K3G_REQUIRE_ALIGNED(prefix2); K3G_REQUIRE_ALIGNED(hidden);
+  if (B == 0) return K3G_OK;
+  K3G_DISPATCH_VPT(H, (attnres_rms_push_kernel<VPT><<<B, kTeam, 0, k3g_stream(stream)>>>(
+      (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed_all, (const unsigned long long*)dst_peer, nb,
+      snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, (const __nv_bfloat16*)p1, (const __nv_bfloat16*)p2,
+      (const __nv_bfloat16*)prefix2, (__nv_bfloat16*)hidden, two, eps)));
   return k3g_launch_status();
 }
 

@@ -21,6 +21,8 @@ OUT = os.path.join(HERE, "_ref")
 MODULES = {
     "k3_residual_v2": ("source/k3_residual_v2.cu", [], False),
     "k3_residual_v2+LAND_BF16=1": ("source/k3_residual_v2.cu", ["-DLAND_BF16=1"], False),
+    "k3_residual_nb_stats": ("source/k3_residual_nb_stats.cu", ["-DLAND_BF16=1"], False),
+    "k3_residual_push_add2": ("source/k3_residual_push_add2.cu", [], False),
     "k3_quant_fp8_pair_v2": ("source/k3_quant_fp8_pair_v2.cu", [], False),
     "k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16":
         ("source/k3_moe_prefill_v4.cu", ["-DEP_RANKS=4", "-DEP_STRIDED=1", "-DTILE_SHIFT=7", "-DSCATTER_WARPS=16"], True),

@@ -99,6 +99,27 @@ def land_add_attnres_rms(partial, prefix, blocks, sw, gamma, nb, snapshot, eps):
     return prefix2, normed
 
 
+def land_add_attnres_rms_stats(partial, prefix, blocks, sw, gamma, nb, snapshot, eps, stats, nb_stats):
+    B, H = partial.shape
+    is_bf16 = int(partial.dtype == np.uint16)
+    prefix2 = np.empty((B, H), np.uint16)
+    normed = np.empty((B, H), np.uint16)
+    lib().k3o_land_add_attnres_rms_stats(_p(partial), I(is_bf16), _p(prefix), _p(blocks), _p(sw), _p(gamma), _p(prefix2),
+                                         _p(normed), I(nb), I(snapshot), I(B), I(H), F(eps), _p(stats), I(nb_stats))
+    return prefix2, normed
+
+
+def attnres_rms_push(blocks, sw, gamma, nb, snapshot, sw_mlp, p1, p2, prefix2, two, eps, want_stats=True):
+    """Returns (hidden, normed, stats); blocks is updated in place when snapshot is set."""
+    B, H = prefix2.shape
+    hidden = np.empty((B, H), np.uint16)
+    normed = np.empty((B, H), np.uint16)
+    stats = np.zeros((B, 8, 2), np.float32) if want_stats else None
+    lib().k3o_attnres_rms_push(_p(blocks), _p(sw), _p(gamma), _p(normed), I(nb), I(snapshot), I(B), _p(sw_mlp), _p(stats),
+                               _p(p1), _p(p2), _p(prefix2), _p(hidden), I(two), I(H), F(eps))
+    return hidden, normed, stats
+
+
 def land_add2(p1, p2, prefix2, two):
     B, H = prefix2.shape
     is_bf16 = int(p1.dtype == np.uint16)

@@ -98,8 +98,11 @@ static float row_reduce(const RowLayout& L, F fn) {
 
 // attnres_rms_row (source/k3_residual_v2.cu:107-257).  pv: the prefix candidate (bf16 row,
 // overwritten with the mixed row); blk_row: the nb snapshot rows.
+// Statistics hand-off: sw_other/stats_out (producer, source/k3_residual_push_add2.cu:273-279) and
+// stats_in/nb_stats (consumer, source/k3_residual_nb_stats.cu:254-258); [8][2] floats for this row.
 static void attnres_rms_row(const RowLayout& L, const u16* blk_row, u16* pv, const float* sw,
-                            const u16* gamma, u16* normed_row, int nb, float eps) {
+                            const u16* gamma, u16* normed_row, int nb, float eps, const float* sw_other = nullptr,
+                            float* stats_out = nullptr, const float* stats_in = nullptr, int nb_stats = 0) {
   const int H = L.H;
   const float invH = 1.0f / (float)H;
   if (nb > 0) {
@@ -108,8 +111,17 @@ static void attnres_rms_row(const RowLayout& L, const u16* blk_row, u16* pv, con
     for (int l = 0; l < 32; ++l) sc[l] = -3.0e38f;
     for (int c = 0; c < ncand; ++c) {                    // lane c's candidate (:171-179)
       const u16* x = (c < nb) ? blk_row + (size_t)c * H : pv;
-      const float sq = row_reduce(L, [&](int e, float& a, float& b) { a = bf2f(x[e]); b = a; });
-      const float dp = row_reduce(L, [&](int e, float& a, float& b) { a = bf2f(x[e]); b = sw[e]; });
+      float sq, dp;
+      if (stats_in && c < nb_stats && c < nb) {
+        sq = stats_in[2 * c]; dp = stats_in[2 * c + 1];
+      } else {
+        sq = row_reduce(L, [&](int e, float& a, float& b) { a = bf2f(x[e]); b = a; });
+        dp = row_reduce(L, [&](int e, float& a, float& b) { a = bf2f(x[e]); b = sw[e]; });
+      }
+      if (stats_out && c < nb) {
+        stats_out[2 * c] = sq;
+        stats_out[2 * c + 1] = row_reduce(L, [&](int e, float& a, float& b) { a = bf2f(x[e]); b = sw_other[e]; });
+      }
       sc[c] = dp * rsqrt_rn(std::fmaf(sq, invH, eps));
     }
     float mxv[32];
@@ -165,6 +177,49 @@ K3O_API void k3o_land_add_attnres_rms(const void* partial, int partial_is_bf16, 
     }
     attnres_rms_row(L, blocks ? blocks + (size_t)b * 8 * H : nullptr, pv.data(), sw, gamma,
                     normed + (size_t)b * H, nb, eps);
+  }
+}
+
+// kern_k3_land_add_attnres_rms_nbK with the statistics of candidates c < nb_stats taken from `stats`
+// [B, 8, 2] (source/k3_residual_nb_stats.cu:366-842).
+K3O_API void k3o_land_add_attnres_rms_stats(const void* partial, int partial_is_bf16, const u16* prefix, const u16* blocks,
+                                            const float* sw, const u16* gamma, u16* prefix2, u16* normed, int nb,
+                                            int snapshot, int B, int H, float eps, const float* stats, int nb_stats) {
+  const RowLayout L(H);
+#pragma omp parallel for schedule(static)
+  for (int b = 0; b < B; ++b) {
+    std::vector<u16> pv(H);
+    for (int e = 0; e < H; ++e) {
+      const size_t off = (size_t)b * H + e;
+      const u16 p = partial_is_bf16 ? ((const u16*)partial)[off] : f2bf(((const float*)partial)[off]);
+      pv[e] = snapshot ? p : f2bf(bf2f(prefix[off]) + bf2f(p));
+      prefix2[off] = pv[e];
+    }
+    attnres_rms_row(L, blocks + (size_t)b * 8 * H, pv.data(), sw, gamma, normed + (size_t)b * H, nb, eps, nullptr, nullptr,
+                    stats + (size_t)b * 16, nb_stats);
+  }
+}
+
+// kern_k3_attnres_rms_push (source/k3_residual_push_add2.cu:369-444): hidden = bf16((prefix2 + p1) + p2),
+// snapshot, mix (+ statistics for the next residual kernel), RMSNorm.  `normed` is the row block every
+// rank receives at rows [rank * B, (rank + 1) * B) of its normed_all.
+K3O_API void k3o_attnres_rms_push(u16* blocks, const float* sw, const u16* gamma, u16* normed, int nb, int snapshot, int B,
+                                  const float* sw_mlp, float* stats, const u16* p1, const u16* p2, const u16* prefix2,
+                                  u16* hidden, int two, int H, float eps) {
+  const RowLayout L(H);
+#pragma omp parallel for schedule(static)
+  for (int b = 0; b < B; ++b) {
+    std::vector<u16> pv(H);
+    for (int e = 0; e < H; ++e) {
+      const size_t off = (size_t)b * H + e;
+      float x = bf2f(prefix2[off]) + bf2f(p1[off]);
+      if (two) x += bf2f(p2[off]);
+      pv[e] = f2bf(x);
+      hidden[off] = pv[e];
+    }
+    if (snapshot && nb < 8) std::memcpy(blocks + ((size_t)b * 8 + nb) * H, pv.data(), (size_t)H * 2);
+    attnres_rms_row(L, blocks ? blocks + (size_t)b * 8 * H : nullptr, pv.data(), sw, gamma, normed + (size_t)b * H, nb, eps,
+                    stats ? sw_mlp : nullptr, stats ? stats + (size_t)b * 16 : nullptr);
   }
 }
 

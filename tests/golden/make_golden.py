@@ -37,6 +37,25 @@ def run_reference(name, inp, dev):
     import torch
     bf = torch.bfloat16
     z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+    if name == "push_add2":
+        B, H = inp["prefix2"].shape
+        blocks, hidden = _up(inp["blocks"], dev), z((B, H), bf)
+        normed_all = z((4 * B, H), bf)
+        others = [z((4 * B, H), bf) for _ in range(3)]      # the three peers' copies, on this GPU
+        tab = torch.tensor([others[0].data_ptr(), normed_all.data_ptr(), others[1].data_ptr(), others[2].data_ptr()], dtype=torch.int64, device=dev)
+        stats = z((B, 8, 2), torch.float32)
+        refcubin.run("k3_residual_push_add2", "kern_k3_attnres_rms_push", B, 128,
+                     [blocks, _up(inp["sw"], dev), _up(inp["gamma"], dev), normed_all, tab, 3, 1, B, 1, 4, _up(inp["sw_mlp"], dev), stats,
+                      _up(inp["p1"], dev), _up(inp["p2"], dev), _up(inp["prefix2"], dev), hidden, 1])
+        torch.cuda.synchronize()
+        for o in others:
+            assert torch.equal(o, normed_all)                # every rank's copy received the same slice
+        p2, n2 = z((B, H), bf), z((B, H), bf)
+        refcubin.run("k3_residual_nb_stats", "kern_k3_land_add_attnres_rms_nb4", B, 128,
+                     [_up(inp["partial"], dev), hidden, blocks, _up(inp["sw_mlp"], dev), _up(inp["gamma"], dev), p2, n2, 4, 0, B, stats, 3])
+        torch.cuda.synchronize()
+        return dict(hidden=_bits(hidden), blocks=_bits(blocks), normed_all=_bits(normed_all), stats=stats.cpu().numpy(),
+                    res_mlp_prefix2=_bits(p2), res_mlp_normed=_bits(n2))
     if name in ("k1b_nb0", "k1b_nb3"):
         nb = 0 if name == "k1b_nb0" else 3
         B, H = inp["partial"].shape

@@ -35,6 +35,14 @@ def test_oracle_matches_reference_kernel_outputs(golden, name):
         assert d.max() <= ulp and (d > 0).mean() <= frac, (name, k, int(d.max()), float((d > 0).mean()))
 
 
+def test_stats_handoff_oracle_vs_reference(golden):
+    """(sum x^2, sum x * sw_mlp) per snapshot candidate: IEEE-only sums in a fixed order, so the oracle's
+    statistics equal the reference kernel's bit for bit."""
+    out = cases.run_oracle("push_add2", cases.inputs("push_add2"))
+    want = golden["push_add2/stats"]
+    assert np.array_equal(out["stats"].view(np.uint32)[:, :3], want.view(np.uint32)[:, :3])
+
+
 def test_router_oracle_vs_reference_indices(golden):
     """The reference uses libdevice expf, the oracle an IEEE-only exp: picks may only differ where two
     biased scores are within a few ulps; weights agree to 1e-6 relative where the picks agree."""

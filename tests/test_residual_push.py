@@ -1,0 +1,71 @@
+"""The residual kernels the reference's default program actually runs: landing add + mix + RMSNorm
+with the normed row pushed to every rank (kern_k3_attnres_rms_push) and the per-candidate-count
+residual kernel that consumes the statistics it hands over (kern_k3_land_add_attnres_rms_nbK)."""
+import numpy as np
+import pytest
+
+import k3o
+from util import bf16_bits, normal_bf16, rng, to_dev, to_dev_bf16
+
+
+def _case(seed, B, H=7168):
+    g = rng(seed)
+    d = dict(blocks=normal_bf16(g, (B, 8, H)), sw=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32),
+             sw_mlp=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32), gamma=normal_bf16(g, (H,), mean=1.0, std=0.02),
+             p1=normal_bf16(g, (B, H), std=0.5), p2=normal_bf16(g, (B, H), std=0.5), prefix2=normal_bf16(g, (B, H)),
+             partial=normal_bf16(g, (B, H), std=0.5))
+    return d
+
+
+@pytest.mark.parametrize("nb,nb_stats", [(1, 1), (4, 4), (4, 2), (8, 8), (3, 0)])
+def test_oracle_stats_handoff_is_bit_neutral(nb, nb_stats):
+    """CPU: statistics written by the push kernel equal what the consumer would recompute, so the
+    consumer's output does not depend on how many candidates the hand-off covers."""
+    d = _case(nb, 5)
+    blocks = d["blocks"].copy()
+    hidden, _, stats = k3o.attnres_rms_push(blocks, d["sw"], d["gamma"], nb, 0, d["sw_mlp"], d["p1"], d["p2"], d["prefix2"], 1, 1e-5)
+    plain = k3o.land_add_attnres_rms(d["partial"], hidden, blocks, d["sw_mlp"], d["gamma"], nb, 0, 1e-5)
+    fed = k3o.land_add_attnres_rms_stats(d["partial"], hidden, blocks, d["sw_mlp"], d["gamma"], nb, 0, 1e-5, stats, nb_stats)
+    assert np.array_equal(plain[0], fed[0]) and np.array_equal(plain[1], fed[1])
+    assert np.array_equal(hidden, k3o.land_add2(d["p1"], d["p2"], d["prefix2"], 1))     # the folded K1c
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("W,nb,snapshot,two", [(1, 0, 1, 0), (2, 1, 0, 1), (4, 4, 1, 1), (4, 8, 1, 1), (8, 3, 0, 0)])
+def test_attnres_rms_push_emulated_ranks(k3g, dev, W, nb, snapshot, two):
+    import torch
+    B, H = 13, 7168
+    cases = [_case(100 * W + r, B) for r in range(W)]
+    normed_all = [torch.zeros((W * B, H), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    tab = torch.tensor([t.data_ptr() for t in normed_all], dtype=torch.int64, device=dev)
+    want_rows = []
+    for r, d in enumerate(cases):
+        o_blocks = d["blocks"].copy()
+        o_hidden, o_normed, o_stats = k3o.attnres_rms_push(o_blocks, d["sw"], d["gamma"], nb, snapshot, d["sw_mlp"], d["p1"], d["p2"], d["prefix2"],
+                                                           two, 1e-5)
+        want_rows.append(o_normed)
+        blocks = to_dev_bf16(d["blocks"], dev)
+        hidden = torch.zeros((B, H), dtype=torch.bfloat16, device=dev)
+        stats = torch.zeros((B, 8, 2), dtype=torch.float32, device=dev)
+        k3g.call("k3g_attnres_rms_push", blocks, to_dev(d["sw"], dev), to_dev_bf16(d["gamma"], dev), normed_all[r], tab, nb, snapshot, B, r, W,
+                 to_dev(d["sw_mlp"], dev), stats, to_dev_bf16(d["p1"], dev), to_dev_bf16(d["p2"], dev) if two else None,
+                 to_dev_bf16(d["prefix2"], dev), hidden, two, H, 1e-5, k3g.current_stream())
+        torch.cuda.synchronize()
+        assert np.array_equal(bf16_bits(hidden), o_hidden)
+        assert np.array_equal(bf16_bits(blocks), o_blocks)
+        assert np.array_equal(stats.cpu().numpy().view(np.uint32), o_stats.view(np.uint32))
+        # the consumer fed with the device statistics == the consumer that recomputes them
+        pre = to_dev_bf16(o_hidden, dev)
+        out = [torch.zeros((B, H), dtype=torch.bfloat16, device=dev) for _ in range(4)]
+        if nb > 0:
+            k3g.call("k3g_land_add_attnres_rms_stats", to_dev_bf16(d["partial"], dev), 1, pre, blocks, to_dev(d["sw_mlp"], dev),
+                     to_dev_bf16(d["gamma"], dev), out[0], out[1], nb, 0, B, H, 1e-5, stats, nb, k3g.current_stream())
+            k3g.call("k3g_land_add_attnres_rms", to_dev_bf16(d["partial"], dev), 1, pre, blocks, to_dev(d["sw_mlp"], dev),
+                     to_dev_bf16(d["gamma"], dev), out[2], out[3], nb, 0, B, H, 1e-5, k3g.current_stream())
+            torch.cuda.synchronize()
+            assert torch.equal(out[0], out[2]) and torch.equal(out[1], out[3])
+            o_p2, o_n = k3o.land_add_attnres_rms(d["partial"], o_hidden, o_blocks, d["sw_mlp"], d["gamma"], nb, 0, 1e-5)
+            assert np.array_equal(bf16_bits(out[1]), o_n)
+    want = np.concatenate(want_rows)
+    for r in range(W):
+        assert np.array_equal(bf16_bits(normed_all[r]), want)     # every rank holds the full gathered matrix

@@ -227,6 +227,39 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     return out
 
 
+def bench_layer(rank, world, timed, iters=20):
+    """Per-layer glue: every non-GEMM call of one KDA layer and one MLA layer of the reference's prefill
+    program (k3g/layer.py), replayed as a CUDA graph, with a per-call breakdown from events."""
+    import torch
+    from k3g.layer import LayerGlue
+    out = {}
+    for kind in ("kda", "mla"):
+        lg = LayerGlue(rank, world, TOKENS, kind=kind)
+        lg.capture()
+        graph_us = timed(lg.replay, iters, 3)
+        lg.check_status()
+        acc = {}
+        order = []
+        timed(lg.run, 2, 1)
+        for _ in range(5):
+            ev = lg.run_timed()
+            torch.cuda.synchronize()
+            for label, a, b in ev:
+                if label not in acc:
+                    acc[label] = 0.0; order.append(label)
+                acc[label] += a.elapsed_time(b) * 1e3 / 5
+        lg.check_status()
+        out[kind] = {"graph_us": round(graph_us, 1), "launches": len(order) + 3, "calls": [{"call": l, "us": round(acc[l], 1)} for l in order]}
+        lg.close()
+        del lg
+        torch.cuda.empty_cache()
+    out["weighted_69kda_24mla_us"] = round((69 * out["kda"]["graph_us"] + 24 * out["mla"]["graph_us"]) / 93, 1)
+    out["note"] = ("all non-GEMM calls of one layer of the reference's prefill program at T=16384, world=%d (rows T/%d per rank, %d heads per rank, "
+                   "56 local experts); GEMM/attention outputs are seeded random buffers; per-call times are eager launches with events, graph_us "
+                   "is the whole list as one CUDA graph" % (world, world, 96 // world))
+    return out
+
+
 def run_gpu(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -353,12 +386,15 @@ def run_gpu(args, rank, world, local_rank):
             "clocks": clocks, "roofline": roof, "nvlink": nv, "collectives": coll, "launch_mode": "cuda graph replay of 4 kernels per step (epoch bump, arrive, fused kernel, arrive)",
             "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps, "mode": e2e_mode, "serial_us": round(e2e_serial_us, 1)},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps, "eager_step_us": round(eager_us, 2), "tokens_per_s": round(TOKENS / step_us * 1e6)}
+    if not args.no_ops:
+        glue.close(); glue = None
+        torch.cuda.empty_cache()
+        line["layer_glue"] = bench_layer(rank, world, timed)
     if rank == 0 and world == 1:
         us, cores = cpu_oracle_us(3, 1)
         line["cpu_baseline"] = {"value": round(us, 1), "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": "%d of %d rows (time scaled by %d), best-effort mean of 3" % (CPU_SAMPLE_ROWS, TOKENS, TOKENS // CPU_SAMPLE_ROWS)}
         if not args.no_ops:
-            glue.close(); glue = None
             line["ops"] = bench_ops(k3g, dev, peak_gbs)
     if glue is not None:
         glue.close()

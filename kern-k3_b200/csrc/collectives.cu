@@ -88,12 +88,28 @@ __device__ __forceinline__ void arrive_and_wait(unsigned long long* flags, const
   if (threadIdx.x == 0) fence_acq_rel_sys();
 }
 
-// Tail of a push kernel: one release-add per block after the CTA barrier that orders the block's
-// stores, then block 0 waits for every peer (lane q polls peer q).
+// Tail of a push kernel.  The reference publishes one system-scope release-add per block
+// (source/k3_allgather4_v3.cu:95-98); a system-scope release is expensive and a grid of a few thousand
+// blocks serialises on it.  Here each block fences at device scope and takes a ticket on a device-scope
+// counter; the block that draws the last ticket has, by causality, every block's stores ordered before
+// it and publishes the whole grid's arrivals (gridDim.x, so the counter protocol is unchanged) with ONE
+// system-scope release-add, then re-arms the ticket counter.  Block 0 waits for every peer (lane q polls
+// peer q); it is resident from the start, and no other block ever waits, so the grid always drains.
+__device__ unsigned g_tail_ticket[64];   // one ticket counter per slot (mod 64): launches on different slots may overlap
+
 __device__ __forceinline__ void block_arrive_tail(unsigned long long* flags, const unsigned long long* flags_peer, int slot, int nranks,
                                                   long long timeout_ns, unsigned* status) {
   __syncthreads();
-  if (threadIdx.x == 0) red_release_sys_add(flags + slot, 1ull);
+  if (threadIdx.x == 0) {
+    __threadfence();
+    unsigned* tk = &g_tail_ticket[slot & 63];
+    const unsigned ticket = atomicAdd(tk, 1u);
+    if (ticket == gridDim.x - 1) {
+      *tk = 0u;                                   // stream order keeps the next launch behind this store
+      __threadfence();
+      red_release_sys_add(flags + slot, (unsigned long long)gridDim.x);
+    }
+  }
   if (blockIdx.x == 0 && threadIdx.x < 32) {
     const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
     const int q = threadIdx.x;

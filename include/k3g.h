@@ -203,6 +203,28 @@ int k3g_span_gather(const void* partial, long long row_stride, const void* cw, i
 int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_stride, long long gate_off, const void* gamma_o,
                      void* gated, void* q, void* sf, int heads, int at, int span, float eps, void* stream);
 
+/* ---- remaining per-layer glue --------------------------------------------------------------------- */
+
+/* kern_k3_situ_rms_bf16, source/k3_land_fused.cu:123 (op land_situ_rms): shared-expert SiTU landing
+ * act [B, n] = bf16((4 tanh(g/4) sigmoid(g)) * 25 tanh(u/25)) from sp [B, 2n] = g | u, and the MoE latent
+ * RMSNorm ln [L, h] = bf16(lat * rs) (x) gam, in one launch.  n % 8 == 0, h % 8 == 0, h <= 8192. */
+int k3g_situ_rms(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* stream);
+
+/* kern_sigmoid_mul_bf16, source/sigmoid_mul.cu:15 (op mla_gate): out = bf16(attn * bf16(sigmoid(gate))),
+ * gate(t, h, d) = gate + t * gate_tstride + h * gate_hstride + d. */
+int k3g_sigmoid_mul(void* out, const void* attn, const void* gate, int tokens, int heads, int head_dim, int gate_tstride,
+                    int gate_hstride, void* stream);
+
+/* kern_k3_span_state, source/k3_span_state.cu:19 (ops span_state_load / span_state_store): copy of the
+ * sequence's [24][128][128] f32 KDA state between its state line and a flat buffer. */
+int k3g_span_state(void* kda_base, const void* line_index, long long line_bytes, const void* span_at, void* buf, int to_line,
+                   void* stream);
+
+/* kern_k3_latent_gather, source/k3_mla_v2.cu:22 (op latent_gather): cached latent rows [n, 576] laid
+ * contiguous from 64-row pages; rows >= lens[0] are zero. */
+int k3g_latent_gather(const void* slab, const void* block_table, long long page_stride, const void* lens, void* out, int n,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,23 +24,30 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr"]
 
 SOURCES = ["resnorm.cu", "quant.cu", "router.cu", "moe_route.cu", "collectives.cu", "mla_prep.cu", "kda.cu",
-           "peer.cu", "quant_noalloc.cu"]
+           "peer.cu", "quant_noalloc.cu", "glue_small.cu"]
 
 # reference module name -> (source, defines).  Names follow kernels.toml of the reference.
 CUBINS = {
     "k3_residual_v2": ("resnorm.cu", []),
     "k3_residual_v2+LAND_BF16=1": ("resnorm.cu", ["-DLAND_BF16=1"]),
-    "k3_residual_nb+LAND_BF16=1": ("resnorm.cu", ["-DLAND_BF16=1"]),
+    "k3_residual_nb+LAND_BF16=1": ("resnorm.cu", ["-DLAND_BF16=1", "-DK3G_NB_NO_STATS=1"]),
     "k3_residual_nb_stats": ("resnorm.cu", ["-DLAND_BF16=1"]),
     "k3_residual_push_add2": ("resnorm.cu", ["-DLAND_BF16=1"]),
     "k3_quant_fp8_pair_v2": ("quant.cu", []),
     "k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16":
         ("moe_route.cu", ["-DEP_RANKS=4", "-DEP_STRIDED=1", "-DTILE_SHIFT=7"]),
     "k3_router_argmax": ("router.cu", []),
+    "k3_moe_prefill_v3+EP_STRIDED=1": ("moe_route.cu", ["-DEP_RANKS=4", "-DEP_STRIDED=1"]),
     "k3_collectives": ("collectives.cu", ["-DK3G_NR=4"]),
+    "k3_rs_arrive_v2": ("collectives.cu", ["-DK3G_NR=4"]),
+    "k3_allgather4_v3": ("collectives.cu", ["-DK3G_NR=4"]),
     "k3_reducescatter_pull_nr4": ("collectives.cu", ["-DK3G_NR=4", "-DK3G_ORDER=6"]),
     "k3_mla_prep_v2+INNER=3072+MLA_FUSED=5184": ("mla_prep.cu", ["-DINNER=3072", "-DMLA_FUSED=5184"]),
     "k3_mla_prep_bf16+INNER=3072+MLA_FUSED=5184": ("mla_prep.cu", ["-DINNER=3072", "-DMLA_FUSED=5184", "-DK3G_MLA_BF16=1"]),
+    "k3_land_fused": ("glue_small.cu", []),
+    "sigmoid_mul": ("glue_small.cu", []),
+    "k3_span_state+HEADS=24": ("glue_small.cu", ["-DHEADS=24"]),
+    "k3_mla_v2": ("glue_small.cu", []),
     "k3_span_gather_v3+HEADS=24": ("kda.cu", ["-DHEADS=24"]),
     "k3_kda_out_gate_v3+HEADS=24": ("kda.cu", ["-DHEADS=24"]),
 }

@@ -461,6 +461,17 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rm
 }
 // ops land_add_attnres_rms_bf16_v2_nb{1..8} (modules k3_residual_nb, k3_residual_nb_stats): one entry per
 // candidate count in the reference; the count is a run-time argument here, the entries share one body.
+#ifdef K3G_NB_NO_STATS   /* module k3_residual_nb: ten parameters, no statistics hand-off */
+#define K3G_NB_ENTRY(K)                                                                                                          \
+  extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rms_nb##K(                                       \
+      const k3g_land_t* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix, const __nv_bfloat16* __restrict__ blocks, \
+      const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,                \
+      __nv_bfloat16* __restrict__ normed, int nb_in, int snapshot, int B) {                                                       \
+    if (nb_in != K) return;                                                                                                      \
+    land_add_attnres_rms_body<K3G_RES_VPT, K3G_LAND_IS_BF16>(partial, prefix, blocks, sw, gamma, prefix2, normed, K, snapshot, B, \
+                                                             K3G_RES_EPS);                                                       \
+  }
+#else                    /* module k3_residual_nb_stats: twelve parameters */
 #define K3G_NB_ENTRY(K)                                                                                                          \
   extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rms_nb##K(                                       \
       const k3g_land_t* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix, const __nv_bfloat16* __restrict__ blocks, \
@@ -470,6 +481,7 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add_attnres_rm
     land_add_attnres_rms_body<K3G_RES_VPT, K3G_LAND_IS_BF16>(partial, prefix, blocks, sw, gamma, prefix2, normed, K, snapshot, B, \
                                                              K3G_RES_EPS, stats, nb_stats);                                      \
   }
+#endif
 K3G_NB_ENTRY(1) K3G_NB_ENTRY(2) K3G_NB_ENTRY(3) K3G_NB_ENTRY(4) K3G_NB_ENTRY(5) K3G_NB_ENTRY(6) K3G_NB_ENTRY(7) K3G_NB_ENTRY(8)
 
 extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_land_add2(

@@ -61,7 +61,9 @@ class LayerGlue:
         self.fp8_big = torch.empty((T, H), dtype=torch.uint8, device=dev)
         self.fp8_small = torch.empty((B, H), dtype=torch.uint8, device=dev)
         self.qpart = torch.empty(2048, dtype=torch.float32, device=dev); self.qscale = torch.empty(4, dtype=torch.float32, device=dev)
-        self.shared_act = rnd(B, SHARED); self.shared_q = torch.empty((B, SHARED), dtype=torch.uint8, device=dev)
+        self.shared_partial = rnd(B, 2 * SHARED, std=2.0); self.shared_act = torch.empty((B, SHARED), dtype=bf, device=dev)
+        self.shared_q = torch.empty((B, SHARED), dtype=torch.uint8, device=dev)
+        self.gamma_lat = self.gamma[:LATENT].contiguous(); self.routed_latent_norm = torch.empty((B, LATENT), dtype=bf, device=dev)
         # attention block
         if kind == "kda":
             self.kda_partial = rnd(T, 4 * inner)
@@ -72,12 +74,18 @@ class LayerGlue:
             self.beta = torch.empty((self.heads, T), dtype=bf, device=dev); self.flow = torch.empty((T, 128), dtype=bf, device=dev)
             self.gamma_o = torch.ones(128, device=dev)
             self.gated = torch.empty((T, inner), dtype=bf, device=dev)
+            self.state_lines = torch.zeros(self.heads * 128 * 128 * 4 + 3 * 3 * inner * 2, dtype=torch.uint8, device=dev)
+            self.state_buf = torch.zeros(self.heads * 128 * 128, dtype=torch.float32, device=dev)
+            self.line_index = torch.zeros(T, dtype=torch.int32, device=dev); self.span_at = torch.zeros(1, dtype=torch.int32, device=dev)
         else:
             self.mla_partial = rnd(T, 2112 + inner)
             self.gq, self.gkv = self.gamma[:1536].contiguous(), self.gamma[:512].contiguous()
             self.slots = torch.arange(T, dtype=torch.int64, device=dev)
             self.slab = torch.zeros((T // 64) * 64 * 576, dtype=bf, device=dev)
             self.q_norm = torch.empty((T, 1536), dtype=bf, device=dev); self.mla_gate = torch.empty((T, inner), dtype=bf, device=dev)
+            self.block_table = torch.arange(T // 64, dtype=torch.int32, device=dev); self.lens = torch.tensor([T], dtype=torch.int32, device=dev)
+            self.latent_rows = torch.empty((T, 576), dtype=bf, device=dev)
+            self.fmha_out = rnd(T, inner); self.attn_gated = torch.empty((T, inner), dtype=bf, device=dev)
         # MoE
         self.logits = rndf(B, EXPERTS); self.bias = rndf(EXPERTS, std=0.1); self.rs = torch.ones(1, dtype=bf, device=dev)
         self.idx = torch.empty((B, TOPK), dtype=torch.int32, device=dev); self.wts = torch.empty((B, TOPK), dtype=torch.float32, device=dev)
@@ -113,11 +121,16 @@ class LayerGlue:
             c += [("span_gather (conv4 + SiLU, beta, flow)", lambda: call(
                       "k3g_span_gather", self.kda_partial, 4 * inner, self.cw, 0, self.win, self.wsm, self.span_q, self.span_k, self.span_v, self.beta,
                       self.flow, heads, 0, T, 0, s())),
+                  ("span_state_in + span_state_out (2 copies)", lambda: (
+                      call("k3g_span_state", self.state_lines, self.line_index, self.state_lines.numel(), self.span_at, self.state_buf, 0, s()),
+                      call("k3g_span_state", self.state_lines, self.line_index, self.state_lines.numel(), self.span_at, self.state_buf, 1, s()))),
                   ("span_out_gate", lambda: call("k3g_kda_out_gate", self.span_v, self.kda_partial, 4 * inner, 3 * inner, self.gamma_o, self.gated, None,
                                                  None, heads, 0, T, 1e-5, s()))]
         else:
             c += [("mla_prep (head + gate)", lambda: call("k3g_mla_prep", self.mla_partial, 1, self.gq, self.gkv, self.slots, self.slab, 0, 64 * 576,
-                                                          self.q_norm, self.mla_gate, T, inner, 1e-5, s()))]
+                                                          self.q_norm, self.mla_gate, T, inner, 1e-5, s())),
+                  ("latent_gather", lambda: call("k3g_latent_gather", self.slab, self.block_table, 64 * 576, self.lens, self.latent_rows, T, s())),
+                  ("mla_gate (sigmoid_mul)", lambda: call("k3g_sigmoid_mul", self.attn_gated, self.fmha_out, self.mla_gate, T, heads, 128, inner, 128, s()))]
         c += [("reduce_attn (arrive)", lambda: call("k3g_rs_arrive", fl, ft, un, 2, W, to, st, s())),
               ("reduce_attn (pull RS)", lambda: call("k3g_rs_pull", self.attn_part, self.attn_own, self.b_attn_part.table, B * H, 2 * (W - 1), r, W, un, s())),
               ("res_mlp (land + attnres + rms, stats)", lambda: call(
@@ -139,6 +152,8 @@ class LayerGlue:
               ("scatter_moe (arrive)", lambda: call("k3g_rs_arrive", fl, ft, un, 4, W, to, st, s())),
               ("scatter_moe (pull RS)", lambda: call("k3g_rs_pull", self.moe_partial, self.routed_latent, self.b_moe_partial.table, B * LATENT,
                                                      2 * (W - 1), r, W, un, s())),
+              ("shared_situ (SiTU landing + latent RMSNorm)", lambda: call("k3g_situ_rms", self.shared_partial, self.shared_act, self.routed_latent,
+                                                                           self.gamma_lat, self.routed_latent_norm, SHARED, B, LATENT, B, s())),
               ("shared_act_quant (fp8 tensor)", lambda: call("k3g_quant_fp8_tensor", self.shared_act, self.shared_q, self.qscale[2:], self.qpart, B * SHARED,
                                                              2048, s()))]
         return c

@@ -33,6 +33,8 @@ MODULES = {
     "k3_allgather4_v3": ("source/k3_allgather4_v3.cu", [], False),
     "k3_mla_prep_v2+INNER=3072+MLA_FUSED=5184": ("source/k3_mla_prep_v2.cu", ["-DINNER=3072", "-DMLA_FUSED=5184"], False),
     "k3_mla_prep_bf16+INNER=3072+MLA_FUSED=5184": ("source/k3_mla_prep_bf16.cu", ["-DINNER=3072", "-DMLA_FUSED=5184"], False),
+    "k3_land_fused": ("source/k3_land_fused.cu", [], False),
+    "sigmoid_mul": ("source/sigmoid_mul.cu", [], False),
     "k3_span_gather_v3+HEADS=24": ("source/k3_span_gather_v3.cu", ["-DHEADS=24"], False),
     "k3_kda_out_gate_v3+HEADS=24": ("source/k3_kda_out_gate_v3.cu", ["-DHEADS=24"], False),
 }

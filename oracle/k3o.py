@@ -271,5 +271,20 @@ def kda_out_gate(attn, gate, gate_stride, gate_off, gamma_o, heads, at, span, ro
     return gated, q, sf
 
 
+def situ_rms(sp, lat, gam, n, h):
+    B, L = sp.shape[0], lat.shape[0]
+    act = np.empty((B, n), np.uint16)
+    ln = np.empty((L, h), np.uint16)
+    lib().k3o_situ_rms(_p(sp), _p(act), _p(lat), _p(gam), _p(ln), I(n), I(B), I(h), I(L))
+    return act, ln
+
+
+def sigmoid_mul(attn, gate, heads, head_dim, gate_tstride, gate_hstride):
+    tokens = attn.shape[0]
+    out = np.empty((tokens, heads * head_dim), np.uint16)
+    lib().k3o_sigmoid_mul(_p(out), _p(attn), _p(gate), I(tokens), I(heads), I(head_dim), I(gate_tstride), I(gate_hstride))
+    return out
+
+
 def num_threads():
     return int(lib().k3o_num_threads())

@@ -705,6 +705,54 @@ K3O_API void k3o_kda_out_gate(const u16* attn, const u16* gate, long long gate_s
   }
 }
 
+// ------------------------------------------------------------------ remaining glue
+// kern_k3_situ_rms_bf16 (source/k3_land_fused.cu:123-202).  situ: (4 tanh(g/4) * sigmoid(g)) * 25 tanh(u/25)
+// with one bf16 landing (the device uses tanh.approx / ex2.approx: bf16 tolerance).  rms: per 16-byte vector
+// an fma chain over its 8 elements, butterfly over each group of 32 consecutive vectors, butterfly over the
+// 32 group slots (:76-92, :146-160), rs = rsqrt(sum / h + 1e-5), ln = bf16(x * rs) (x) gamma.
+K3O_API void k3o_situ_rms(const u16* sp, u16* act, const u16* lat, const u16* gam, u16* ln, int n, int B, int h, int L) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < B; ++row)
+    for (int i = 0; i < n; ++i) {
+      const double g = bf2f(sp[(size_t)row * 2 * n + i]), u = bf2f(sp[(size_t)row * 2 * n + n + i]);
+      const double a = 4.0 * std::tanh(g * 0.25), s = 1.0 / (1.0 + std::exp(-g)), c = 25.0 * std::tanh(u * 0.04);
+      act[(size_t)row * n + i] = f2bf((float)((a * s) * c));
+    }
+  const int nvec = h / 8;
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < L; ++row) {
+    const u16* x = lat + (size_t)row * h;
+    float slots[32];
+    for (int g = 0; g < 32; ++g) {
+      float lanes[32];
+      for (int l = 0; l < 32; ++l) {
+        const int v = 32 * g + l;
+        float p = 0.f;
+        if (v < nvec)
+          for (int k = 0; k < 8; ++k) { const float f = bf2f(x[8 * v + k]); p = std::fmaf(f, f, p); }
+        lanes[l] = p;
+      }
+      slots[g] = butterfly(lanes, 32);
+    }
+    const float rs = rsqrt_rn(butterfly(slots, 32) / (float)h + 1e-5f);
+    for (int i = 0; i < h; ++i) ln[(size_t)row * h + i] = bfmul(f2bf(bf2f(x[i]) * rs), gam[i]);
+  }
+}
+
+// kern_sigmoid_mul_bf16 (source/sigmoid_mul.cu:15-44): g = bf16(sigmoid(gate)), out = bf16(attn * g).
+K3O_API void k3o_sigmoid_mul(u16* out, const u16* attn, const u16* gate, int tokens, int heads, int head_dim, int gate_tstride,
+                             int gate_hstride) {
+  const int n = heads * head_dim;
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < tokens; ++t)
+    for (int j = 0; j < n; ++j) {
+      const int hh = j / head_dim, d = j % head_dim;
+      const double x = bf2f(gate[(size_t)t * gate_tstride + (size_t)hh * gate_hstride + d]);
+      const u16 g = f2bf((float)(1.0 / (1.0 + std::exp(-x))));
+      out[(size_t)t * n + j] = bfmul(attn[(size_t)t * n + j], g);
+    }
+}
+
 K3O_API int k3o_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -136,6 +136,18 @@ def main():
     add("kda_out_gate, 16384 rows",
         lambda: refcubin.run("k3_kda_out_gate_v3+HEADS=24", "kern_k3_kda_out_gate", (T, 3), 128, [oq, kp, gamma_o, gated, span_at, T]),
         lambda: k3g.call("k3g_kda_out_gate", oq, kp, 4 * inner, 3 * inner, gamma_o, gated, None, None, 24, 0, T, 1e-5, s), T * inner * 6)
+    fm, ag = rnd(T, inner), torch.empty((T, inner), dtype=bf, device=dev)
+    add("sigmoid_mul (mla gate), 16384x3072",
+        lambda: refcubin.run("sigmoid_mul", "kern_sigmoid_mul_bf16", (T, 2), 256, [ag, fm, oq, 24, 128, inner, 128]),
+        lambda: k3g.call("k3g_sigmoid_mul", ag, fm, oq, T, 24, 128, inner, 128, s), T * inner * 6)
+    del kp
+    SH, LAT = 6144, 3584
+    sp, lat, gl = rnd(B, 2 * SH), rnd(B, LAT), gamma[:LAT].contiguous()
+    act, ln = torch.empty((B, SH), dtype=bf, device=dev), torch.empty((B, LAT), dtype=bf, device=dev)
+    add("situ_rms (SiTU landing + latent RMSNorm), 4096 rows",
+        lambda: refcubin.run("k3_land_fused", "kern_k3_situ_rms_bf16", 3 * ((4 * B + 15) // 16), 512,
+                             [sp, act, lat, gl, ln, SH, B, LAT, B]),
+        lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, B, LAT, B, s), B * (SH * 6 + LAT * 4))
     if len(sys.argv) > 1:
         json.dump(rows, open(sys.argv[1], "w"), indent=1)
 

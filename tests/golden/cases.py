@@ -25,7 +25,7 @@ def _bf(g, shape, mean=0.0, std=1.0):
 
 def inputs(name):
     g = _g({"k1b_nb0": 1, "k1b_nb3": 2, "k1a_nb2": 3, "k1c": 4, "moe_quant": 5, "quant_pair": 6, "router": 7, "route": 8, "rs_pull": 9,
-            "mla_prep": 10, "span_gather": 11, "out_gate": 12, "push_add2": 13}[name])
+            "mla_prep": 10, "span_gather": 11, "out_gate": 12, "push_add2": 13, "situ_rms": 14, "sigmoid_mul": 15}[name])
     H = 7168
     if name in ("k1b_nb0", "k1b_nb3", "k1a_nb2"):
         B = 3
@@ -36,6 +36,10 @@ def inputs(name):
         return dict(blocks=_bf(g, (B, 8, H)), sw=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32),
                     sw_mlp=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32), gamma=_bf(g, (H,), 1.0, 0.02),
                     p1=_bf(g, (B, H), std=0.5), p2=_bf(g, (B, H), std=0.5), prefix2=_bf(g, (B, H)), partial=_bf(g, (B, H), std=0.5))
+    if name == "situ_rms":
+        return dict(sp=_bf(g, (6, 2 * 6144), std=3.0), lat=_bf(g, (6, 3584)), gam=_bf(g, (3584,), 1.0, 0.02))
+    if name == "sigmoid_mul":
+        return dict(attn=_bf(g, (9, 3072)), gate=_bf(g, (9, 3072), std=2.0))
     if name == "k1c":
         B = 3
         return dict(p1=g.standard_normal((B, H), dtype=np.float32), p2=g.standard_normal((B, H), dtype=np.float32), prefix2=_bf(g, (B, H)))
@@ -74,10 +78,11 @@ def inputs(name):
     raise KeyError(name)
 
 
-NAMES = ["push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
+NAMES = ["situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
 
 # outputs that must be bit-identical between the reference cubin and the CPU oracle
 EXACT = {
+    "situ_rms": [], "sigmoid_mul": [],
     "push_add2": ["hidden", "blocks", "res_mlp_prefix2"],
     "k1b_nb0": ["prefix2"], "k1b_nb3": ["prefix2"], "k1a_nb2": ["blocks"], "k1c": ["hidden"], "moe_quant": ["q", "sf"],
     "quant_pair": ["y", "scale"], "router": [], "route": ["blockcount", "blockoff", "cta_batch", "cta_limit", "num_non_exiting", "total_padded",
@@ -86,6 +91,7 @@ EXACT = {
 }
 # bf16 outputs compared at tolerance: name -> (max ulp, max fraction of differing elements)
 TOLERANT = {
+    "situ_rms": {"act": (2, 0.2), "ln": (1, 2e-3)}, "sigmoid_mul": {"out": (1, 5e-3)},
     "push_add2": {"normed_all": (4, 5e-3), "res_mlp_normed": (4, 5e-3)},   # mixed rows: a cancelling mix amplifies the 1e-7 softmax difference
     "k1b_nb0": {"normed": (1, 2e-3)}, "k1b_nb3": {"normed": (2, 5e-3)}, "k1a_nb2": {"normed": (2, 5e-3)},
     "mla_prep": {"q_norm": (1, 2e-3), "slab": (1, 2e-3)}, "span_gather": {"q": (1, 5e-3), "k": (1, 5e-3), "v": (1, 5e-3)},
@@ -95,6 +101,11 @@ TOLERANT = {
 
 def run_oracle(name, inp):
     """CPU oracle outputs as a dict of numpy arrays (eps and constants as the reference builds them)."""
+    if name == "situ_rms":
+        act, ln = k3o.situ_rms(inp["sp"], inp["lat"], inp["gam"], 6144, 3584)
+        return dict(act=act, ln=ln)
+    if name == "sigmoid_mul":
+        return dict(out=k3o.sigmoid_mul(inp["attn"], inp["gate"], 24, 128, 3072, 128))
     if name == "push_add2":
         # res_in (push, nb = 3, snapshot, two partials, rank 1 of 4) followed by res_mlp (nb = 4) fed with its statistics
         blocks = inp["blocks"].copy()

@@ -37,6 +37,19 @@ def run_reference(name, inp, dev):
     import torch
     bf = torch.bfloat16
     z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+    if name == "situ_rms":
+        B, n, h = inp["sp"].shape[0], 6144, 3584
+        act, ln = z((B, n), bf), z((B, h), bf)
+        refcubin.run("k3_land_fused", "kern_k3_situ_rms_bf16", 3 * ((4 * B + 15) // 16), 512,
+                     [_up(inp["sp"], dev), act, _up(inp["lat"], dev), _up(inp["gam"], dev), ln, n, B, h, B])
+        torch.cuda.synchronize()
+        return dict(act=_bits(act), ln=_bits(ln))
+    if name == "sigmoid_mul":
+        T = inp["attn"].shape[0]
+        out = z((T, 3072), bf)
+        refcubin.run("sigmoid_mul", "kern_sigmoid_mul_bf16", (T, 2), 256, [out, _up(inp["attn"], dev), _up(inp["gate"], dev), 24, 128, 3072, 128])
+        torch.cuda.synchronize()
+        return dict(out=_bits(out))
     if name == "push_add2":
         B, H = inp["prefix2"].shape
         blocks, hidden = _up(inp["blocks"], dev), z((B, H), bf)

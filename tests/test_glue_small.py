@@ -1,0 +1,77 @@
+"""Parity of the remaining per-layer glue kernels (SiTU landing + latent RMSNorm, MLA output gate,
+KDA state staging copy, latent cache gather) with the CPU oracle."""
+import numpy as np
+import pytest
+
+import k3o
+from util import bf16_bits, bf16_ulp_diff, normal_bf16, rng, to_dev, to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,L,n,h", [(1, 1, 6144, 3584), (5, 5, 6144, 3584), (37, 9, 6144, 3584), (9, 37, 256, 512), (6, 6, 1024, 8192), (0, 7, 64, 3584)])
+def test_situ_rms(k3g, dev, B, L, n, h):
+    import torch
+    g = rng(B * 100 + L + h)
+    sp = normal_bf16(g, (max(B, 1), 2 * n), std=3.0)[:B]
+    lat = normal_bf16(g, (L, h)); gam = normal_bf16(g, (h,), mean=1.0, std=0.02)
+    o_act, o_ln = k3o.situ_rms(np.ascontiguousarray(sp), lat, gam, n, h)
+    act = torch.zeros((B, n), dtype=torch.bfloat16, device=dev); ln = torch.zeros((L, h), dtype=torch.bfloat16, device=dev)
+    k3g.call("k3g_situ_rms", to_dev_bf16(np.ascontiguousarray(sp), dev) if B else ln, act if B else ln, to_dev_bf16(lat, dev), to_dev_bf16(gam, dev), ln,
+             n, B, h, L, k3g.current_stream())
+    torch.cuda.synchronize()
+    assert np.array_equal(bf16_bits(ln), o_ln)                    # IEEE-only: bit exact
+    if B:
+        d = bf16_ulp_diff(bf16_bits(act), o_act)                  # tanh.approx / ex2.approx on the device: bf16 tolerance
+        assert d.max() <= 2 and (d > 1).mean() < 1e-3
+        a, b = k3o.bf16_to_f32(bf16_bits(act)).astype(np.float64), k3o.bf16_to_f32(o_act).astype(np.float64)
+        assert np.all(np.abs(a - b) <= 1.6e-2 * np.abs(b) + 1e-30)
+
+
+@pytest.mark.parametrize("tokens,heads,hd", [(1, 24, 128), (33, 24, 128), (7, 16, 128), (5, 3, 64)])
+def test_sigmoid_mul(k3g, dev, tokens, heads, hd):
+    import torch
+    g = rng(tokens + heads)
+    n = heads * hd
+    attn = normal_bf16(g, (tokens, n))
+    tstride, hstride = heads * 2 * hd, 2 * hd                      # gate = second half of a per-head [q | gate] pair
+    fused = normal_bf16(g, (tokens, heads * 2 * hd), std=2.0)
+    gate_view = np.ascontiguousarray(fused.reshape(-1)[hd:])       # view starting at the first gate half
+    want = k3o.sigmoid_mul(attn, np.concatenate([gate_view, np.zeros(hd, np.uint16)]), heads, hd, tstride, hstride)
+    d_fused = to_dev_bf16(fused, dev)
+    out = torch.zeros((tokens, n), dtype=torch.bfloat16, device=dev)
+    k3g.call("k3g_sigmoid_mul", out, to_dev_bf16(attn, dev), d_fused.view(-1)[hd:], tokens, heads, hd, tstride, hstride, k3g.current_stream())
+    torch.cuda.synchronize()
+    d = bf16_ulp_diff(bf16_bits(out), want)
+    assert d.max() <= 1 and (d > 0).mean() < 5e-3
+
+
+def test_span_state_roundtrip_and_latent_gather(k3g, dev):
+    import torch
+    g = rng(3)
+    rec_floats = 24 * 128 * 128
+    line_bytes = rec_floats * 4 + 3 * 3 * 3072 * 2
+    lines = torch.from_numpy(g.integers(0, 256, 3 * line_bytes, dtype=np.uint8)).to(dev)
+    before = lines.clone()
+    line_index = torch.tensor([2, 0, 1], dtype=torch.int32, device=dev); span_at = torch.tensor([1], dtype=torch.int32, device=dev)   # row 1 -> line 0
+    buf = torch.zeros(rec_floats, dtype=torch.float32, device=dev)
+    s = k3g.current_stream()
+    k3g.call("k3g_span_state", lines, line_index, line_bytes, span_at, buf, 0, s)
+    torch.cuda.synchronize()
+    assert torch.equal(buf.view(torch.uint8), before[:rec_floats * 4]) and torch.equal(lines, before)
+    buf += 1.0
+    k3g.call("k3g_span_state", lines, line_index, line_bytes, span_at, buf, 1, s)
+    torch.cuda.synchronize()
+    assert torch.equal(lines[:rec_floats * 4], buf.view(torch.uint8)) and torch.equal(lines[rec_floats * 4:], before[rec_floats * 4:])
+    # latent gather: 3 pages of 64 rows in shuffled order, 150 cached rows, 200 output rows
+    page_stride = 64 * 576 * 2
+    slab = normal_bf16(g, (4 * page_stride,))
+    table = np.array([2, 0, 3, 1], np.int32); lens = np.array([150], np.int32)
+    out = torch.full((200, 576), 7.0, dtype=torch.bfloat16, device=dev)
+    k3g.call("k3g_latent_gather", to_dev_bf16(slab, dev), to_dev(table, dev), page_stride, to_dev(lens, dev), out, 200, s)
+    torch.cuda.synchronize()
+    want = np.zeros((200, 576), np.uint16)
+    for t in range(150):
+        o = table[t // 64] * page_stride + (t % 64) * 576
+        want[t] = slab[o:o + 576]
+    assert np.array_equal(bf16_bits(out), want)

@@ -1,0 +1,83 @@
+"""The manifest patcher: launches of kernels this library provides are repointed at its cubins, with
+entry names, parameter lists and argument mappings untouched; everything else is left alone."""
+import copy
+import json
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
+REF_MANIFEST = "/root/reference/manifests/k3-tp4-prefill-16k.json"
+
+
+@pytest.fixture(scope="module")
+def pm():
+    if not os.path.isdir(os.path.join(ROOT, "kern-k3_b200", "lib", "cubin")):
+        import build
+        build.build()
+    import patch_manifest
+    return patch_manifest
+
+
+def _mini():
+    return {
+        "modules": {"k3_router_argmax": {"source": "x", "sha256": "0"}, "k3_moe_prefill_v3+EP_STRIDED=1": {"source": "y", "sha256": "1"},
+                    "k3_rs_arrive_v2": {"source": "z", "sha256": "2"}, "gemm": {"source": "g", "sha256": "3"}},
+        "ops": {
+            "router_topk": {"params": ["in buffer<f32>"], "impl": {"launches": [
+                {"module": "k3_router_argmax", "entry": "kern_k3_router_topk", "block": [256, 1, 1], "grid": [{"ceil_div": ["tokens", 4]}, 1, 1]}]}},
+            "argmax": {"impl": {"launches": [{"module": "k3_router_argmax", "entry": "kern_k3_argmax_f32_partial", "block": [1024, 1, 1], "grid": [1, 64, 1]}]}},
+            "moe_quant": {"impl": {"launches": [{"module": "k3_moe_prefill_v3+EP_STRIDED=1", "entry": "kern_k3_moe_quant", "block": [256, 1, 1],
+                                                 "grid": [7, 1, 1], "args": [{"param": 0}, {"i32": 3584}]}]}},
+            "k3_allgather_push": {"impl": {"launches": [{"module": "k3_rs_arrive_v2", "entry": "kern_k3_rs_arrive1", "block": [32, 1, 1], "grid": [1, 1, 1],
+                                                         "args": [{"param": 0}, {"rank": "tp"}]}]}},
+            "gemm_bf16": {"impl": {"launches": [{"module": "gemm", "entry": "extern:cublas", "block": [1, 1, 1], "grid": [1, 1, 1]}]}},
+        },
+    }
+
+
+def test_patch_small_manifest(pm):
+    m = _mini()
+    before = copy.deepcopy(m)
+    s = pm.patch(m)
+    assert not s["missing"]
+    l = m["ops"]["router_topk"]["impl"]["launches"][0]
+    assert l["module"] == "b200/k3_router_argmax" and l["entry"] == "kern_k3_router_topk"
+    assert l["grid"] != before["ops"]["router_topk"]["impl"]["launches"][0]["grid"]           # better geometry applied
+    assert m["ops"]["argmax"]["impl"]["launches"][0]["module"] == "k3_router_argmax"          # not ours: untouched
+    assert "k3_router_argmax" in m["modules"]                                                 # still referenced by argmax
+    q = m["ops"]["moe_quant"]["impl"]["launches"][0]
+    assert q["module"] == "b200/k3_quant_fp8_pair_v2" and q["args"] == before["ops"]["moe_quant"]["impl"]["launches"][0]["args"]
+    assert "k3_moe_prefill_v3+EP_STRIDED=1" not in m["modules"]                               # no launch left on it
+    assert m["ops"]["k3_allgather_push"]["impl"]["launches"][0]["args"] == [{"param": 0}, {"rank": "tp"}]
+    assert m["ops"]["gemm_bf16"] == before["ops"]["gemm_bf16"]
+    sha = m["modules"]["b200/k3_router_argmax"]["sha256"]
+    assert len(sha) == 64 and sha == pm.sha256(os.path.join(pm.CUBIN_DIR, "k3_router_argmax.cubin"))
+    again = copy.deepcopy(m)
+    pm.patch(again)
+    assert again == m                                                                         # idempotent
+    keep = _mini()
+    pm.patch(keep, keep_grids=True)
+    assert keep["ops"]["router_topk"]["impl"]["launches"][0]["grid"] == before["ops"]["router_topk"]["impl"]["launches"][0]["grid"]
+
+
+@pytest.mark.skipif(not os.path.exists(REF_MANIFEST), reason="reference checkout not present")
+def test_patch_reference_default_manifest(pm):
+    m = json.load(open(REF_MANIFEST))
+    calls = m["programs"]["prefill"]["calls"]
+    s = pm.patch(m)
+    assert not s["missing"]
+    moved_ops = {op for op, _, _ in s["moved"]}
+    for op in ("attnres_rms_push_add2", "k3_reducescatter_bf16", "k3_allgather4_push", "k3_allgather_push", "quant_fp8_tensor", "router_topk",
+               "moe_quant", "moe_route_count", "moe_route_tables", "moe_route_scatter", "moe_finalize", "mla_prep", "span_gather_v2",
+               "kda_out_gate_v2", "k3_epoch_bump"):
+        assert op in moved_ops, op
+    assert any(op.startswith("land_add_attnres_rms_bf16_v2_nb") for op in moved_ops)
+    # share of the prefill program's calls that now run on this library's kernels
+    n = sum(1 for c in calls if c["op"] in moved_ops)
+    assert n > 0.5 * len(calls), (n, len(calls))
+    for _, entry, mod in s["moved"]:
+        blob = open(os.path.join(pm.CUBIN_DIR, mod[len("b200/"):] + ".cubin"), "rb").read()
+        assert entry.encode() + b"\0" in blob

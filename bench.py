@@ -224,6 +224,15 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     gq = torch.empty((T, inner), dtype=torch.uint8, device=dev); gsf = torch.empty((T, inner // 32), dtype=torch.uint8, device=dev)
     add("config4 kda_out_gate+mxfp8 16384x3072", lambda: k3g.call("k3g_kda_out_gate", oq, gate, inner, 0, gamma_o, None, gq, gsf, 24, 0, T, EPS, s),
         T * inner * (2 + 2 + 1) + T * inner // 32)
+    del gate, gq, gsf
+    fm, ag = rnd(T, inner), torch.empty((T, inner), dtype=torch.bfloat16, device=dev)
+    add("mla_gate sigmoid_mul 16384x3072", lambda: k3g.call("k3g_sigmoid_mul", ag, fm, oq, T, 24, 128, inner, 128, s), T * inner * 6)
+    SH, LAT, B = 6144, 3584, T // 4
+    sp, lat, gl = rnd(B, 2 * SH), rnd(B, LAT), gm[:LAT].contiguous()
+    act, ln = torch.empty((B, SH), dtype=torch.bfloat16, device=dev), torch.empty((B, LAT), dtype=torch.bfloat16, device=dev)
+    add("land_situ_rms 4096x(2x6144 -> 6144) + rms 4096x3584", lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, B, LAT, B, s), B * (SH * 6 + LAT * 4))
+    add("land_situ_rms SiTU part only", lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, B, LAT, 0, s), B * SH * 6)
+    add("land_situ_rms norm part only", lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, 0, LAT, B, s), B * LAT * 4)
     return out
 
 

@@ -210,6 +210,11 @@ int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_stride, 
  * RMSNorm ln [L, h] = bf16(lat * rs) (x) gam, in one launch.  n % 8 == 0, h % 8 == 0, h <= 8192. */
 int k3g_situ_rms(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* stream);
 
+/* Diagnostic: out[i] = bf16(SiTU(g[i], u[i])) for n bf16 pairs, with the kernel's formula (literal = 0) or the
+ * reference's formula written out operation for operation (literal = 1, source/k3_land_fused.cu:88).  The two
+ * must agree bit for bit on every input; the tests sweep all 65536 values of g and of u. */
+int k3g_situ_probe(const void* g, const void* u, void* out, long long n, int literal, void* stream);
+
 /* kern_sigmoid_mul_bf16, source/sigmoid_mul.cu:15 (op mla_gate): out = bf16(attn * bf16(sigmoid(gate))),
  * gate(t, h, d) = gate + t * gate_tstride + h * gate_hstride + d. */
 int k3g_sigmoid_mul(void* out, const void* attn, const void* gate, int tokens, int heads, int head_dim, int gate_tstride,

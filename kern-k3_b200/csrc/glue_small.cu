@@ -14,10 +14,11 @@
 // reference's order -- a per-vector fma chain over 8 elements, an xor-butterfly over each group of 32
 // consecutive vectors, then one butterfly over the (up to 32) group sums.
 //
-// Layout for B200: one launch, every block is a team of 128 threads; blocks with blockIdx.x % 3 == 0
-// normalise latent rows (4 per pass, all 4 x 4 vector loads of the team's threads issued up front),
-// the others run the SiTU stream (2 rows per pass), so the latency-bound norm hides under the
-// MUFU/HBM-bound activation exactly as in the reference's job split, with grid-stride passes.
+// Layout for B200: one launch of short 128-thread blocks, one in four of which normalises latent rows
+// (2 rows per item, all 8 vector loads of a thread issued up front) while the others run SiTU items (512
+// consecutive vectors of the flat activation, 8 loads per thread up front); 64 registers per thread keep 8
+// blocks resident per SM, so the latency-bound norm hides under the MUFU-bound activation as in the
+// reference's 1:2 job split.
 #include "k3g_device.cuh"
 #include "k3g_host.h"
 
@@ -25,34 +26,50 @@ using namespace k3g;
 
 namespace {
 
-__device__ __forceinline__ float tanh_approx(float x) {
+__device__ __forceinline__ float mufu_tanh(float x) {
   float r;
   asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-__device__ __forceinline__ float situ1(float g, float u) {
-  const float a = 4.0f * tanh_approx(g * 0.25f);
+// The reference's formula, operation for operation (source/k3_land_fused.cu:88-92).
+__device__ __forceinline__ float situ_reference_form(float g, float u) {
+  const float a = 4.0f * mufu_tanh(g * 0.25f);
   const float s = __frcp_rn(1.0f + __expf(-g));
-  const float c = 25.0f * tanh_approx(u * 0.04f);
+  const float c = 25.0f * mufu_tanh(u * 0.04f);
   return (a * s) * c;
 }
-__device__ __forceinline__ V8 situ8(const V8& g, const V8& u) {
+// The same function with fewer instructions; every step below is value-preserving:
+//  - __expf(-g) is ex2.approx(-g * log2 e); flushing a subnormal exponential to zero cannot change 1 + e;
+//  - x = 1 + e >= 1, where one Newton step on rcp.approx is the correctly rounded reciprocal as long as the
+//    result is a normal number (x <= 2^126); larger x (g < -87) takes the full-range reciprocal;
+//  - scaling by 4 is exact and commutes with rounding, so (4 t s) c = (t s)(4 c) and 4 (25 th) = 100 th.
+// tests/test_glue_small.py compares the two on every bf16 value of g and of u.
+__device__ __forceinline__ float situ_value(float g, float u) {
+  const float t = mufu_tanh(g * 0.25f);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(g, -1.4426950408889634f)));
+  const float x = 1.0f + e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  r = __fmaf_rn(r, __fmaf_rn(-x, r, 1.0f), r);
+  if (x > 0x1p126f) r = __frcp_rn(x);
+  const float c4 = 100.0f * mufu_tanh(u * 0.04f);
+  return (t * r) * c4;
+}
+__device__ __forceinline__ V8 situ_vec(const V8& g, const V8& u) {
   V8 o;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) o.w[j] = pack_bf2(situ1(bf_lo(g.w[j]), bf_lo(u.w[j])), situ1(bf_hi(g.w[j]), bf_hi(u.w[j])));
+  for (int j = 0; j < 4; ++j) o.w[j] = pack_bf2(situ_value(bf_lo(g.w[j]), bf_lo(u.w[j])), situ_value(bf_hi(g.w[j]), bf_hi(u.w[j])));
   return o;
 }
 
-constexpr int kRmsRows = 4;      // rows per norm pass (= the reference's RMS_R, so its grid maps one block to one pass)
-constexpr int kSituRows = 2;     // rows per SiTU pass
-constexpr int kMaxVpt = 8;       // vectors per thread of a 128-thread team: h <= 8192
+constexpr int kRmsRows = 2;      // rows per norm item
 
 // sums[r] = sum of squares of row r in the reference's order.  v[r][k] is vector (t + 128 k) of row r.
-template <int VPT>
-__device__ __forceinline__ void rms_rows(const V8 (&v)[kRmsRows][VPT], int nvec, float* sm, float* sums) {
+template <int ROWS, int VPT>
+__device__ __forceinline__ void rms_rows(const V8 (&v)[ROWS][VPT], int nvec, float* sm, float* sums) {
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 #pragma unroll
-  for (int r = 0; r < kRmsRows; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       float p = 0.f;
@@ -70,89 +87,153 @@ __device__ __forceinline__ void rms_rows(const V8 (&v)[kRmsRows][VPT], int nvec,
   }
   __syncthreads();
 #pragma unroll
-  for (int r = 0; r < kRmsRows; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const float x = lane < 4 * VPT ? sm[r * 32 + lane] : 0.f;   // groups past the row's end hold 0, like the reference's idle warps
     sums[r] = butterfly_sum<32>(x);
   }
   __syncthreads();
 }
 
-template <int VPT>
-__device__ __forceinline__ void rms_job(const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
-                                        __nv_bfloat16* __restrict__ ln, int h, int L, int pass, int npass_stride, float* sm) {
+template <int ROWS, int VPT>
+__device__ __forceinline__ void rms_item(const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
+                                         __nv_bfloat16* __restrict__ ln, int h, int L, int r0, float* sm) {
   const int t = threadIdx.x, nvec = h >> 3;
-  const int groups = (L + kRmsRows - 1) / kRmsRows;
-  for (int q = pass; q < groups; q += npass_stride) {
-    const int r0 = q * kRmsRows;
-    V8 v[kRmsRows][VPT];
+  V8 v[ROWS][VPT];
 #pragma unroll
-    for (int r = 0; r < kRmsRows; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        v[r][k] = V8{{0u, 0u, 0u, 0u}};
-        if (r0 + r < L && t + 128 * k < nvec) v[r][k] = ld_stream(lat + (size_t)(r0 + r) * h + (t + 128 * k) * 8);
-      }
+    for (int k = 0; k < VPT; ++k) {
+      v[r][k] = V8{{0u, 0u, 0u, 0u}};
+      if (r0 + r < L && t + 128 * k < nvec) v[r][k] = ld_stream(lat + (size_t)(r0 + r) * h + (t + 128 * k) * 8);
     }
-    float sums[kRmsRows];
-    rms_rows<VPT>(v, nvec, sm, sums);
+  }
+  float sums[ROWS];
+  rms_rows<ROWS, VPT>(v, nvec, sm, sums);
 #pragma unroll
-    for (int r = 0; r < kRmsRows; ++r) {
-      if (r0 + r >= L) continue;
-      const float rs = __frsqrt_rn(__fadd_rn(__fdiv_rn(sums[r], (float)h), 1e-5f));
+  for (int r = 0; r < ROWS; ++r) {
+    if (r0 + r >= L) continue;
+    const float rs = __frsqrt_rn(__fadd_rn(__fdiv_rn(sums[r], (float)h), 1e-5f));
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) {
-        if (t + 128 * k >= nvec) continue;
-        const V8 g = ld_keep(gam + (t + 128 * k) * 8);
-        V8 o;
+    for (int k = 0; k < VPT; ++k) {
+      if (t + 128 * k >= nvec) continue;
+      const V8 g = ld_keep(gam + (t + 128 * k) * 8);
+      V8 o;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(v[r][k].w[j]), rs), __fmul_rn(bf_hi(v[r][k].w[j]), rs)), g.w[j]);
-        st_stream(ln + (size_t)(r0 + r) * h + (t + 128 * k) * 8, o);
-      }
+      for (int j = 0; j < 4; ++j)
+        o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(v[r][k].w[j]), rs), __fmul_rn(bf_hi(v[r][k].w[j]), rs)), g.w[j]);
+      st_stream(ln + (size_t)(r0 + r) * h + (t + 128 * k) * 8, o);
     }
   }
 }
 
-__device__ __forceinline__ void situ_job(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act, int n, int B, int pass,
-                                         int npass_stride) {
-  const int nv = n >> 3;
-  const int groups = (B + kSituRows - 1) / kSituRows;
-  for (int j0 = pass; j0 < groups; j0 += npass_stride) {
+// Rows wider than 4 x 128 vectors (h > 4096, not a shape of the reference deployment): one row at a time,
+// vectors read once for the sum and again (from L2) for the output, so no vector stays in a register.
+__device__ __noinline__ void rms_row_wide(const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
+                                          __nv_bfloat16* __restrict__ ln, int h, int row, float* sm) {
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nvec = h >> 3;
+  const int vpt = (nvec + 127) >> 7;
+  const __nv_bfloat16* src = lat + (size_t)row * h;
+  for (int k = 0; k < vpt; ++k) {
+    float p = 0.f;
+    if (t + 128 * k < nvec) {
+      const V8 v = ld_plain(src + (t + 128 * k) * 8);
 #pragma unroll
-    for (int r = 0; r < kSituRows; ++r) {
-      const int row = kSituRows * j0 + r;
-      if (row >= B) break;
-      const __nv_bfloat16* grow = sp + (size_t)row * 2 * n;
-      __nv_bfloat16* orow = act + (size_t)row * n;
-      for (int v0 = threadIdx.x; v0 < nv; v0 += 2 * blockDim.x) {       // two vectors (four loads) in flight per thread
-        const int v1 = v0 + blockDim.x;
-        const V8 g0 = ld_stream(grow + v0 * 8), u0 = ld_stream(grow + n + v0 * 8);
-        V8 g1, u1;
-        if (v1 < nv) { g1 = ld_stream(grow + v1 * 8); u1 = ld_stream(grow + n + v1 * 8); }
-        st_stream(orow + v0 * 8, situ8(g0, u0));
-        if (v1 < nv) st_stream(orow + v1 * 8, situ8(g1, u1));
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf_lo(v.w[j]), hi = bf_hi(v.w[j]);
+        p = __fmaf_rn(lo, lo, p);
+        p = __fmaf_rn(hi, hi, p);
       }
     }
+    p = butterfly_sum<32>(p);
+    if (lane == 0) sm[warp + 4 * k] = p;
   }
+  __syncthreads();
+  const float sum = butterfly_sum<32>(lane < 4 * vpt ? sm[lane] : 0.f);
+  __syncthreads();
+  const float rs = __frsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)h), 1e-5f));
+  for (int k = 0; k < vpt; ++k) {
+    if (t + 128 * k >= nvec) continue;
+    const V8 v = ld_plain(src + (t + 128 * k) * 8), g = ld_keep(gam + (t + 128 * k) * 8);
+    V8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(v.w[j]), rs), __fmul_rn(bf_hi(v.w[j]), rs)), g.w[j]);
+    st_stream(ln + (size_t)row * h + (t + 128 * k) * 8, o);
+  }
+}
+
+// One SiTU item: kSituVec x 128 consecutive 16-byte vectors of the flat [B][n / 8] activation; every load
+// of the item is issued before the first store.
+#ifndef K3G_SITU_VEC
+#define K3G_SITU_VEC 4
+#endif
+constexpr int kSituVec = K3G_SITU_VEC;
+__device__ __forceinline__ void situ_item(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act, unsigned nv, unsigned total,
+                                          unsigned chunk) {
+  const unsigned base = chunk * (kSituVec * 128u) + threadIdx.x;
+  V8 g[kSituVec], u[kSituVec];
+  size_t off[kSituVec];
+#pragma unroll
+  for (int k = 0; k < kSituVec; ++k) {
+    const unsigned idx = base + 128u * k;
+    if (idx < total) {
+      const unsigned row = idx / nv, col = idx - row * nv;
+      const __nv_bfloat16* p = sp + ((size_t)row * 2 * nv + col) * 8;
+      g[k] = ld_stream(p);
+      u[k] = ld_stream(p + (size_t)nv * 8);
+      off[k] = (size_t)idx * 8;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kSituVec; ++k)
+    if (base + 128u * k < total) st_stream(act + off[k], situ_vec(g[k], u[k]));
 }
 
 }  // namespace
 
-// grid: any multiple of 3 blocks (the reference launches 3 * ceil(tokens / 16) blocks of 512 threads; a
-// team here is 128 threads, so a 512-thread block simply idles its upper warps' vector slots -- the
-// vector ownership t + 128 k only uses threadIdx.x < 128).  Requires n % 8 == 0, h % 8 == 0, h <= 8192.
+// Work items: ceil(L / 2) norm items (2 latent rows each) and ceil(B * n / 4096) SiTU items (512 vectors
+// each).  Blocks with blockIdx.x % K3G_SITU_MOD == 0 stride over the norm items, the others over the SiTU
+// items, so that the hardware block scheduler keeps both kinds resident on every SM and the latency-bound
+// norm hides under the MUFU-bound activation.  Any grid of at least K3G_SITU_MOD blocks and any block of at
+// least 128 threads is valid (the reference launches 3 * ceil(tokens / 16) blocks of 512): a block is one
+// team of 128 threads, further threads exit.  Requires n % 8 == 0, h % 8 == 0, h <= 8192, B * n / 8 < 2^31.
+#ifndef K3G_SITU_MOD
+#define K3G_SITU_MOD 5
+#endif
+#ifndef K3G_SITU_IPB
+#define K3G_SITU_IPB 1
+#endif
 extern "C" __global__ void __launch_bounds__(512) kern_k3_situ_rms_bf16(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
                                                                        const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
                                                                        __nv_bfloat16* __restrict__ ln, int n, int B, int h, int L) {
   __shared__ float sm[kRmsRows * 32];
-  const int q = blockIdx.x / 3, job = blockIdx.x - 3 * q, stride = gridDim.x / 3;
+  if (threadIdx.x >= 128) return;
+  const unsigned nv = (unsigned)n >> 3, total = (unsigned)B * nv;
+  const unsigned RG = (unsigned)(L + kRmsRows - 1) / kRmsRows, SC = (total + kSituVec * 128u - 1) / (kSituVec * 128u);
+  const unsigned q = blockIdx.x / K3G_SITU_MOD, job = blockIdx.x - q * K3G_SITU_MOD;
+  const unsigned norm_blocks = (gridDim.x + K3G_SITU_MOD - 1) / K3G_SITU_MOD;
   if (job == 0) {
-    if (threadIdx.x >= 128) return;                        // one 128-thread team per norm block
     const int vpt = ((h >> 3) + 127) >> 7;
-    if (vpt <= 4) rms_job<4>(lat, gam, ln, h, L, q, stride, sm);
-    else rms_job<kMaxVpt>(lat, gam, ln, h, L, q, stride, sm);
+    for (unsigned r = q; r < RG; r += norm_blocks) {
+      const int r0 = (int)r * kRmsRows;
+      if (vpt <= 4) {
+        rms_item<kRmsRows, 4>(lat, gam, ln, h, L, r0, sm);
+      } else {
+        for (int w = 0; w < kRmsRows && r0 + w < L; ++w) rms_row_wide(lat, gam, ln, h, r0 + w, sm);
+      }
+    }
   } else {
-    situ_job(sp, act, n, B, 2 * q + (job - 1), 2 * stride);
+    const unsigned situ_blocks = gridDim.x - norm_blocks;
+    for (unsigned c = blockIdx.x - q - 1; c < SC; c += situ_blocks) situ_item(sp, act, nv, total, c);
+  }
+}
+
+// Element-wise SiTU of n (g, u) pairs with the production formula (literal = 0) or the reference's literal
+// formula (literal = 1): lets a test prove that the two agree on every bf16 input.
+__global__ void __launch_bounds__(256) situ_probe_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+                                                         __nv_bfloat16* __restrict__ out, long long n, int literal) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gf = __bfloat162float(g[i]), uf = __bfloat162float(u[i]);
+    out[i] = __float2bfloat16_rn(literal ? situ_reference_form(gf, uf) : situ_value(gf, uf));
   }
 }
 
@@ -214,11 +295,25 @@ K3G_API int k3g_situ_rms(const void* sp, void* act, const void* lat, const void*
   K3G_REQUIRE_ALIGNED(sp); K3G_REQUIRE_ALIGNED(act); K3G_REQUIRE_ALIGNED(lat); K3G_REQUIRE_ALIGNED(gam); K3G_REQUIRE_ALIGNED(ln);
   K3G_REQUIRE(n > 0 && n % 8 == 0 && h > 0 && h % 8 == 0 && h <= 8192 && B >= 0 && L >= 0, K3G_ESHAPE);
   if (B == 0 && L == 0) return K3G_OK;
-  const int rg = (L + kRmsRows - 1) / kRmsRows, sg = (B + kSituRows - 1) / kSituRows;
-  int q = rg > (sg + 1) / 2 ? rg : (sg + 1) / 2;
-  if (q < 1) q = 1;
-  kern_k3_situ_rms_bf16<<<3 * q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)lat,
+  K3G_REQUIRE((long long)B * (n / 8) < (1ll << 31), K3G_ESHAPE);
+  // K3G_SITU_IPB items per block: short blocks, so the block scheduler balances the two kinds of work
+  const long long rg = (L + kRmsRows - 1) / kRmsRows, sc = ((long long)B * (n / 8) + kSituVec * 128 - 1) / (kSituVec * 128);
+  const long long nb = (rg + K3G_SITU_IPB - 1) / K3G_SITU_IPB, sb = (sc + K3G_SITU_IPB * (K3G_SITU_MOD - 1) - 1) / (K3G_SITU_IPB * (K3G_SITU_MOD - 1));
+  long long q = K3G_SITU_MOD * (nb > sb ? nb : sb);
+  if (q < K3G_SITU_MOD) q = K3G_SITU_MOD;
+  K3G_REQUIRE(q < (1ll << 31), K3G_ESHAPE);
+  kern_k3_situ_rms_bf16<<<(unsigned)q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)lat,
                                                               (const __nv_bfloat16*)gam, (__nv_bfloat16*)ln, n, B, h, L);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_situ_probe(const void* g, const void* u, void* out, long long n, int literal, void* stream) {
+  K3G_REQUIRE_PTR(g); K3G_REQUIRE_PTR(u); K3G_REQUIRE_PTR(out);
+  K3G_REQUIRE(n >= 0, K3G_ESHAPE);
+  if (n == 0) return K3G_OK;
+  const long long blocks = (n + 255) / 256;
+  situ_probe_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
+                                                                                              (__nv_bfloat16*)out, n, literal);
   return k3g_launch_status();
 }
 

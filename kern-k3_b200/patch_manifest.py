@@ -59,6 +59,7 @@ GRIDS = {
     "kern_k3_span_gather": ([128, 1, 1], [6, 4, {"ceil_div": ["tokens", 64]}]),                   # 64 rows per block
     "kern_k3_kda_out_gate": ([128, 1, 1], [{"ceil_div": ["tokens", 2]}, 3, 1]),                   # two rows per pass
     "kern_k3_mla_prep_head": ([128, 1, 1], [{"ceil_div": ["tokens", 4]}, 1, 1]),                  # one warp per row
+    "kern_k3_situ_rms_bf16": ([128, 1, 1], [{"mul": [{"ceil_div": ["tokens", 8]}, 5]}, 1, 1]),            # one item per 128-thread block, 1 norm : 4 SiTU
     "kern_k3_mla_prep_gate": ([256, 1, 1], [{"ceil_div": [{"mul": ["tokens", 384]}, 256]}, 1, 1]),  # 8 columns per thread, flat
 }
 

@@ -28,6 +28,28 @@ def test_situ_rms(k3g, dev, B, L, n, h):
         assert np.all(np.abs(a - b) <= 1.6e-2 * np.abs(b) + 1e-30)
 
 
+def test_situ_formula_equals_the_reference_form_on_every_bf16_input(k3g, dev):
+    """The kernel's SiTU uses fewer instructions than the reference's formula; the two must be the same
+    function.  Its domain is only 2^32 (g, u) pairs of bf16 values, so the whole domain is swept, 1024 values
+    of g against all 65536 values of u per pass: infinities, NaNs, subnormals and the g < -87 range where the
+    sigmoid's reciprocal is subnormal included.  NaN results only have to be NaN in both."""
+    import torch
+    bits = lambda lo, hi: (torch.arange(lo, hi, dtype=torch.int32, device=dev) << 16 >> 16).to(torch.int16)   # sign-extend 16 bits
+    u = bits(0, 65536).repeat(1024).view(torch.bfloat16)
+    o0 = torch.empty(u.numel(), dtype=torch.bfloat16, device=dev); o1 = torch.empty_like(o0)
+    s = k3g.current_stream()
+    for c in range(64):
+        g = bits(c * 1024, (c + 1) * 1024).repeat_interleave(65536).view(torch.bfloat16)
+        k3g.call("k3g_situ_probe", g, u, o0, u.numel(), 0, s)
+        k3g.call("k3g_situ_probe", g, u, o1, u.numel(), 1, s)
+        a, b = o0.view(torch.int16), o1.view(torch.int16)
+        bad = (a != b) & ~(torch.isnan(o0) & torch.isnan(o1))
+        if bool(bad.any()):
+            i = int(torch.nonzero(bad)[0])
+            raise AssertionError("g=%#06x u=%#06x kernel=%#06x reference form=%#06x (%d pairs differ in this pass)" % (
+                int(g.view(torch.int16)[i]) & 0xffff, int(u.view(torch.int16)[i]) & 0xffff, int(a[i]) & 0xffff, int(b[i]) & 0xffff, int(bad.sum())))
+
+
 @pytest.mark.parametrize("tokens,heads,hd", [(1, 24, 128), (33, 24, 128), (7, 16, 128), (5, 3, 64)])
 def test_sigmoid_mul(k3g, dev, tokens, heads, hd):
     import torch

@@ -231,6 +231,11 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     sp, lat, gl = rnd(B, 2 * SH), rnd(B, LAT), gm[:LAT].contiguous()
     act, ln = torch.empty((B, SH), dtype=torch.bfloat16, device=dev), torch.empty((B, LAT), dtype=torch.bfloat16, device=dev)
     add("land_situ_rms 4096x(2x6144 -> 6144) + rms 4096x3584", lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, B, LAT, B, s), B * (SH * 6 + LAT * 4))
+    del sp, act
+    pf = torch.randn((B, 2 * 33792), generator=g, device=dev); act33 = torch.empty((B, 33792), dtype=torch.bfloat16, device=dev)
+    add("land_situ f32 4096x(2x33792 -> 33792) (layer 0 dense MLP)", lambda: k3g.call("k3g_land_situ", pf, act33, 33792, B, s), B * 33792 * 10)
+    del pf, act33
+    sp = rnd(B, 2 * SH); act = torch.empty((B, SH), dtype=torch.bfloat16, device=dev)
     add("land_situ_rms SiTU part only", lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, B, LAT, 0, s), B * SH * 6)
     add("land_situ_rms norm part only", lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, 0, LAT, B, s), B * LAT * 4)
     return out

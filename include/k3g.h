@@ -61,7 +61,9 @@ int k3g_land_add_attnres_rms_stats(const void* partial, int partial_is_bf16, con
  * (hidden = bf16(prefix2 + p1 (+ p2))), optional snapshot, attention-residual mix, RMSNorm, and the normed
  * row pushed into this rank's slice of every rank's normed_all [nranks * B, H] (dst_peer = peer table of
  * normed_all).  stats (may be null) receives (sum x^2, sum x * sw_mlp) per snapshot candidate.  The
- * all-gather's barrier is a separate k3g_rs_arrive. */
+ * all-gather's barrier is a separate k3g_rs_arrive.  p1 == NULL selects the first layer's form
+ * (kern_k3_attnres_rms_push of source/k3_residual_push_v3.cu:328, op attnres_rms_push_first_v3): the row
+ * is prefix2 itself, nothing is added and hidden is not written. */
 int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
                          int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
                          const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream);
@@ -203,12 +205,45 @@ int k3g_span_gather(const void* partial, long long row_stride, const void* cw, i
 int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_stride, long long gate_off, const void* gamma_o,
                      void* gated, void* q, void* sf, int heads, int at, int span, float eps, void* stream);
 
+/* kern_k3_argmax_f32_partial + kern_k3_argmax_f32_final, source/k3_router_argmax.cu:186,225 (op argmax_f32_one):
+ * out [B] i64 = index of the largest of n f32 logits per row, ties to the smallest index; pmax / pidx [B, parts]
+ * are the caller's scratch for the two stages. */
+int k3g_argmax_f32(const void* logits, void* pmax, void* pidx, void* out, int B, int n, int parts, void* stream);
+
+/* ---- once-per-prefill helpers (byte movement) ---------------------------------------------------------- */
+
+/* kern_k3_rank_rows, source/k3_prefill.cu:28 (op rank_rows): dst[j] = src[min(rank * own + j, rows - 1)], j < own. */
+int k3g_rank_rows(void* dst, const void* src, int rank, int own, int row_bytes, int rows, void* stream);
+/* kern_k3_zero_rows, source/k3_prefill.cu:42 (op zero_rows): rows [from, to) of buf zeroed. */
+int k3g_zero_rows(void* buf, int row_bytes, int from, int to, void* stream);
+/* kern_k3_fmha_lens, source/k3_prefill.cu:49 (op fmha_lens): lens[8] = {kv, 0, 0, T, 0, kv, 0, 0}, kv = seq_lens[0]. */
+int k3g_fmha_lens(const void* seq_lens, void* lens, int T, void* stream);
+/* kern_embedding_i64_bf16, source/embedding.cu:6 (op embedding): out[r] = table[ids[r]], rows of `hidden` bf16. */
+int k3g_embedding(const void* ids, const void* table, void* out, int tokens, int hidden, void* stream);
+/* kern_copy_rows_bf16, source/copy_rows.cu:23: dst[r, :width] = src[r, :width], strides in elements. */
+int k3g_copy_rows(void* dst, const void* src, int dst_stride, int src_stride, int width, int rows, void* stream);
+/* kern_last_row_bf16, source/copy_rows.cu:32 (op last_row): dst[0, :width] = src[rows - 1, :width]. */
+int k3g_last_row(void* dst, const void* src, int src_stride, int width, int rows, void* stream);
+/* kern_own_rows, source/copy_rows.cu:39: dst[j] = src[min(blocks[rank] + j, rows - 1)], j < own. */
+int k3g_own_rows(void* dst, const void* src, const void* blocks, int rank, int own, int row_bytes, int rows, void* stream);
+
 /* ---- remaining per-layer glue --------------------------------------------------------------------- */
 
 /* kern_k3_situ_rms_bf16, source/k3_land_fused.cu:123 (op land_situ_rms): shared-expert SiTU landing
  * act [B, n] = bf16((4 tanh(g/4) sigmoid(g)) * 25 tanh(u/25)) from sp [B, 2n] = g | u, and the MoE latent
  * RMSNorm ln [L, h] = bf16(lat * rs) (x) gam, in one launch.  n % 8 == 0, h % 8 == 0, h <= 8192. */
 int k3g_situ_rms(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* stream);
+
+/* kern_k3_land_situ, source/k3_land.cu:211 (op land_situ_n33792): act [B, n] = bf16(SiTU(bf16(g), bf16(u))) from
+ * the f32 partial p [B, 2n] = g | u (both operands land to bf16 before the activation). */
+int k3g_land_situ(const void* p, void* act, int n, int B, void* stream);
+
+/* kern_k3_land, source/k3_land.cu:166: o [B, n] = bf16(p[b * ldc + off + i]). */
+int k3g_land(const void* p, void* o, int n, int off, int ldc, int B, void* stream);
+
+/* kern_k3_rms, source/k3_land.cu:107: o [B, h] = bf16(x * rs) (x) gamma, rs = rsqrt(mean(x^2) + 1e-5); the sum in
+ * the order of the reference's 1024-thread block.  h % 8 == 0, h <= 8192. */
+int k3g_rms(const void* x, const void* gamma, void* o, int h, int B, void* stream);
 
 /* Diagnostic: out[i] = bf16(SiTU(g[i], u[i])) for n bf16 pairs, with the kernel's formula (literal = 0) or the
  * reference's formula written out operation for operation (literal = 1, source/k3_land_fused.cu:88).  The two

@@ -24,7 +24,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr"]
 
 SOURCES = ["resnorm.cu", "quant.cu", "router.cu", "moe_route.cu", "collectives.cu", "mla_prep.cu", "kda.cu",
-           "peer.cu", "quant_noalloc.cu", "glue_small.cu"]
+           "peer.cu", "quant_noalloc.cu", "glue_small.cu", "prefill_misc.cu"]
 
 # reference module name -> (source, defines).  Names follow kernels.toml of the reference.
 CUBINS = {
@@ -44,7 +44,12 @@ CUBINS = {
     "k3_reducescatter_pull_nr4": ("collectives.cu", ["-DK3G_NR=4", "-DK3G_ORDER=6"]),
     "k3_mla_prep_v2+INNER=3072+MLA_FUSED=5184": ("mla_prep.cu", ["-DINNER=3072", "-DMLA_FUSED=5184"]),
     "k3_mla_prep_bf16+INNER=3072+MLA_FUSED=5184": ("mla_prep.cu", ["-DINNER=3072", "-DMLA_FUSED=5184", "-DK3G_MLA_BF16=1"]),
+    "k3_residual_push_v3": ("resnorm.cu", ["-DLAND_BF16=1", "-DK3G_PUSH_V3=1"]),
     "k3_land_fused": ("glue_small.cu", []),
+    "k3_land": ("glue_small.cu", []),
+    "k3_prefill": ("prefill_misc.cu", []),
+    "embedding": ("prefill_misc.cu", []),
+    "copy_rows": ("prefill_misc.cu", []),
     "sigmoid_mul": ("glue_small.cu", []),
     "k3_span_state+HEADS=24": ("glue_small.cu", ["-DHEADS=24"]),
     "k3_mla_v2": ("glue_small.cu", []),

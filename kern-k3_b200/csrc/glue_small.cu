@@ -6,6 +6,9 @@
 //   kern_sigmoid_mul_bf16   source/sigmoid_mul.cu:15-44        (op mla_gate)
 //   kern_k3_span_state      source/k3_span_state.cu:19-29      (ops span_state_load / span_state_store)
 //   kern_k3_latent_gather   source/k3_mla_v2.cu:22-33          (op latent_gather)
+//   kern_k3_land_situ       source/k3_land.cu:211-237          (op land_situ_n33792: SiTU on an f32 partial)
+//   kern_k3_land            source/k3_land.cu:166-188          (f32 -> bf16 landing of a column band)
+//   kern_k3_rms             source/k3_land.cu:107-160          (stand-alone latent RMSNorm)
 //
 // SiTU: act = bf16((4 tanh(g/4) * sigmoid(g)) * 25 tanh(u/25)), g = sp[row, i], u = sp[row, n + i].
 // The activation uses the same hardware approximations as the reference (tanh.approx, ex2.approx in
@@ -227,6 +230,98 @@ extern "C" __global__ void __launch_bounds__(512) kern_k3_situ_rms_bf16(const __
   }
 }
 
+// ---- f32 landings (module k3_land) -----------------------------------------------------------------
+// row / column of flat index i over rows of `width` items: 32-bit division whenever the index fits
+__device__ __forceinline__ void split_index(long long i, int width, long long& row, int& col) {
+  if (i < (1ll << 32)) {
+    const unsigned r = (unsigned)i / (unsigned)width;
+    row = r; col = (int)((unsigned)i - r * (unsigned)width);
+  } else {
+    row = i / width; col = (int)(i - row * width);
+  }
+}
+
+__device__ __forceinline__ float land_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// act[b, i] = bf16(SiTU(bf16(p[b, i]), bf16(p[b, n + i]))): both operands land to bf16 before the activation.
+// Flat over the B * n / 4 groups of four elements, any 1-D or 2-D grid (the reference launches (B, ceil(n / 1024))
+// blocks of 1024); n % 4 != 0 takes the element-wise path.
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_land_situ(const float* __restrict__ p, __nv_bfloat16* __restrict__ act, int n, int B) {
+  const long long nthreads = (long long)gridDim.x * gridDim.y * blockDim.x;
+  const long long tid = ((long long)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+  if ((n & 3) == 0) {
+    const int nq = n >> 2;
+    const long long items = (long long)B * nq;
+    for (long long i0 = tid; i0 < items; i0 += 2 * nthreads) {       // two groups (four 16-byte loads) in flight per thread
+      const long long i1 = i0 + nthreads;
+      long long r0, r1;
+      int c0, c1;
+      split_index(i0, nq, r0, c0);
+      split_index(i1, nq, r1, c1);
+      const float4 g0 = __ldcs(reinterpret_cast<const float4*>(p + r0 * 2 * n) + c0), u0 = __ldcs(reinterpret_cast<const float4*>(p + r0 * 2 * n + n) + c0);
+      float4 g1 = g0, u1 = u0;
+      if (i1 < items) { g1 = __ldcs(reinterpret_cast<const float4*>(p + r1 * 2 * n) + c1); u1 = __ldcs(reinterpret_cast<const float4*>(p + r1 * 2 * n + n) + c1); }
+      st_stream8(act + r0 * n + 4 * c0, pack_bf2(situ_value(land_bf16(g0.x), land_bf16(u0.x)), situ_value(land_bf16(g0.y), land_bf16(u0.y))),
+                 pack_bf2(situ_value(land_bf16(g0.z), land_bf16(u0.z)), situ_value(land_bf16(g0.w), land_bf16(u0.w))));
+      if (i1 < items)
+        st_stream8(act + r1 * n + 4 * c1, pack_bf2(situ_value(land_bf16(g1.x), land_bf16(u1.x)), situ_value(land_bf16(g1.y), land_bf16(u1.y))),
+                   pack_bf2(situ_value(land_bf16(g1.z), land_bf16(u1.z)), situ_value(land_bf16(g1.w), land_bf16(u1.w))));
+    }
+  } else {
+    const long long items = (long long)B * n;
+    for (long long i = tid; i < items; i += nthreads) {
+      long long r;
+      int c;
+      split_index(i, n, r, c);
+      act[i] = __float2bfloat16_rn(situ_value(land_bf16(p[r * 2 * n + c]), land_bf16(p[r * 2 * n + n + c])));
+    }
+  }
+}
+
+// o[b, i] = bf16(p[b * ldc + off + i]), i < n.
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_land(const float* __restrict__ p, __nv_bfloat16* __restrict__ o, int n, int off, int ldc, int B) {
+  const long long nthreads = (long long)gridDim.x * gridDim.y * blockDim.x;
+  const long long tid = ((long long)blockIdx.y * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+  if (((n | off | ldc) & 3) == 0) {
+    const int nq = n >> 2;
+    const long long items = (long long)B * nq;
+    for (long long i = tid; i < items; i += nthreads) {
+      long long r;
+      int c;
+      split_index(i, nq, r, c);
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(p + r * ldc + off) + c);
+      st_stream8(o + r * n + 4 * c, pack_bf2(v.x, v.y), pack_bf2(v.z, v.w));
+    }
+  } else {
+    const long long items = (long long)B * n;
+    for (long long i = tid; i < items; i += nthreads) {
+      long long r;
+      int c;
+      split_index(i, n, r, c);
+      o[i] = __float2bfloat16_rn(p[r * ldc + off + c]);
+    }
+  }
+}
+
+// o [B, h] = bf16(x * rs) (x) gamma, rs = rsqrt_rn(sum x^2 / h + 1e-5): the norm items of kern_k3_situ_rms_bf16 alone.
+// The sum's order is the one a 1024-thread block of the reference produces for h <= 8192 (one vector per
+// thread): warp w sums vectors 32 w .. 32 w + 31 by butterfly, warp 0 sums the warp totals.
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_rms(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                                                              __nv_bfloat16* __restrict__ o, int h, int B) {
+  __shared__ float sm[kRmsRows * 32];
+  if (threadIdx.x >= 128) return;
+  const int vpt = ((h >> 3) + 127) >> 7;
+  const int groups = (B + kRmsRows - 1) / kRmsRows;
+  for (int q = blockIdx.x; q < groups; q += gridDim.x) {
+    const int r0 = q * kRmsRows;
+    if (vpt <= 4) {
+      rms_item<kRmsRows, 4>(x, gamma, o, h, B, r0, sm);
+    } else {
+      for (int w = 0; w < kRmsRows && r0 + w < B; ++w) rms_row_wide(x, gamma, o, h, r0 + w, sm);
+    }
+  }
+}
+
 // Element-wise SiTU of n (g, u) pairs with the production formula (literal = 0) or the reference's literal
 // formula (literal = 1): lets a test prove that the two agree on every bf16 input.
 __global__ void __launch_bounds__(256) situ_probe_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
@@ -304,6 +399,40 @@ K3G_API int k3g_situ_rms(const void* sp, void* act, const void* lat, const void*
   K3G_REQUIRE(q < (1ll << 31), K3G_ESHAPE);
   kern_k3_situ_rms_bf16<<<(unsigned)q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)lat,
                                                               (const __nv_bfloat16*)gam, (__nv_bfloat16*)ln, n, B, h, L);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_land_situ(const void* p, void* act, int n, int B, void* stream) {
+  K3G_REQUIRE_PTR(p); K3G_REQUIRE_PTR(act);
+  K3G_REQUIRE_ALIGNED(p); K3G_REQUIRE_ALIGNED(act);
+  K3G_REQUIRE(n > 0 && B >= 0, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  const long long items = (n & 3) ? (long long)B * n : (long long)B * (n >> 2);
+  long long blocks = (items + 511) / 512;                 // 256 threads, two groups each
+  if (blocks > (1ll << 30)) blocks = 1ll << 30;
+  kern_k3_land_situ<<<(unsigned)blocks, 256, 0, k3g_stream(stream)>>>((const float*)p, (__nv_bfloat16*)act, n, B);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_land(const void* p, void* o, int n, int off, int ldc, int B, void* stream) {
+  K3G_REQUIRE_PTR(p); K3G_REQUIRE_PTR(o);
+  K3G_REQUIRE_ALIGNED(p); K3G_REQUIRE_ALIGNED(o);
+  K3G_REQUIRE(n > 0 && off >= 0 && ldc >= off + n && B >= 0, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  const long long items = ((n | off | ldc) & 3) ? (long long)B * n : (long long)B * (n >> 2);
+  long long blocks = (items + 255) / 256;
+  if (blocks > (1ll << 30)) blocks = 1ll << 30;
+  kern_k3_land<<<(unsigned)blocks, 256, 0, k3g_stream(stream)>>>((const float*)p, (__nv_bfloat16*)o, n, off, ldc, B);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_rms(const void* x, const void* gamma, void* o, int h, int B, void* stream) {
+  K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(o);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(o);
+  K3G_REQUIRE(h > 0 && h % 8 == 0 && h <= 8192 && B >= 0, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  kern_k3_rms<<<(unsigned)((B + kRmsRows - 1) / kRmsRows), 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma,
+                                                                                        (__nv_bfloat16*)o, h, B);
   return k3g_launch_status();
 }
 

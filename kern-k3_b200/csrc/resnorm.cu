@@ -298,7 +298,9 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
 // (the K1c expression, f32 adds in that order, one rounding), optional snapshot, attention-residual
 // mix with the statistics hand-off, RMSNorm, and the normed row stored to this rank's slice of every
 // rank's normed_all (own copy write-back, peer copies streaming).  The barrier is a separate launch.
-template <int VPT>
+// ADD = false is the first layer's form (source/k3_residual_push_v3.cu:328-400): the row comes from `prefix2`
+// as it is, nothing is added and no hidden row is stored.
+template <int VPT, bool ADD = true>
 __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
                                                       const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ normed_all,
                                                       const unsigned long long* __restrict__ dst_peer, int nb, int snapshot, int B, int rank,
@@ -318,7 +320,10 @@ __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict_
   for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
     const size_t base = (size_t)b * H;
     V8 x[VPT];
-    {
+    if constexpr (!ADD) {
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) x[v] = ld_stream(prefix2 + base + (t + v * kTeam) * 8);
+    } else {
       V8 a[VPT], c[VPT];
 #pragma unroll
       for (int v = 0; v < VPT; ++v) a[v] = ld_stream(prefix2 + base + (t + v * kTeam) * 8);
@@ -434,6 +439,16 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms(
   attnres_rms_body<K3G_RES_VPT>(prefix, blocks, sw, gamma, normed, nb, snapshot, B, K3G_RES_EPS);
 }
 
+#ifdef K3G_PUSH_V3
+// op attnres_rms_push_first_v3 (module k3_residual_push_v3): 11 kernel parameters, reference order.
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms_push(
+    const __nv_bfloat16* __restrict__ prefix, __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
+    const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ normed_all, const unsigned long long* __restrict__ dst_peer, int nb,
+    int snapshot, int B, int rank, int nranks) {
+  attnres_rms_push_body<K3G_RES_VPT, false>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, nullptr, nullptr, nullptr,
+                                            nullptr, prefix, nullptr, 0, K3G_RES_EPS);
+}
+#else
 // op attnres_rms_push_add2 (module k3_residual_push_add2): 17 kernel parameters, reference order.
 extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms_push(
     __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma,
@@ -443,6 +458,7 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms_push(
   attnres_rms_push_body<K3G_RES_VPT>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2,
                                      hidden, two, K3G_RES_EPS);
 }
+#endif
 
 #if defined(K3G_CUBIN_ONLY)
 // one landing dtype per module, as in the reference (-DLAND_BF16 selects bf16)
@@ -504,13 +520,13 @@ __global__ void __launch_bounds__(128, 4) land_add_attnres_rms_kernel(const void
                                                                      const float* stats, int nb_stats) {
   land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps, stats, nb_stats);
 }
-template <int VPT>
+template <int VPT, bool ADD>
 __global__ void __launch_bounds__(128, 4) attnres_rms_push_kernel(__nv_bfloat16* blocks, const float* sw, const __nv_bfloat16* gamma,
                                                                  __nv_bfloat16* normed_all, const unsigned long long* dst_peer, int nb,
                                                                  int snapshot, int B, int rank, int nranks, const float* sw_mlp, float* stats,
                                                                  const __nv_bfloat16* p1, const __nv_bfloat16* p2, const __nv_bfloat16* prefix2,
                                                                  __nv_bfloat16* hidden, int two, float eps) {
-  attnres_rms_push_body<VPT>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two, eps);
+  attnres_rms_push_body<VPT, ADD>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two, eps);
 }
 template <int VPT, bool LB>
 __global__ void __launch_bounds__(128, 4) land_add2_kernel(const void* p1, const void* p2, const __nv_bfloat16* prefix2,
@@ -614,9 +630,9 @@ K3G_API int k3g_land_add_attnres_rms_stats(const void* partial, int partial_is_b
 K3G_API int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
                                  int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
                                  const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream) {
-  K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(normed_all); K3G_REQUIRE_PTR(dst_peer); K3G_REQUIRE_PTR(p1); K3G_REQUIRE_PTR(prefix2);
-  K3G_REQUIRE_PTR(hidden);
-  if (two) K3G_REQUIRE_PTR(p2);
+  K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(normed_all); K3G_REQUIRE_PTR(dst_peer); K3G_REQUIRE_PTR(prefix2);
+  if (p1) K3G_REQUIRE_PTR(hidden);
+  if (two) { K3G_REQUIRE_PTR(p1); K3G_REQUIRE_PTR(p2); }
   K3G_REQUIRE(nb >= 0 && nb <= kNbMax, K3G_ERANGE);
   if (nb > 0 || snapshot) K3G_REQUIRE_PTR(blocks);
   if (nb > 0) K3G_REQUIRE_PTR(sw);
@@ -626,10 +642,16 @@ K3G_API int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma
   K3G_REQUIRE_ALIGNED(blocks); K3G_REQUIRE_ALIGNED(sw); K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(normed_all); K3G_REQUIRE_ALIGNED(sw_mlp);
   K3G_REQUIRE_ALIGNED(p1); K3G_REQUIRE_ALIGNED(p2); K3G_REQUIRE_ALIGNED(prefix2); K3G_REQUIRE_ALIGNED(hidden);
   if (B == 0) return K3G_OK;
-  K3G_DISPATCH_VPT(H, (attnres_rms_push_kernel<VPT><<<B, kTeam, 0, k3g_stream(stream)>>>(
-      (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed_all, (const unsigned long long*)dst_peer, nb,
-      snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, (const __nv_bfloat16*)p1, (const __nv_bfloat16*)p2,
-      (const __nv_bfloat16*)prefix2, (__nv_bfloat16*)hidden, two, eps)));
+  if (p1) {
+    K3G_DISPATCH_VPT(H, (attnres_rms_push_kernel<VPT, true><<<B, kTeam, 0, k3g_stream(stream)>>>(
+        (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed_all, (const unsigned long long*)dst_peer, nb,
+        snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, (const __nv_bfloat16*)p1, (const __nv_bfloat16*)p2,
+        (const __nv_bfloat16*)prefix2, (__nv_bfloat16*)hidden, two, eps)));
+  } else {                                               // first layer: the row is prefix2 itself
+    K3G_DISPATCH_VPT(H, (attnres_rms_push_kernel<VPT, false><<<B, kTeam, 0, k3g_stream(stream)>>>(
+        (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed_all, (const unsigned long long*)dst_peer, nb,
+        snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, nullptr, nullptr, (const __nv_bfloat16*)prefix2, nullptr, 0, eps)));
+  }
   return k3g_launch_status();
 }
 

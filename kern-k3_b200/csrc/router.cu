@@ -112,6 +112,88 @@ extern "C" __global__ void __launch_bounds__(256) kern_k3_router_topk(const floa
   router_rows<16>(S, bias, rs, idx, wts, B);
 }
 
+// ---- f32 argmax over a logits row, two stages (ops argmax_f32_one / argmax_f32) --------------------
+// Replaces kern_k3_argmax_f32_partial / kern_k3_argmax_f32_final (source/k3_router_argmax.cu:186-241):
+// largest value under the monotone bit order of ord_f32, ties to the smallest index; stage 1 reduces
+// gridDim.y contiguous chunks of the row to (pmax, pidx), an empty chunk giving (-inf, 0x7fffffff);
+// stage 2 applies the same rule to the partials (0 when there is none).  A candidate is the pair
+// (ord, index); within a thread indices only grow, so a strict compare keeps the smallest; across lanes
+// and warps one REDUX.MAX on the order and one REDUX.MIN on the index of whoever matched.
+namespace {
+constexpr int kNoIndex = 0x7fffffff;
+
+// Block-wide (ord, idx) reduction; every thread returns the winner.  ord == 0 means "no candidate"
+// (ord_f32 never returns 0 for a non-NaN float other than -NaN patterns, which order lowest anyway).
+__device__ __forceinline__ void block_argmax(unsigned& o, int& i, unsigned* s_ord, int* s_idx) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  unsigned m = __reduce_max_sync(0xffffffffu, o);
+  int w = __reduce_min_sync(0xffffffffu, o == m ? i : kNoIndex);
+  if (lane == 0) { s_ord[warp] = m; s_idx[warp] = w; }
+  __syncthreads();
+  o = lane < nwarps ? s_ord[lane] : 0u;
+  i = lane < nwarps ? s_idx[lane] : kNoIndex;
+  m = __reduce_max_sync(0xffffffffu, o);
+  w = __reduce_min_sync(0xffffffffu, o == m ? i : kNoIndex);
+  o = m; i = w;
+}
+__device__ __forceinline__ float unord_f32(unsigned o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o); }
+__device__ __forceinline__ void take(unsigned& bo, int& bi, float v, int i) {
+  const unsigned o = ord_f32(v);
+  if (o > bo) { bo = o; bi = i; }
+}
+}  // namespace
+
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_argmax_f32_partial(const float* __restrict__ logits, float* __restrict__ pmax,
+                                                                             int* __restrict__ pidx, int n) {
+  __shared__ unsigned s_ord[32];
+  __shared__ int s_idx[32];
+  const int parts = gridDim.y;
+  const int chunk = (n + parts - 1) / parts;
+  const int lo = blockIdx.y * chunk, hi = min(lo + chunk, n);
+  const float* row = logits + (long long)blockIdx.x * n;
+  unsigned bo = 0u;
+  int bi = kNoIndex;
+  if (((n | chunk) & 3) == 0 && (reinterpret_cast<unsigned long long>(logits) & 15ull) == 0) {
+    const float4* v4 = reinterpret_cast<const float4*>(row + lo);
+    const int nv = (hi - lo) >> 2;
+    for (int u = threadIdx.x; u < nv; u += 2 * blockDim.x) {     // two 16-byte loads in flight per thread
+      const int u1 = u + blockDim.x;
+      const float4 a = __ldcs(v4 + u);
+      float4 b = a;
+      if (u1 < nv) b = __ldcs(v4 + u1);
+      const int ia = lo + 4 * u, ib = lo + 4 * u1;
+      take(bo, bi, a.x, ia); take(bo, bi, a.y, ia + 1); take(bo, bi, a.z, ia + 2); take(bo, bi, a.w, ia + 3);
+      if (u1 < nv) { take(bo, bi, b.x, ib); take(bo, bi, b.y, ib + 1); take(bo, bi, b.z, ib + 2); take(bo, bi, b.w, ib + 3); }
+    }
+  } else {
+    for (int j = lo + threadIdx.x; j < hi; j += blockDim.x) take(bo, bi, row[j], j);
+  }
+  block_argmax(bo, bi, s_ord, s_idx);
+  if (threadIdx.x == 0) {
+    const int o = blockIdx.x * parts + blockIdx.y;
+    const bool none = bo == 0u || bi == kNoIndex;
+    pmax[o] = none ? __int_as_float(0xff800000) : unord_f32(bo);
+    pidx[o] = none ? kNoIndex : bi;
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_argmax_f32_final(const float* __restrict__ pmax, const int* __restrict__ pidx,
+                                                                           long long* __restrict__ out, int parts) {
+  __shared__ unsigned s_ord[32];
+  __shared__ int s_idx[32];
+  const long long base = (long long)blockIdx.x * parts;
+  unsigned bo = 0u;
+  int bi = kNoIndex;
+  for (int t = threadIdx.x; t < parts; t += blockDim.x) {
+    const int i = pidx[base + t];
+    if (i == kNoIndex) continue;
+    const unsigned o = ord_f32(pmax[base + t]);
+    if (o > bo || (o == bo && i < bi)) { bo = o; bi = i; }
+  }
+  block_argmax(bo, bi, s_ord, s_idx);
+  if (threadIdx.x == 0) out[blockIdx.x] = (bo == 0u || bi == kNoIndex) ? 0ll : (long long)bi;
+}
+
 #ifndef K3G_CUBIN_ONLY
 K3G_API int k3g_router_topk(const void* S, const void* bias, const void* rs, void* idx, void* wts, int B, int experts,
                             int topk, void* stream) {
@@ -125,6 +207,14 @@ K3G_API int k3g_router_topk(const void* S, const void* bias, const void* rs, voi
   else
     router_topk_kernel<16><<<grid, 256, 0, k3g_stream(stream)>>>((const float*)S, (const float*)bias, (const __nv_bfloat16*)rs,
                                                                 (int*)idx, (float*)wts, B);
+  return k3g_launch_status();
+}
+K3G_API int k3g_argmax_f32(const void* logits, void* pmax, void* pidx, void* out, int B, int n, int parts, void* stream) {
+  K3G_REQUIRE_PTR(logits); K3G_REQUIRE_PTR(pmax); K3G_REQUIRE_PTR(pidx); K3G_REQUIRE_PTR(out);
+  K3G_REQUIRE(B >= 0 && n > 0 && parts > 0 && parts <= 65535, K3G_ESHAPE);
+  if (B == 0) return K3G_OK;
+  kern_k3_argmax_f32_partial<<<dim3((unsigned)B, (unsigned)parts, 1), 512, 0, k3g_stream(stream)>>>((const float*)logits, (float*)pmax, (int*)pidx, n);
+  kern_k3_argmax_f32_final<<<(unsigned)B, 64, 0, k3g_stream(stream)>>>((const float*)pmax, (const int*)pidx, (long long*)out, parts);
   return k3g_launch_status();
 }
 #endif

@@ -8,8 +8,8 @@ Every launch whose (module, entry) pair this library provides is moved to a new 
 list and the argument mapping are left untouched, because the kernels take exactly the reference's
 parameters.  Launch dims are kept unless this library has a better geometry for the kernel (all
 kernels are grid-stride, so the reference's dims stay valid); `--keep-grids` disables the overrides.
-Launches of kernels outside the glue path (GEMM, FMHA, FlashKDA, load-time preparation, small copies)
-are not touched.  Prints a summary; exits non-zero if a provided entry is missing from its cubin.
+Launches of kernels outside the glue path (GEMM, FMHA, FlashKDA, load-time weight preparation) are not
+touched.  Prints a summary; exits non-zero if a provided entry is missing from its cubin.
 """
 import argparse
 import hashlib
@@ -33,7 +33,12 @@ PROVIDED = {
     "k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16":
         ("k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16",
          ["kern_k3_moe_route_count", "kern_k3_moe_route_tables", "kern_k3_moe_route_scatter", "kern_k3_moe_finalize"]),
-    "k3_router_argmax": ("k3_router_argmax", ["kern_k3_router_topk"]),
+    "k3_router_argmax": ("k3_router_argmax", ["kern_k3_router_topk", "kern_k3_argmax_f32_partial", "kern_k3_argmax_f32_final"]),
+    "k3_residual_push_v3": ("k3_residual_push_v3", ["kern_k3_attnres_rms_push"]),
+    "k3_land": ("k3_land", ["kern_k3_land_situ", "kern_k3_land", "kern_k3_rms"]),
+    "k3_prefill": ("k3_prefill", ["kern_k3_rank_rows", "kern_k3_zero_rows", "kern_k3_fmha_lens"]),
+    "embedding": ("embedding", ["kern_embedding_i64_bf16"]),
+    "copy_rows": ("copy_rows", ["kern_copy_rows_bf16", "kern_last_row_bf16", "kern_own_rows"]),
     "k3_collectives": ("k3_collectives", ["kern_k3_flags_init", "kern_k3_epoch_bump"]),
     "k3_rs_arrive_v2": ("k3_rs_arrive_v2", ["kern_k3_rs_arrive1"]),
     "k3_reducescatter_pull_nr4": ("k3_reducescatter_pull_nr4", ["kern_k3_rs_pull"]),

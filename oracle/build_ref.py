@@ -34,6 +34,11 @@ MODULES = {
     "k3_mla_prep_v2+INNER=3072+MLA_FUSED=5184": ("source/k3_mla_prep_v2.cu", ["-DINNER=3072", "-DMLA_FUSED=5184"], False),
     "k3_mla_prep_bf16+INNER=3072+MLA_FUSED=5184": ("source/k3_mla_prep_bf16.cu", ["-DINNER=3072", "-DMLA_FUSED=5184"], False),
     "k3_land_fused": ("source/k3_land_fused.cu", [], False),
+    "k3_land": ("source/k3_land.cu", [], False),
+    "k3_prefill": ("source/k3_prefill.cu", [], False),
+    "embedding": ("source/embedding.cu", [], False),
+    "copy_rows": ("source/copy_rows.cu", [], False),
+    "k3_residual_push_v3": ("source/k3_residual_push_v3.cu", [], False),
     "sigmoid_mul": ("source/sigmoid_mul.cu", [], False),
     "k3_span_gather_v3+HEADS=24": ("source/k3_span_gather_v3.cu", ["-DHEADS=24"], False),
     "k3_kda_out_gate_v3+HEADS=24": ("source/k3_kda_out_gate_v3.cu", ["-DHEADS=24"], False),

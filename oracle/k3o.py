@@ -286,5 +286,64 @@ def sigmoid_mul(attn, gate, heads, head_dim, gate_tstride, gate_hstride):
     return out
 
 
+# ---- once-per-prefill helpers and f32 landings (byte movement / thin wrappers) ------------------------------
+def land_situ(p, n):
+    """kern_k3_land_situ (source/k3_land.cu:199-237): both operands land to bf16, then SiTU; p is f32 [B, 2n]."""
+    sp = f32_to_bf16(np.ascontiguousarray(p, np.float32))
+    h = 8
+    return situ_rms(sp, np.zeros((0, h), np.uint16), np.zeros(h, np.uint16), n, h)[0]
+
+
+def land(p, n, off, ldc):
+    """kern_k3_land (source/k3_land.cu:166-188): o[b, i] = bf16(p[b * ldc + off + i])."""
+    p = np.ascontiguousarray(p, np.float32).reshape(-1, ldc)
+    return f32_to_bf16(np.ascontiguousarray(p[:, off:off + n]))
+
+
+def rms(x, gamma):
+    """kern_k3_rms at block 1024 (source/k3_land.cu:107-160) for h <= 8192: the latent norm of situ_rms."""
+    h = x.shape[1]
+    return situ_rms(np.zeros((0, 16), np.uint16), x, gamma, 8, h)[1]
+
+
+def rank_rows(src, rank, own):
+    """kern_k3_rank_rows (source/k3_prefill.cu:28-40)."""
+    rows = src.shape[0]
+    return src[np.minimum(rank * own + np.arange(own), rows - 1)].copy()
+
+
+def zero_rows(buf, lo, hi):
+    """kern_k3_zero_rows (source/k3_prefill.cu:42-47)."""
+    out = buf.copy()
+    if hi > lo:
+        out[lo:hi] = 0
+    return out
+
+
+def fmha_lens(seq_lens, T):
+    """kern_k3_fmha_lens (source/k3_prefill.cu:49-60)."""
+    kv = int(seq_lens[0])
+    return np.array([kv, 0, 0, T, 0, kv, 0, 0], np.int32)
+
+
+def embedding(ids, table):
+    """kern_embedding_i64_bf16 (source/embedding.cu:6-16)."""
+    return table[ids].copy()
+
+
+def own_rows(src, blocks, rank, own):
+    """kern_own_rows (source/copy_rows.cu:39-47)."""
+    rows = src.shape[0]
+    return src[np.minimum(int(blocks[rank]) + np.arange(own), rows - 1)].copy()
+
+
+def argmax_f32(logits):
+    """kern_k3_argmax_f32_partial/_final (source/k3_router_argmax.cu:186-241): the largest value under the monotone
+    u32 order of the float's bits (so +NaN patterns order above +inf), ties to the smallest index."""
+    b = np.ascontiguousarray(logits, np.float32).view(np.uint32)
+    key = np.where(b & np.uint32(0x80000000), ~b, b | np.uint32(0x80000000))
+    return np.argmax(key, axis=1).astype(np.int64)
+
+
 def num_threads():
     return int(lib().k3o_num_threads())

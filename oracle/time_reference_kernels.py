@@ -148,6 +148,11 @@ def main():
         lambda: refcubin.run("k3_land_fused", "kern_k3_situ_rms_bf16", 3 * ((4 * B + 15) // 16), 512,
                              [sp, act, lat, gl, ln, SH, B, LAT, B]),
         lambda: k3g.call("k3g_situ_rms", sp, act, lat, gl, ln, SH, B, LAT, B, s), B * (SH * 6 + LAT * 4))
+    del sp, act
+    pf, act33 = rndf(B, 2 * 33792), torch.empty((B, 33792), dtype=bf, device=dev)
+    add("land_situ f32 (layer 0 dense MLP), 4096 x 33792",
+        lambda: refcubin.run("k3_land", "kern_k3_land_situ", (B, 33), 1024, [pf, act33, 33792, B]),
+        lambda: k3g.call("k3g_land_situ", pf, act33, 33792, B, s), B * 33792 * 10)
     if len(sys.argv) > 1:
         json.dump(rows, open(sys.argv[1], "w"), indent=1)
 

@@ -25,7 +25,8 @@ def _bf(g, shape, mean=0.0, std=1.0):
 
 def inputs(name):
     g = _g({"k1b_nb0": 1, "k1b_nb3": 2, "k1a_nb2": 3, "k1c": 4, "moe_quant": 5, "quant_pair": 6, "router": 7, "route": 8, "rs_pull": 9,
-            "mla_prep": 10, "span_gather": 11, "out_gate": 12, "push_add2": 13, "situ_rms": 14, "sigmoid_mul": 15}[name])
+            "mla_prep": 10, "span_gather": 11, "out_gate": 12, "push_add2": 13, "situ_rms": 14, "sigmoid_mul": 15,
+            "land_situ": 16, "rms": 17, "argmax": 18, "push_first": 19, "copies": 20}[name])
     H = 7168
     if name in ("k1b_nb0", "k1b_nb3", "k1a_nb2"):
         B = 3
@@ -40,6 +41,22 @@ def inputs(name):
         return dict(sp=_bf(g, (6, 2 * 6144), std=3.0), lat=_bf(g, (6, 3584)), gam=_bf(g, (3584,), 1.0, 0.02))
     if name == "sigmoid_mul":
         return dict(attn=_bf(g, (9, 3072)), gate=_bf(g, (9, 3072), std=2.0))
+    if name == "land_situ":
+        return dict(p=(g.standard_normal((5, 2 * 1280), dtype=np.float32) * 3.0).astype(np.float32))
+    if name == "rms":
+        return dict(x=_bf(g, (6, 3584), std=2.0), gam=_bf(g, (3584,), 1.0, 0.02))
+    if name == "argmax":
+        x = g.standard_normal((3, 163840), dtype=np.float32)
+        x[0, 70000] = 9.0; x[0, 163839] = 9.0                       # tie: the smaller index wins
+        x[1, :] = -1.0; x[1, 5] = -0.5
+        return dict(x=x)
+    if name == "push_first":
+        B = 3
+        return dict(prefix=_bf(g, (B, H)), blocks=_bf(g, (B, 8, H)), sw=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32),
+                    gamma=_bf(g, (H,), 1.0, 0.02))
+    if name == "copies":
+        return dict(src=_bf(g, (11, 7168)), table=_bf(g, (40, 7168)), ids=g.integers(0, 40, 9).astype(np.int64),
+                    seq=np.array([12345], np.int32))
     if name == "k1c":
         B = 3
         return dict(p1=g.standard_normal((B, H), dtype=np.float32), p2=g.standard_normal((B, H), dtype=np.float32), prefix2=_bf(g, (B, H)))
@@ -78,10 +95,12 @@ def inputs(name):
     raise KeyError(name)
 
 
-NAMES = ["situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
+NAMES = ["land_situ", "rms", "argmax", "push_first", "copies", "situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
 
 # outputs that must be bit-identical between the reference cubin and the CPU oracle
 EXACT = {
+    "land_situ": [], "rms": [], "argmax": ["out"], "push_first": ["blocks"],
+    "copies": ["rank_rows", "zero_rows", "lens", "embedding", "last_row"],
     "situ_rms": [], "sigmoid_mul": [],
     "push_add2": ["hidden", "blocks", "res_mlp_prefix2"],
     "k1b_nb0": ["prefix2"], "k1b_nb3": ["prefix2"], "k1a_nb2": ["blocks"], "k1c": ["hidden"], "moe_quant": ["q", "sf"],
@@ -91,6 +110,7 @@ EXACT = {
 }
 # bf16 outputs compared at tolerance: name -> (max ulp, max fraction of differing elements)
 TOLERANT = {
+    "land_situ": {"act": (2, 0.2)}, "rms": {"o": (1, 2e-3)}, "push_first": {"normed_all": (1, 2e-3)},
     "situ_rms": {"act": (2, 0.2), "ln": (1, 2e-3)}, "sigmoid_mul": {"out": (1, 5e-3)},
     "push_add2": {"normed_all": (4, 5e-3), "res_mlp_normed": (4, 5e-3)},   # mixed rows: a cancelling mix amplifies the 1e-7 softmax difference
     "k1b_nb0": {"normed": (1, 2e-3)}, "k1b_nb3": {"normed": (2, 5e-3)}, "k1a_nb2": {"normed": (2, 5e-3)},
@@ -104,6 +124,23 @@ def run_oracle(name, inp):
     if name == "situ_rms":
         act, ln = k3o.situ_rms(inp["sp"], inp["lat"], inp["gam"], 6144, 3584)
         return dict(act=act, ln=ln)
+    if name == "land_situ":
+        return dict(act=k3o.land_situ(inp["p"], 1280))
+    if name == "rms":
+        return dict(o=k3o.rms(inp["x"], inp["gam"]))
+    if name == "argmax":
+        return dict(out=k3o.argmax_f32(inp["x"]))
+    if name == "push_first":
+        # first layer: nb = 0, snapshot = 1, rank 1 of 4 (manifest op attnres_rms_push_first_v3)
+        blocks = inp["blocks"].copy()
+        normed = k3o.attnres_rms(inp["prefix"], blocks, inp["sw"], inp["gamma"], 0, 1, 1e-5)
+        B, H = normed.shape
+        normed_all = np.zeros((4 * B, H), np.uint16)
+        normed_all[B:2 * B] = normed
+        return dict(blocks=blocks, normed_all=normed_all)
+    if name == "copies":
+        return dict(rank_rows=k3o.rank_rows(inp["src"], 2, 4), zero_rows=k3o.zero_rows(inp["src"], 3, 9), lens=k3o.fmha_lens(inp["seq"], 4096),
+                    embedding=k3o.embedding(inp["ids"], inp["table"]), last_row=inp["src"][10].copy())
     if name == "sigmoid_mul":
         return dict(out=k3o.sigmoid_mul(inp["attn"], inp["gate"], 24, 128, 3072, 128))
     if name == "push_add2":

@@ -37,6 +37,51 @@ def run_reference(name, inp, dev):
     import torch
     bf = torch.bfloat16
     z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=dev)
+    if name == "land_situ":
+        B, n = inp["p"].shape[0], 1280
+        act = z((B, n), bf)
+        refcubin.run("k3_land", "kern_k3_land_situ", (B, (n + 1023) // 1024), 1024, [_up(inp["p"], dev), act, n, B])
+        torch.cuda.synchronize()
+        return dict(act=_bits(act))
+    if name == "rms":
+        B, h = inp["x"].shape
+        o = z((B, h), bf)
+        refcubin.run("k3_land", "kern_k3_rms", B, 1024, [_up(inp["x"], dev), _up(inp["gam"], dev), o, h, B])
+        torch.cuda.synchronize()
+        return dict(o=_bits(o))
+    if name == "argmax":
+        B, n = inp["x"].shape
+        pmax, pidx, out = z((B, 64), torch.float32), z((B, 64), torch.int32), z((B,), torch.int64)
+        refcubin.run("k3_router_argmax", "kern_k3_argmax_f32_partial", (B, 64), 1024, [_up(inp["x"], dev), pmax, pidx, n])
+        refcubin.run("k3_router_argmax", "kern_k3_argmax_f32_final", B, 64, [pmax, pidx, out, 64])
+        torch.cuda.synchronize()
+        return dict(out=out.cpu().numpy())
+    if name == "push_first":
+        B, H = inp["prefix"].shape
+        blocks = _up(inp["blocks"], dev)
+        normed_all = z((4 * B, H), bf)
+        others = [z((4 * B, H), bf) for _ in range(3)]
+        tab = torch.tensor([others[0].data_ptr(), normed_all.data_ptr(), others[1].data_ptr(), others[2].data_ptr()], dtype=torch.int64, device=dev)
+        refcubin.run("k3_residual_push_v3", "kern_k3_attnres_rms_push", B, 128,
+                     [_up(inp["prefix"], dev), blocks, _up(inp["sw"], dev), _up(inp["gamma"], dev), normed_all, tab, 0, 1, B, 1, 4])
+        torch.cuda.synchronize()
+        for o in others:
+            assert torch.equal(o, normed_all)
+        return dict(blocks=_bits(blocks), normed_all=_bits(normed_all))
+    if name == "copies":
+        src, table = _up(inp["src"], dev), _up(inp["table"], dev)
+        rr = z((4, 7168), bf)
+        refcubin.run("k3_prefill", "kern_k3_rank_rows", 4, 256, [rr, src, 2, 4, 14336, 11])
+        zr = src.clone()
+        refcubin.run("k3_prefill", "kern_k3_zero_rows", 1, 1024, [zr, 14336, 3, 9])
+        lens = torch.full((8,), -1, dtype=torch.int32, device=dev)
+        refcubin.run("k3_prefill", "kern_k3_fmha_lens", 1, 32, [_up(inp["seq"], dev), lens, 4096])
+        emb = z((9, 7168), bf)
+        refcubin.run("embedding", "kern_embedding_i64_bf16", 9, 256, [_up(inp["ids"], dev), table, emb, 9, 7168])
+        last = z((7168,), bf)
+        refcubin.run("copy_rows", "kern_last_row_bf16", 1, 1024, [last, src, 7168, 7168, 11])
+        torch.cuda.synchronize()
+        return dict(rank_rows=_bits(rr), zero_rows=_bits(zr), lens=lens.cpu().numpy(), embedding=_bits(emb), last_row=_bits(last))
     if name == "situ_rms":
         B, n, h = inp["sp"].shape[0], 6144, 3584
         act, ln = z((B, n), bf), z((B, h), bf)

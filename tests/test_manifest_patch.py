@@ -28,7 +28,7 @@ def _mini():
         "ops": {
             "router_topk": {"params": ["in buffer<f32>"], "impl": {"launches": [
                 {"module": "k3_router_argmax", "entry": "kern_k3_router_topk", "block": [256, 1, 1], "grid": [{"ceil_div": ["tokens", 4]}, 1, 1]}]}},
-            "argmax": {"impl": {"launches": [{"module": "k3_router_argmax", "entry": "kern_k3_argmax_f32_partial", "block": [1024, 1, 1], "grid": [1, 64, 1]}]}},
+            "argmax": {"impl": {"launches": [{"module": "k3_router_argmax", "entry": "kern_k3_decode_only", "block": [1024, 1, 1], "grid": [1, 64, 1]}]}},
             "moe_quant": {"impl": {"launches": [{"module": "k3_moe_prefill_v3+EP_STRIDED=1", "entry": "kern_k3_moe_quant", "block": [256, 1, 1],
                                                  "grid": [7, 1, 1], "args": [{"param": 0}, {"i32": 3584}]}]}},
             "k3_allgather_push": {"impl": {"launches": [{"module": "k3_rs_arrive_v2", "entry": "kern_k3_rs_arrive1", "block": [32, 1, 1], "grid": [1, 1, 1],
@@ -78,6 +78,11 @@ def test_patch_reference_default_manifest(pm):
     # share of the prefill program's calls that now run on this library's kernels
     n = sum(1 for c in calls if c["op"] in moved_ops)
     assert n > 0.5 * len(calls), (n, len(calls))
+    # every launch the prefill program still makes on a reference module is a GEMM, an attention kernel or FlashKDA
+    for c in calls:
+        for l in m["ops"][c["op"]]["impl"]["launches"]:
+            if not str(l.get("module", "")).startswith("b200/"):
+                assert str(l.get("entry", l.get("extern", ""))).startswith(("extern:", "bmm_", "fmha", "_Z22_flash_kda", "_Z25_flash_kda")), (c["op"], l["entry"][:60])
     for _, entry, mod in s["moved"]:
         blob = open(os.path.join(pm.CUBIN_DIR, mod[len("b200/"):] + ".cubin"), "rb").read()
         assert entry.encode() + b"\0" in blob

@@ -205,6 +205,13 @@ int k3g_span_gather(const void* partial, long long row_stride, const void* cw, i
 int k3g_kda_out_gate(const void* attn, const void* gate, long long gate_stride, long long gate_off, const void* gamma_o,
                      void* gated, void* q, void* sf, int heads, int at, int span, float eps, void* stream);
 
+/* kern_k3_moe_w_shuffle / kern_k3_moe_sf_shuffle, source/k3_moe_prefill_v4.cu:304-327 (load time): expert weight
+ * rows [experts, n, row_bytes] and their scale bytes [experts, n, kg] rearranged into the layouts the grouped GEMM
+ * reads -- rows permuted inside groups of 32 (and gate/up rows interleaved when gated), scales additionally packed
+ * into 128 x 4 tiles of 512 bytes.  n % 32 == 0 (weights), n % 128 == 0 and kg % 4 == 0 (scales). */
+int k3g_moe_w_shuffle(const void* src, void* dst, int experts, int n, int row_bytes, int gated, void* stream);
+int k3g_moe_sf_shuffle(const void* src, void* dst, int experts, int n, int kg, int gated, void* stream);
+
 /* kern_k3_argmax_f32_partial + kern_k3_argmax_f32_final, source/k3_router_argmax.cu:186,225 (op argmax_f32_one):
  * out [B] i64 = index of the largest of n f32 logits per row, ties to the smallest index; pmax / pidx [B, parts]
  * are the caller's scratch for the two stages. */

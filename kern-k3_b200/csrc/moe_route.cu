@@ -322,6 +322,68 @@ extern "C" __global__ void __launch_bounds__(128) kern_k3_moe_finalize(const __n
   finalize_body<false>(fc2, exp2perm, wts, nullptr, out, T, cols, 16);
 }
 
+// ---- load-time expert weight / scale layouts (the formats the grouped GEMM reads) ---------------------
+// Replaces kern_k3_moe_w_shuffle / kern_k3_moe_sf_shuffle (source/k3_moe_prefill_v4.cu:304-327).  Row r of the
+// GEMM layout takes source row src_row(r): inside every group of 32 rows, row (r % 8) * 4 + (r % 32) / 8; for a
+// gated (gate | up) matrix the two halves are then interleaved row by row.
+__device__ __forceinline__ int shuffled_src_row(int r, int n, int gated) {
+  const int u = (r & ~31) + ((r & 7) << 2) + ((r & 31) >> 3);
+  return gated ? ((u & 1) ? n / 2 : 0) + (u >> 1) : u;
+}
+
+// dst[e][r][:] = src[e][src_row(r)][:], rows of row_bytes bytes (a multiple of 16), moved as 16-byte vectors.
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_moe_w_shuffle(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                                                                        int experts, int n, int row_bytes, int gated) {
+  const int per_row = row_bytes >> 4;
+  const long long total = (long long)experts * n * per_row;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nthreads) {
+    const long long row = i / per_row;                       // e * n + r
+    const int c = (int)(i - row * per_row);
+    const long long e = row / n;
+    const int r = (int)(row - e * n);
+    reinterpret_cast<uint4*>(dst)[i] = __ldg(reinterpret_cast<const uint4*>(src + (e * n + shuffled_src_row(r, n, gated)) * row_bytes) + c);
+  }
+}
+
+// Scale bytes [e][n][kg] -> 128 x 4 tiles of 512 bytes: byte (r, c) lands at
+//   ((r / 128) * (kg / 4) + c / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4
+// of expert e's block, read from source row src_row(r).  One thread assembles one 16-byte destination vector
+// (four rows 32 apart x four consecutive k groups) from four 4-byte source words, so stores are coalesced.
+// n % 128 == 0 and kg % 4 == 0 take that path; other shapes go byte by byte.
+extern "C" __global__ void __launch_bounds__(1024) kern_k3_moe_sf_shuffle(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                                                                         int experts, int n, int kg, int gated) {
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((n & 127) == 0 && (kg & 3) == 0 && ((reinterpret_cast<unsigned long long>(src) & 3ull) == 0) &&
+      ((reinterpret_cast<unsigned long long>(dst) & 15ull) == 0)) {
+    const long long per_expert = (long long)n * kg >> 4;     // 16-byte vectors per expert
+    const int kq = kg >> 2;
+    for (long long v = tid; v < experts * per_expert; v += nthreads) {
+      const long long e = v / per_expert;
+      const long long w = v - e * per_expert;                // vector inside the expert: (tile, q) with 32 vectors per tile
+      const long long tile = w >> 5;
+      const int q = (int)(w & 31);
+      const int R = (int)(tile / kq), C = (int)(tile - (long long)R * kq);
+      unsigned word[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = R * 128 + j * 32 + q;
+        word[j] = __ldg(reinterpret_cast<const unsigned*>(src + (e * n + shuffled_src_row(r, n, gated)) * kg + 4 * C));
+      }
+      reinterpret_cast<uint4*>(dst)[v] = make_uint4(word[0], word[1], word[2], word[3]);
+    }
+  } else {
+    const long long total = (long long)experts * n * kg;
+    for (long long i = tid; i < total; i += nthreads) {
+      const int c = (int)(i % kg), r = (int)(i / kg % n);
+      const long long e = i / kg / n;
+      const long long at = ((long long)(r / 128) * (kg / 4) + c / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4;
+      dst[e * n * kg + at] = src[(e * n + shuffled_src_row(r, n, gated)) * kg + c];
+    }
+  }
+}
+
 #ifndef K3G_CUBIN_ONLY
 static int check_route(int T, int E, int topk, int ep_ranks) {
   K3G_REQUIRE(T >= 0 && E > 0 && E <= kMaxE, K3G_ESHAPE);
@@ -395,6 +457,28 @@ K3G_API int k3g_permute_gather(const void* q, const void* sf, const void* route_
   if (grid > 148 * 64) grid = 148 * 64;            // then rows are walked with a warp stride
   permute_gather_kernel<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
                                                                        cols, (uint8_t*)out_q, (uint8_t*)out_sf);
+  return k3g_launch_status();
+}
+K3G_API int k3g_moe_w_shuffle(const void* src, void* dst, int experts, int n, int row_bytes, int gated, void* stream) {
+  K3G_REQUIRE_PTR(src); K3G_REQUIRE_PTR(dst);
+  K3G_REQUIRE_ALIGNED(src); K3G_REQUIRE_ALIGNED(dst);
+  K3G_REQUIRE(experts >= 0 && n > 0 && n % 32 == 0 && row_bytes > 0 && row_bytes % 16 == 0 && (!gated || n % 64 == 0), K3G_ESHAPE);
+  const long long total = (long long)experts * n * (row_bytes / 16);
+  if (total == 0) return K3G_OK;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  kern_k3_moe_w_shuffle<<<(unsigned)blocks, 256, 0, k3g_stream(stream)>>>((const unsigned char*)src, (unsigned char*)dst, experts, n, row_bytes, gated);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_moe_sf_shuffle(const void* src, void* dst, int experts, int n, int kg, int gated, void* stream) {
+  K3G_REQUIRE_PTR(src); K3G_REQUIRE_PTR(dst);
+  K3G_REQUIRE(experts >= 0 && n > 0 && n % 128 == 0 && kg > 0 && kg % 4 == 0 && (!gated || n % 64 == 0), K3G_ESHAPE);
+  const long long total = (long long)experts * n * kg / 16;
+  if (total == 0) return K3G_OK;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  kern_k3_moe_sf_shuffle<<<(unsigned)blocks, 256, 0, k3g_stream(stream)>>>((const unsigned char*)src, (unsigned char*)dst, experts, n, kg, gated);
   return k3g_launch_status();
 }
 #endif

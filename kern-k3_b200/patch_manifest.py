@@ -32,7 +32,8 @@ PROVIDED = {
     "k3_moe_prefill_v3+EP_STRIDED=1": ("k3_moe_prefill_v3+EP_STRIDED=1", ["kern_k3_moe_route_count", "kern_k3_moe_finalize"]),
     "k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16":
         ("k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16",
-         ["kern_k3_moe_route_count", "kern_k3_moe_route_tables", "kern_k3_moe_route_scatter", "kern_k3_moe_finalize"]),
+         ["kern_k3_moe_route_count", "kern_k3_moe_route_tables", "kern_k3_moe_route_scatter", "kern_k3_moe_finalize",
+          "kern_k3_moe_w_shuffle", "kern_k3_moe_sf_shuffle"]),
     "k3_router_argmax": ("k3_router_argmax", ["kern_k3_router_topk", "kern_k3_argmax_f32_partial", "kern_k3_argmax_f32_final"]),
     "k3_residual_push_v3": ("k3_residual_push_v3", ["kern_k3_attnres_rms_push"]),
     "k3_land": ("k3_land", ["kern_k3_land_situ", "kern_k3_land", "kern_k3_rms"]),

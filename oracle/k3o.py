@@ -345,5 +345,26 @@ def argmax_f32(logits):
     return np.argmax(key, axis=1).astype(np.int64)
 
 
+def _shuffled_src_row(r, n, gated):
+    u = (r // 32) * 32 + (r % 8) * 4 + (r % 32) // 8
+    return np.where(u % 2 == 1, n // 2, 0) + u // 2 if gated else u
+
+
+def moe_w_shuffle(src, gated):
+    """kern_k3_moe_w_shuffle (source/k3_moe_prefill_v4.cu:304-317): src [experts, n, row_bytes] u8."""
+    n = src.shape[1]
+    return src[:, _shuffled_src_row(np.arange(n), n, gated)].copy()
+
+
+def moe_sf_shuffle(src, gated):
+    """kern_k3_moe_sf_shuffle (source/k3_moe_prefill_v4.cu:319-327): src [experts, n, kg] u8 -> same size, tiled."""
+    experts, n, kg = src.shape
+    r, c = np.meshgrid(np.arange(n), np.arange(kg), indexing="ij")
+    at = ((r // 128) * (kg // 4) + c // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + c % 4
+    out = np.zeros((experts, n * kg), np.uint8)
+    out[:, at.reshape(-1)] = src[:, _shuffled_src_row(np.arange(n), n, gated)].reshape(experts, -1)
+    return out.reshape(experts, n, kg)
+
+
 def num_threads():
     return int(lib().k3o_num_threads())

@@ -26,7 +26,7 @@ def _bf(g, shape, mean=0.0, std=1.0):
 def inputs(name):
     g = _g({"k1b_nb0": 1, "k1b_nb3": 2, "k1a_nb2": 3, "k1c": 4, "moe_quant": 5, "quant_pair": 6, "router": 7, "route": 8, "rs_pull": 9,
             "mla_prep": 10, "span_gather": 11, "out_gate": 12, "push_add2": 13, "situ_rms": 14, "sigmoid_mul": 15,
-            "land_situ": 16, "rms": 17, "argmax": 18, "push_first": 19, "copies": 20}[name])
+            "land_situ": 16, "rms": 17, "argmax": 18, "push_first": 19, "copies": 20, "moe_shuffle": 21}[name])
     H = 7168
     if name in ("k1b_nb0", "k1b_nb3", "k1a_nb2"):
         B = 3
@@ -54,6 +54,8 @@ def inputs(name):
         B = 3
         return dict(prefix=_bf(g, (B, H)), blocks=_bf(g, (B, 8, H)), sw=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32),
                     gamma=_bf(g, (H,), 1.0, 0.02))
+    if name == "moe_shuffle":
+        return dict(w=g.integers(0, 256, (3, 128, 48), dtype=np.uint8), sf=g.integers(0, 256, (3, 256, 12), dtype=np.uint8))
     if name == "copies":
         return dict(src=_bf(g, (11, 7168)), table=_bf(g, (40, 7168)), ids=g.integers(0, 40, 9).astype(np.int64),
                     seq=np.array([12345], np.int32))
@@ -95,12 +97,12 @@ def inputs(name):
     raise KeyError(name)
 
 
-NAMES = ["land_situ", "rms", "argmax", "push_first", "copies", "situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
+NAMES = ["moe_shuffle", "land_situ", "rms", "argmax", "push_first", "copies", "situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
 
 # outputs that must be bit-identical between the reference cubin and the CPU oracle
 EXACT = {
     "land_situ": [], "rms": [], "argmax": ["out"], "push_first": ["blocks"],
-    "copies": ["rank_rows", "zero_rows", "lens", "embedding", "last_row"],
+    "copies": ["rank_rows", "zero_rows", "lens", "embedding", "last_row"], "moe_shuffle": ["w_plain", "w_gated", "sf_plain", "sf_gated"],
     "situ_rms": [], "sigmoid_mul": [],
     "push_add2": ["hidden", "blocks", "res_mlp_prefix2"],
     "k1b_nb0": ["prefix2"], "k1b_nb3": ["prefix2"], "k1a_nb2": ["blocks"], "k1c": ["hidden"], "moe_quant": ["q", "sf"],
@@ -138,6 +140,9 @@ def run_oracle(name, inp):
         normed_all = np.zeros((4 * B, H), np.uint16)
         normed_all[B:2 * B] = normed
         return dict(blocks=blocks, normed_all=normed_all)
+    if name == "moe_shuffle":
+        return dict(w_plain=k3o.moe_w_shuffle(inp["w"], 0), w_gated=k3o.moe_w_shuffle(inp["w"], 1),
+                    sf_plain=k3o.moe_sf_shuffle(inp["sf"], 0), sf_gated=k3o.moe_sf_shuffle(inp["sf"], 1))
     if name == "copies":
         return dict(rank_rows=k3o.rank_rows(inp["src"], 2, 4), zero_rows=k3o.zero_rows(inp["src"], 3, 9), lens=k3o.fmha_lens(inp["seq"], 4096),
                     embedding=k3o.embedding(inp["ids"], inp["table"]), last_row=inp["src"][10].copy())

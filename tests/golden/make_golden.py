@@ -68,6 +68,19 @@ def run_reference(name, inp, dev):
         for o in others:
             assert torch.equal(o, normed_all)
         return dict(blocks=_bits(blocks), normed_all=_bits(normed_all))
+    if name == "moe_shuffle":
+        w, sf = _up(inp["w"], dev), _up(inp["sf"], dev)
+        res = {}
+        for gated in (0, 1):
+            dw, dsf = torch.zeros_like(w), torch.zeros_like(sf)
+            e, n, rb = inp["w"].shape
+            refcubin.run(cases.MOE, "kern_k3_moe_w_shuffle", (e * n * (rb // 16) + 255) // 256, 256, [w, dw, e, n, rb, gated])
+            e, n, kg = inp["sf"].shape
+            refcubin.run(cases.MOE, "kern_k3_moe_sf_shuffle", (e * n * kg + 255) // 256, 256, [sf, dsf, e, n, kg, gated])
+            torch.cuda.synchronize()
+            tag = "gated" if gated else "plain"
+            res["w_" + tag], res["sf_" + tag] = dw.cpu().numpy(), dsf.cpu().numpy()
+        return res
     if name == "copies":
         src, table = _up(inp["src"], dev), _up(inp["table"], dev)
         rr = z((4, 7168), bf)

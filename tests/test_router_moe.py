@@ -145,3 +145,20 @@ def test_permute_gather(k3g, dev, T, cols, topk, tile):
     # round trip: scattering the gathered rows back through exp2perm reproduces every token row
     e2p = tabs["exp2perm"]
     assert np.array_equal(o_q[e2p[:, 0]], q)
+
+
+@pytest.mark.parametrize("experts,n,row_bytes,kg", [(3, 128, 48, 12), (2, 256, 1792, 112), (1, 384, 16, 4), (0, 128, 16, 4)])
+@pytest.mark.parametrize("gated", [0, 1])
+def test_expert_weight_and_scale_layouts(k3g, dev, experts, n, row_bytes, kg, gated):
+    """Load-time rearrangement of expert weights / scale bytes into the grouped GEMM's layouts (byte-exact)."""
+    import torch
+    g = rng(experts * 13 + n + gated)
+    w = g.integers(0, 256, (experts, n, row_bytes), dtype=np.uint8); sf = g.integers(0, 256, (experts, n, kg), dtype=np.uint8)
+    dw = torch.zeros((max(experts, 1), n, row_bytes), dtype=torch.uint8, device=dev); dsf = torch.zeros((max(experts, 1), n, kg), dtype=torch.uint8, device=dev)
+    s = k3g.current_stream()
+    k3g.call("k3g_moe_w_shuffle", to_dev(w, dev) if experts else dw, dw, experts, n, row_bytes, gated, s)
+    k3g.call("k3g_moe_sf_shuffle", to_dev(sf, dev) if experts else dsf, dsf, experts, n, kg, gated, s)
+    torch.cuda.synchronize()
+    if experts:
+        assert np.array_equal(dw.cpu().numpy(), k3o.moe_w_shuffle(w, gated))
+        assert np.array_equal(dsf.cpu().numpy(), k3o.moe_sf_shuffle(sf, gated))

@@ -29,7 +29,8 @@ PROVIDED = {
     "k3_residual_nb_stats": ("k3_residual_nb_stats", RES),
     "k3_residual_push_add2": ("k3_residual_push_add2", ["kern_k3_attnres_rms_push"]),
     "k3_quant_fp8_pair_v2": ("k3_quant_fp8_pair_v2", ["kern_quant_fp8_amax_v2", "kern_quant_fp8_apply_v2"]),
-    "k3_moe_prefill_v3+EP_STRIDED=1": ("k3_moe_prefill_v3+EP_STRIDED=1", ["kern_k3_moe_route_count", "kern_k3_moe_finalize"]),
+    "k3_moe_prefill_v3+EP_STRIDED=1": ("k3_moe_prefill_v3+EP_STRIDED=1", ["kern_k3_moe_route_count", "kern_k3_moe_finalize", "kern_k3_moe_w_shuffle",
+                                                                        "kern_k3_moe_sf_shuffle"]),
     "k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16":
         ("k3_moe_prefill_v4+EP_RANKS=4+EP_STRIDED=1+TILE_SHIFT=7+SCATTER_WARPS=16",
          ["kern_k3_moe_route_count", "kern_k3_moe_route_tables", "kern_k3_moe_route_scatter", "kern_k3_moe_finalize",

@@ -68,6 +68,25 @@ int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* 
                          int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
                          const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream);
 
+/* Producer-side maxima for a following per-tensor FP8 quantisation (no counterpart in the reference, which
+ * always runs the two-pass pair): the same kernels also store max |output| per row (per 4096 elements for
+ * SiTU) as non-negative f32, and k3g_quant_fp8_apply consumes them in place of the amax pass.  Outputs of the
+ * kernels themselves are unchanged; the quantised result is bit-identical to k3g_quant_fp8_tensor.
+ *   k3g_attnres_rms_push_amax: rowmax_all [nranks * B] f32 on every rank (rowmax_peer = u64 peer table),
+ *                              index rank * B + b, pushed like the row itself.
+ *   k3g_land_add_attnres_rms_stats_amax: rowmax [B] f32.
+ *   k3g_situ_rms_amax: item_max [ceil(B * n / 4096)] f32. */
+int k3g_attnres_rms_push_amax(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
+                              int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
+                              const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* rowmax_all,
+                              const void* rowmax_peer, void* stream);
+int k3g_land_add_attnres_rms_stats_amax(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+                                        const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
+                                        int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream);
+int k3g_situ_rms_amax(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* item_max,
+                      void* stream);
+int k3g_quant_fp8_apply(const void* x, void* y, void* scale_out, const void* partials, int nparts, int n, int grid, void* stream);
+
 /* kern_k3_land_add2, source/k3_residual_v2.cu:349 (op land_add2_v2; bf16 partials as in
  * source/k3_land_bf16.cu:96). */
 int k3g_land_add2(const void* p1, const void* p2, int partial_is_bf16, const void* prefix2, void* hidden, int two,

@@ -170,8 +170,10 @@ __device__ __noinline__ void rms_row_wide(const __nv_bfloat16* __restrict__ lat,
 #define K3G_SITU_VEC 4
 #endif
 constexpr int kSituVec = K3G_SITU_VEC;
+// item_max != nullptr: item_max[chunk] = max |act| over the item (bit-pattern maximum, as the per-tensor FP8
+// amax pass takes it), so a following quantisation of act can skip its own pass over the tensor.
 __device__ __forceinline__ void situ_item(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act, unsigned nv, unsigned total,
-                                          unsigned chunk) {
+                                          unsigned chunk, float* __restrict__ item_max = nullptr, unsigned* s_max = nullptr) {
   const unsigned base = chunk * (kSituVec * 128u) + threadIdx.x;
   V8 g[kSituVec], u[kSituVec];
   size_t off[kSituVec];
@@ -186,9 +188,22 @@ __device__ __forceinline__ void situ_item(const __nv_bfloat16* __restrict__ sp, 
       off[k] = (size_t)idx * 8;
     }
   }
+  unsigned m2 = 0u;
 #pragma unroll
   for (int k = 0; k < kSituVec; ++k)
-    if (base + 128u * k < total) st_stream(act + off[k], situ_vec(g[k], u[k]));
+    if (base + 128u * k < total) {
+      const V8 o = situ_vec(g[k], u[k]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) m2 = __vmaxu2(m2, o.w[j] & 0x7fff7fffu);
+      st_stream(act + off[k], o);
+    }
+  if (item_max != nullptr) {
+    unsigned m = __reduce_max_sync(0xffffffffu, max(m2 & 0xffffu, m2 >> 16));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) item_max[chunk] = __uint_as_float(max(max(s_max[0], s_max[1]), max(s_max[2], s_max[3])) << 16);
+    __syncthreads();
+  }
 }
 
 }  // namespace
@@ -205,9 +220,9 @@ __device__ __forceinline__ void situ_item(const __nv_bfloat16* __restrict__ sp, 
 #ifndef K3G_SITU_IPB
 #define K3G_SITU_IPB 1
 #endif
-extern "C" __global__ void __launch_bounds__(512) kern_k3_situ_rms_bf16(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
-                                                                       const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
-                                                                       __nv_bfloat16* __restrict__ ln, int n, int B, int h, int L) {
+__device__ __forceinline__ void situ_rms_blocks(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
+                                                const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
+                                                __nv_bfloat16* __restrict__ ln, int n, int B, int h, int L, float* __restrict__ item_max) {
   __shared__ float sm[kRmsRows * 32];
   if (threadIdx.x >= 128) return;
   const unsigned nv = (unsigned)n >> 3, total = (unsigned)B * nv;
@@ -226,8 +241,19 @@ extern "C" __global__ void __launch_bounds__(512) kern_k3_situ_rms_bf16(const __
     }
   } else {
     const unsigned situ_blocks = gridDim.x - norm_blocks;
-    for (unsigned c = blockIdx.x - q - 1; c < SC; c += situ_blocks) situ_item(sp, act, nv, total, c);
+    for (unsigned c = blockIdx.x - q - 1; c < SC; c += situ_blocks) situ_item(sp, act, nv, total, c, item_max, reinterpret_cast<unsigned*>(sm));
   }
+}
+extern "C" __global__ void __launch_bounds__(512) kern_k3_situ_rms_bf16(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
+                                                                       const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
+                                                                       __nv_bfloat16* __restrict__ ln, int n, int B, int h, int L) {
+  situ_rms_blocks(sp, act, lat, gam, ln, n, B, h, L, nullptr);
+}
+// The same launch, with item_max [ceil(B * n / 4096)] f32 = max |act| per SiTU item.
+__global__ void __launch_bounds__(512) situ_rms_amax_kernel(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
+                                                            const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
+                                                            __nv_bfloat16* __restrict__ ln, int n, int B, int h, int L, float* __restrict__ item_max) {
+  situ_rms_blocks(sp, act, lat, gam, ln, n, B, h, L, item_max);
 }
 
 // ---- f32 landings (module k3_land) -----------------------------------------------------------------
@@ -385,7 +411,8 @@ extern "C" __global__ void __launch_bounds__(576) kern_k3_latent_gather(const __
 }
 
 #ifndef K3G_CUBIN_ONLY
-K3G_API int k3g_situ_rms(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* stream) {
+static int situ_rms_impl(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* item_max,
+                         void* stream) {
   K3G_REQUIRE_PTR(sp); K3G_REQUIRE_PTR(act); K3G_REQUIRE_PTR(lat); K3G_REQUIRE_PTR(gam); K3G_REQUIRE_PTR(ln);
   K3G_REQUIRE_ALIGNED(sp); K3G_REQUIRE_ALIGNED(act); K3G_REQUIRE_ALIGNED(lat); K3G_REQUIRE_ALIGNED(gam); K3G_REQUIRE_ALIGNED(ln);
   K3G_REQUIRE(n > 0 && n % 8 == 0 && h > 0 && h % 8 == 0 && h <= 8192 && B >= 0 && L >= 0, K3G_ESHAPE);
@@ -397,9 +424,25 @@ K3G_API int k3g_situ_rms(const void* sp, void* act, const void* lat, const void*
   long long q = K3G_SITU_MOD * (nb > sb ? nb : sb);
   if (q < K3G_SITU_MOD) q = K3G_SITU_MOD;
   K3G_REQUIRE(q < (1ll << 31), K3G_ESHAPE);
-  kern_k3_situ_rms_bf16<<<(unsigned)q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)lat,
-                                                              (const __nv_bfloat16*)gam, (__nv_bfloat16*)ln, n, B, h, L);
+  if (item_max)
+    situ_rms_amax_kernel<<<(unsigned)q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)lat,
+                                                                     (const __nv_bfloat16*)gam, (__nv_bfloat16*)ln, n, B, h, L, (float*)item_max);
+  else
+    kern_k3_situ_rms_bf16<<<(unsigned)q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)lat,
+                                                                      (const __nv_bfloat16*)gam, (__nv_bfloat16*)ln, n, B, h, L);
   return k3g_launch_status();
+}
+
+K3G_API int k3g_situ_rms(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* stream) {
+  return situ_rms_impl(sp, act, lat, gam, ln, n, B, h, L, nullptr, stream);
+}
+
+// The same call with item_max [ceil(B * n / 4096)] f32 = max |act| over each run of 4096 consecutive elements of
+// act: the partials a following k3g_quant_fp8_apply of act takes instead of a pass over the tensor.
+K3G_API int k3g_situ_rms_amax(const void* sp, void* act, const void* lat, const void* gam, void* ln, int n, int B, int h, int L, void* item_max,
+                              void* stream) {
+  K3G_REQUIRE_PTR(item_max);
+  return situ_rms_impl(sp, act, lat, gam, ln, n, B, h, L, item_max, stream);
 }
 
 K3G_API int k3g_land_situ(const void* p, void* act, int n, int B, void* stream) {

@@ -128,4 +128,15 @@ K3G_API int k3g_quant_fp8_tensor(const void* x, void* y, void* scale_out, void* 
                                                                   grid, (float*)scale_out);
   return k3g_launch_status();
 }
+// The apply launch alone, for tensors whose producer already left partial maxima (k3g_attnres_rms_push_amax,
+// k3g_land_add_attnres_rms_stats_amax, k3g_situ_rms_amax): partials [nparts] f32 non-negative, any partition
+// of the tensor; the result is bit-identical to k3g_quant_fp8_tensor because the maximum is exact and order-free.
+K3G_API int k3g_quant_fp8_apply(const void* x, void* y, void* scale_out, const void* partials, int nparts, int n, int grid, void* stream) {
+  K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(y); K3G_REQUIRE_PTR(partials);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE(((uintptr_t)y & 7) == 0, K3G_EALIGN);
+  K3G_REQUIRE(n >= 0 && grid > 0 && nparts > 0, K3G_ESHAPE);
+  kern_quant_fp8_apply_v2<<<grid, K3G_QT, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (uint8_t*)y, n, (const float*)partials, nparts,
+                                                                  (float*)scale_out);
+  return k3g_launch_status();
+}
 #endif

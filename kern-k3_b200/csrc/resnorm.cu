@@ -49,24 +49,40 @@ __device__ __forceinline__ float team_sumsq(const V8 (&x)[VPT], float* s_red, in
   return tot;
 }
 
+// max |bf16| over the team's row from per-thread packed maxima m2 (two 15-bit maxima, packed like the data):
+// the maximum of bit patterns, exact and order-free, as kern_quant_fp8_amax_v2 takes it.  One barrier.
+__device__ __forceinline__ unsigned team_absmax_bits(unsigned m2, unsigned* s_buf, int lane, int warp) {
+  unsigned m = max(m2 & 0xffffu, m2 >> 16);
+  m = __reduce_max_sync(0xffffffffu, m);
+  if (lane == 0) s_buf[warp] = m;
+  __syncthreads();
+  return max(max(s_buf[0], s_buf[1]), max(s_buf[2], s_buf[3]));
+}
+
 // RMSNorm of the team's row x (bf16 in registers) with optional MXFP8 epilogue.
+// amax_dst != nullptr: thread 0 also stores max |normed| of the row there (s_amax: 4 words of shared memory),
+// the per-row partial a following per-tensor FP8 quantisation needs instead of its own pass over the tensor.
 //   normed = bf16(bf16(x * r) * gamma),  r = rsqrt_rn(fma(sum x^2, 1/H, eps))
 template <int VPT, bool STORE_NORMED, bool QUANT>
 __device__ __forceinline__ void team_rms_store(const V8 (&x)[VPT], const __nv_bfloat16* __restrict__ gamma,
                                                __nv_bfloat16* __restrict__ normed_row, uint8_t* __restrict__ q_row,
-                                               uint8_t* __restrict__ sf_row, float eps, float* s_red, int t) {
+                                               uint8_t* __restrict__ sf_row, float eps, float* s_red, int t,
+                                               float* __restrict__ amax_dst = nullptr, unsigned* s_amax = nullptr) {
   constexpr int H = VPT * 1024;
   const int lane = t & 31, warp = t >> 5;
   const float tot = team_sumsq<VPT>(x, s_red, lane, warp);
   const float r = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
+  unsigned m2 = 0u;
 #pragma unroll
   for (int v = 0; v < VPT; ++v) {
     const int u = (t + v * kTeam) * 8;
     const V8 g = ld_keep(gamma + u);
     V8 o;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 4; ++j) {
       o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(x[v].w[j]), r), __fmul_rn(bf_hi(x[v].w[j]), r)), g.w[j]);
+      m2 = __vmaxu2(m2, o.w[j] & 0x7fff7fffu);
+    }
     if (STORE_NORMED) st_stream(normed_row + u, o);
     if (QUANT) {
       unsigned am = absmax8(o);
@@ -82,6 +98,10 @@ __device__ __forceinline__ void team_rms_store(const V8 (&x)[VPT], const __nv_bf
       sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
       if ((lane & 15) == 0) *reinterpret_cast<unsigned*>(sf_row + (u >> 5)) = sfb;
     }
+  }
+  if (amax_dst != nullptr) {
+    const unsigned m = team_absmax_bits(m2, s_amax, lane, warp);
+    if (t == 0) *amax_dst = __uint_as_float(m << 16);
   }
 }
 
@@ -254,10 +274,12 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
                                                           const __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
                                                           const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,
                                                           __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps,
-                                                          const float* __restrict__ stats = nullptr, int nb_stats = 0) {
+                                                          const float* __restrict__ stats = nullptr, int nb_stats = 0,
+                                                          float* __restrict__ rowmax = nullptr) {
   constexpr int H = VPT * 1024;
   __shared__ float s_red[2][kTeam / 32];
   __shared__ float s_mix[kMixSmem];
+  __shared__ unsigned s_amax[2][kTeam / 32];
   const int t = threadIdx.x;
   if (stats == nullptr) nb_stats = 0;
   int it = 0;
@@ -289,7 +311,8 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
     if (nb > 0)
       team_attnres_mix<VPT>(x, blocks + (size_t)b * kNbMax * H, sw, nb, eps, s_mix, t, nullptr, nullptr,
                             nb_stats > 0 ? stats + (size_t)b * kNbMax * 2 : nullptr, nb_stats);
-    team_rms_store<VPT, true, false>(x, gamma, normed + base, nullptr, nullptr, eps, s_red[it & 1], t);
+    team_rms_store<VPT, true, false>(x, gamma, normed + base, nullptr, nullptr, eps, s_red[it & 1], t, rowmax ? rowmax + b : nullptr,
+                                     s_amax[it & 1]);
   }
 }
 
@@ -307,10 +330,12 @@ __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict_
                                                       int nranks, const float* __restrict__ sw_mlp, float* __restrict__ stats,
                                                       const __nv_bfloat16* __restrict__ p1, const __nv_bfloat16* __restrict__ p2,
                                                       const __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ hidden, int two,
-                                                      float eps) {
+                                                      float eps, float* __restrict__ rowmax_all = nullptr,
+                                                      const unsigned long long* __restrict__ rowmax_peer = nullptr) {
   constexpr int H = VPT * 1024;
   __shared__ float s_red[2][kTeam / 32];
   __shared__ float s_mix[kMixSmem];
+  __shared__ unsigned s_amax[2][kTeam / 32];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int nr = nranks < 8 ? nranks : 8;
   __nv_bfloat16* peer[8];
@@ -360,18 +385,31 @@ __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict_
     const float tot = team_sumsq<VPT>(x, s_red[it & 1], lane, warp);
     const float r = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
     const size_t dst_off = ((size_t)rank * B + b) * H;
+    unsigned m2 = 0u;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int u = (t + v * kTeam) * 8;
       const V8 g = ld_keep(gamma + u);
       V8 o;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < 4; ++j) {
         o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(x[v].w[j]), r), __fmul_rn(bf_hi(x[v].w[j]), r)), g.w[j]);
+        m2 = __vmaxu2(m2, o.w[j] & 0x7fff7fffu);
+      }
       st_plain(normed_all + dst_off + u, o);            // own slice: the next GEMM reads it, keep it in L2
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         if (peer[q] != nullptr) st_stream(peer[q] + dst_off + u, o);
+    }
+    if (rowmax_all != nullptr) {                        // max |normed| of the row, gathered like the row itself
+      const unsigned m = team_absmax_bits(m2, s_amax[it & 1], lane, warp);
+      if (t == 0) {
+        const float f = __uint_as_float(m << 16);
+        const size_t at = (size_t)rank * B + b;
+        rowmax_all[at] = f;
+        for (int q = 0; q < nr; ++q)
+          if (q != rank) reinterpret_cast<float*>(rowmax_peer[q])[at] = f;
+      }
     }
   }
 }
@@ -517,16 +555,18 @@ template <int VPT, bool LB>
 __global__ void __launch_bounds__(128, 4) land_add_attnres_rms_kernel(const void* partial, const __nv_bfloat16* prefix, const __nv_bfloat16* blocks,
                                                                      const float* sw, const __nv_bfloat16* gamma, __nv_bfloat16* prefix2,
                                                                      __nv_bfloat16* normed, int nb, int snapshot, int B, float eps,
-                                                                     const float* stats, int nb_stats) {
-  land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps, stats, nb_stats);
+                                                                     const float* stats, int nb_stats, float* rowmax) {
+  land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps, stats, nb_stats, rowmax);
 }
 template <int VPT, bool ADD>
 __global__ void __launch_bounds__(128, 4) attnres_rms_push_kernel(__nv_bfloat16* blocks, const float* sw, const __nv_bfloat16* gamma,
                                                                  __nv_bfloat16* normed_all, const unsigned long long* dst_peer, int nb,
                                                                  int snapshot, int B, int rank, int nranks, const float* sw_mlp, float* stats,
                                                                  const __nv_bfloat16* p1, const __nv_bfloat16* p2, const __nv_bfloat16* prefix2,
-                                                                 __nv_bfloat16* hidden, int two, float eps) {
-  attnres_rms_push_body<VPT, ADD>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two, eps);
+                                                                 __nv_bfloat16* hidden, int two, float eps, float* rowmax_all,
+                                                                 const unsigned long long* rowmax_peer) {
+  attnres_rms_push_body<VPT, ADD>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two, eps,
+                                  rowmax_all, rowmax_peer);
 }
 template <int VPT, bool LB>
 __global__ void __launch_bounds__(128, 4) land_add2_kernel(const void* p1, const void* p2, const __nv_bfloat16* prefix2,
@@ -585,7 +625,7 @@ K3G_API int k3g_attnres_rms(const void* prefix, void* blocks, const void* sw, co
 
 static int land_add_attnres_rms_impl(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
                                      const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
-                                     int B, int H, float eps, const void* stats, int nb_stats, void* stream) {
+                                     int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream) {
   K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(prefix2); K3G_REQUIRE_PTR(normed);
   if (!snapshot) K3G_REQUIRE_PTR(prefix);
   K3G_REQUIRE(nb >= 0 && nb <= kNbMax, K3G_ERANGE);
@@ -597,11 +637,11 @@ static int land_add_attnres_rms_impl(const void* partial, int partial_is_bf16, c
   if (partial_is_bf16) {
     K3G_DISPATCH_VPT(H, (land_add_attnres_rms_kernel<VPT, true><<<B, kTeam, 0, k3g_stream(stream)>>>(
         partial, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma,
-        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats, nb_stats)));
+        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats, nb_stats, (float*)rowmax)));
   } else {
     K3G_DISPATCH_VPT(H, (land_add_attnres_rms_kernel<VPT, false><<<B, kTeam, 0, k3g_stream(stream)>>>(
         partial, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma,
-        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats, nb_stats)));
+        (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats, nb_stats, (float*)rowmax)));
   }
   return k3g_launch_status();
 }
@@ -610,7 +650,7 @@ K3G_API int k3g_land_add_attnres_rms(const void* partial, int partial_is_bf16, c
                                      const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
                                      int B, int H, float eps, void* stream) {
   return land_add_attnres_rms_impl(partial, partial_is_bf16, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, H, eps, nullptr, 0,
-                                   stream);
+                                   nullptr, stream);
 }
 
 // The per-candidate-count entries of the reference (kern_k3_land_add_attnres_rms_nb1..8) with the
@@ -622,14 +662,27 @@ K3G_API int k3g_land_add_attnres_rms_stats(const void* partial, int partial_is_b
   K3G_REQUIRE(nb_stats >= 0 && nb_stats <= nb, K3G_ERANGE);
   if (nb_stats > 0) K3G_REQUIRE_PTR(stats);
   return land_add_attnres_rms_impl(partial, partial_is_bf16, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, H, eps, stats,
-                                   nb_stats, stream);
+                                   nb_stats, nullptr, stream);
+}
+
+// The same call with the row maxima a following per-tensor FP8 quantisation of `normed` needs:
+// rowmax [B] f32 = max |normed[b, :]|, so that quantisation can skip its own pass over the tensor (k3g_quant_fp8_apply).
+K3G_API int k3g_land_add_attnres_rms_stats_amax(const void* partial, int partial_is_bf16, const void* prefix, const void* blocks,
+                                                const void* sw, const void* gamma, void* prefix2, void* normed, int nb, int snapshot,
+                                                int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream) {
+  K3G_REQUIRE(nb_stats >= 0 && nb_stats <= nb, K3G_ERANGE);
+  if (nb_stats > 0) K3G_REQUIRE_PTR(stats);
+  K3G_REQUIRE_PTR(rowmax);
+  return land_add_attnres_rms_impl(partial, partial_is_bf16, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, H, eps, stats,
+                                   nb_stats, rowmax, stream);
 }
 
 // kern_k3_attnres_rms_push (op attnres_rms_push_add2): landing add + snapshot + mix + RMSNorm + push of the
 // normed row into every rank's normed_all [nranks * B, H]; stats (may be null) receives the hand-off.
-K3G_API int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
+static int attnres_rms_push_impl(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
                                  int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
-                                 const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream) {
+                                 const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* rowmax_all,
+                                 const void* rowmax_peer, void* stream) {
   K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(normed_all); K3G_REQUIRE_PTR(dst_peer); K3G_REQUIRE_PTR(prefix2);
   if (p1) K3G_REQUIRE_PTR(hidden);
   if (two) { K3G_REQUIRE_PTR(p1); K3G_REQUIRE_PTR(p2); }
@@ -646,13 +699,33 @@ K3G_API int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma
     K3G_DISPATCH_VPT(H, (attnres_rms_push_kernel<VPT, true><<<B, kTeam, 0, k3g_stream(stream)>>>(
         (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed_all, (const unsigned long long*)dst_peer, nb,
         snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, (const __nv_bfloat16*)p1, (const __nv_bfloat16*)p2,
-        (const __nv_bfloat16*)prefix2, (__nv_bfloat16*)hidden, two, eps)));
+        (const __nv_bfloat16*)prefix2, (__nv_bfloat16*)hidden, two, eps, (float*)rowmax_all, (const unsigned long long*)rowmax_peer)));
   } else {                                               // first layer: the row is prefix2 itself
     K3G_DISPATCH_VPT(H, (attnres_rms_push_kernel<VPT, false><<<B, kTeam, 0, k3g_stream(stream)>>>(
         (__nv_bfloat16*)blocks, (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)normed_all, (const unsigned long long*)dst_peer, nb,
-        snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, nullptr, nullptr, (const __nv_bfloat16*)prefix2, nullptr, 0, eps)));
+        snapshot, B, rank, nranks, (const float*)sw_mlp, (float*)stats, nullptr, nullptr, (const __nv_bfloat16*)prefix2, nullptr, 0, eps,
+        (float*)rowmax_all, (const unsigned long long*)rowmax_peer)));
   }
   return k3g_launch_status();
+}
+
+K3G_API int k3g_attnres_rms_push(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
+                                 int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
+                                 const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* stream) {
+  return attnres_rms_push_impl(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two,
+                               H, eps, nullptr, nullptr, stream);
+}
+
+// The same call with the row maxima a following per-tensor FP8 quantisation of the gathered normed_all needs:
+// rowmax_all [nranks * B] f32 on every rank (rowmax_peer = its peer table) receives max |normed row| at index
+// rank * B + b, pushed like the row itself, so that quantisation can skip its own pass (k3g_quant_fp8_apply).
+K3G_API int k3g_attnres_rms_push_amax(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
+                                      int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
+                                      const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* rowmax_all,
+                                      const void* rowmax_peer, void* stream) {
+  K3G_REQUIRE_PTR(rowmax_all); K3G_REQUIRE_PTR(rowmax_peer);
+  return attnres_rms_push_impl(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2, hidden, two,
+                               H, eps, rowmax_all, rowmax_peer, stream);
 }
 
 K3G_API int k3g_land_add2(const void* p1, const void* p2, int partial_is_bf16, const void* prefix2, void* hidden, int two,

@@ -21,9 +21,10 @@ SHARED = 6144
 
 
 class LayerGlue:
-    def __init__(self, rank, world, tokens=16384, kind="kda", nb=4, seed=1, timeout_us=2_000_000, group=None):
+    def __init__(self, rank, world, tokens=16384, kind="kda", nb=4, seed=1, timeout_us=2_000_000, group=None, producer_amax=False):
         assert kind in ("kda", "mla")
         self.rank, self.world, self.T, self.kind, self.nb, self.timeout_us = rank, world, tokens, kind, nb, timeout_us
+        self.producer_amax = producer_amax
         self.B = shard_rows(tokens, world)
         assert self.B * world == tokens and 96 % world == 0
         self.heads = 96 // world
@@ -46,6 +47,9 @@ class LayerGlue:
         self.b_lsf = sym("latent_sf_all", T * LATENT // 32); self.latent_sf_all = self.b_lsf.tensor(torch.uint8, (T, LATENT // 32))
         self.b_idx = sym("topk_idx_all", T * TOPK * 4); self.idx_all = self.b_idx.tensor(torch.int32, (T, TOPK))
         self.b_w = sym("topk_weight_all", T * TOPK * 4); self.wts_all = self.b_w.tensor(torch.float32, (T, TOPK))
+        self.b_rowmax = sym("rowmax_all", T * 4); self.rowmax_all = self.b_rowmax.tensor(torch.float32, (T,))
+        self.rowmax = torch.zeros(B, dtype=torch.float32, device=dev)
+        self.item_max = torch.zeros((B * SHARED + 4095) // 4096, dtype=torch.float32, device=dev)
         self.attn_part.copy_(rnd(T, H, std=0.5 / world))
         # residual stream
         self.prefix2, self.p1, self.p2 = rnd(B, H), rnd(B, H, std=0.3), rnd(B, H, std=0.3)
@@ -156,6 +160,28 @@ class LayerGlue:
                                                                            self.gamma_lat, self.routed_latent_norm, SHARED, B, LATENT, B, s())),
               ("shared_act_quant (fp8 tensor)", lambda: call("k3g_quant_fp8_tensor", self.shared_act, self.shared_q, self.qscale[2:], self.qpart, B * SHARED,
                                                              2048, s()))]
+        if self.producer_amax:
+            # The producers leave the maxima a per-tensor quantisation needs, and the three quantisations run
+            # their apply launch only: same outputs, one pass over each tensor less.
+            swap = {
+                "res_in (land_add2 + attnres + rms + push)": ("res_in (land_add2 + attnres + rms + push, row maxima)", lambda: call(
+                    "k3g_attnres_rms_push_amax", self.blocks, self.sw, self.gamma, self.normed_all, self.b_normed_all.table, nb, 0, B, r, W,
+                    self.sw_mlp, self.stats, self.p1, self.p2, self.prefix2, self.hidden, 1, H, 1e-5, self.rowmax_all, self.b_rowmax.table, s())),
+                "qkvg_quant (fp8 tensor, T rows)": ("qkvg_quant (fp8 apply only, T rows)", lambda: call(
+                    "k3g_quant_fp8_apply", self.normed_all, self.fp8_big, self.qscale, self.rowmax_all, T, T * H, 2048, s())),
+                "res_mlp (land + attnres + rms, stats)": ("res_mlp (land + attnres + rms, stats, row maxima)", lambda: call(
+                    "k3g_land_add_attnres_rms_stats_amax", self.attn_own, 1, self.hidden, self.blocks, self.sw_mlp, self.gamma, self.prefix2_next,
+                    self.normed, nb, 0, B, H, 1e-5, self.stats, nb, self.rowmax, s())),
+                "normed_quant (fp8 tensor, B rows)": ("normed_quant (fp8 apply only, B rows)", lambda: call(
+                    "k3g_quant_fp8_apply", self.normed, self.fp8_small, self.qscale[1:], self.rowmax, B, B * H, 2048, s())),
+                "shared_situ (SiTU landing + latent RMSNorm)": ("shared_situ (SiTU landing + latent RMSNorm, item maxima)", lambda: call(
+                    "k3g_situ_rms_amax", self.shared_partial, self.shared_act, self.routed_latent, self.gamma_lat, self.routed_latent_norm, SHARED,
+                    B, LATENT, B, self.item_max, s())),
+                "shared_act_quant (fp8 tensor)": ("shared_act_quant (fp8 apply only)", lambda: call(
+                    "k3g_quant_fp8_apply", self.shared_act, self.shared_q, self.qscale[2:], self.item_max, self.item_max.numel(), B * SHARED, 2048,
+                    s())),
+            }
+            c = [swap.get(label, (label, fn)) for label, fn in c]
         return c
 
     def run(self):

@@ -69,3 +69,81 @@ def test_attnres_rms_push_emulated_ranks(k3g, dev, W, nb, snapshot, two):
     want = np.concatenate(want_rows)
     for r in range(W):
         assert np.array_equal(bf16_bits(normed_all[r]), want)     # every rank holds the full gathered matrix
+
+
+def _rowmax(bits):
+    """max |x| per row of a bf16 bit array, as f32 (the bit-pattern maximum the amax pass takes)."""
+    m = (bits & 0x7fff).max(axis=-1).astype(np.uint32)
+    return (m << 16).view(np.float32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("W", [1, 4])
+def test_producer_side_amax_equals_two_pass_quantisation(k3g, dev, W):
+    """Row maxima left by the producers (push kernel: gathered over the emulated ranks; per-count residual kernel;
+    SiTU items) fed to the apply launch give exactly the bytes and scale of the two-pass per-tensor quantisation."""
+    import torch
+    B, H, nb = 9, 7168, 3
+    s = k3g.current_stream()
+    cases = [_case(500 + 10 * W + r, B) for r in range(W)]
+    normed_all = [torch.zeros((W * B, H), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    rowmax_all = [torch.full((W * B,), -1.0, dtype=torch.float32, device=dev) for _ in range(W)]
+    tab = torch.tensor([t.data_ptr() for t in normed_all], dtype=torch.int64, device=dev)
+    mtab = torch.tensor([t.data_ptr() for t in rowmax_all], dtype=torch.int64, device=dev)
+    for r, d in enumerate(cases):
+        blocks = to_dev_bf16(d["blocks"], dev)
+        hidden = torch.zeros((B, H), dtype=torch.bfloat16, device=dev); stats = torch.zeros((B, 8, 2), dtype=torch.float32, device=dev)
+        k3g.call("k3g_attnres_rms_push_amax", blocks, to_dev(d["sw"], dev), to_dev_bf16(d["gamma"], dev), normed_all[r], tab, nb, 1, B, r, W,
+                 to_dev(d["sw_mlp"], dev), stats, to_dev_bf16(d["p1"], dev), to_dev_bf16(d["p2"], dev), to_dev_bf16(d["prefix2"], dev), hidden, 1,
+                 H, 1e-5, rowmax_all[r], mtab, s)
+        # consumer of the same layer: per-count residual kernel with its own row maxima
+        p2o, nrm = torch.zeros((B, H), dtype=torch.bfloat16, device=dev), torch.zeros((B, H), dtype=torch.bfloat16, device=dev)
+        rowmax = torch.full((B,), -1.0, dtype=torch.float32, device=dev)
+        k3g.call("k3g_land_add_attnres_rms_stats_amax", to_dev_bf16(d["partial"], dev), 1, hidden, blocks, to_dev(d["sw_mlp"], dev),
+                 to_dev_bf16(d["gamma"], dev), p2o, nrm, nb + 1, 0, B, H, 1e-5, stats, nb, rowmax, s)
+        torch.cuda.synchronize()
+        assert np.array_equal(rowmax.cpu().numpy(), _rowmax(bf16_bits(nrm)))
+        n = B * H
+        y0, y1 = torch.zeros(n, dtype=torch.uint8, device=dev), torch.zeros(n, dtype=torch.uint8, device=dev)
+        sc0, sc1, part = torch.zeros(1, device=dev), torch.zeros(1, device=dev), torch.zeros(64, device=dev)
+        k3g.call("k3g_quant_fp8_tensor", nrm, y0, sc0, part, n, 64, s)
+        k3g.call("k3g_quant_fp8_apply", nrm, y1, sc1, rowmax, B, n, 64, s)
+        torch.cuda.synchronize()
+        assert torch.equal(y0, y1) and torch.equal(sc0, sc1)
+    for r in range(W):
+        assert torch.equal(normed_all[r], normed_all[0]) and torch.equal(rowmax_all[r], rowmax_all[0])
+    assert np.array_equal(rowmax_all[0].cpu().numpy(), _rowmax(bf16_bits(normed_all[0])))
+    n = W * B * H
+    y0, y1 = torch.zeros(n, dtype=torch.uint8, device=dev), torch.zeros(n, dtype=torch.uint8, device=dev)
+    sc0, sc1, part = torch.zeros(1, device=dev), torch.zeros(1, device=dev), torch.zeros(2048, device=dev)
+    k3g.call("k3g_quant_fp8_tensor", normed_all[0], y0, sc0, part, n, 2048, s)
+    k3g.call("k3g_quant_fp8_apply", normed_all[0], y1, sc1, rowmax_all[0], W * B, n, 2048, s)
+    torch.cuda.synchronize()
+    assert torch.equal(y0, y1) and torch.equal(sc0, sc1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,n", [(7, 6144), (3, 1000 * 8), (1, 64)])
+def test_situ_item_maxima(k3g, dev, B, n):
+    import torch
+    g = rng(B + n)
+    s = k3g.current_stream()
+    sp = to_dev_bf16(normal_bf16(g, (B, 2 * n), std=3.0), dev)
+    h = 3584
+    lat, gam = to_dev_bf16(normal_bf16(g, (B, h)), dev), to_dev_bf16(normal_bf16(g, (h,), mean=1.0, std=0.02), dev)
+    act0, act1 = torch.zeros((B, n), dtype=torch.bfloat16, device=dev), torch.zeros((B, n), dtype=torch.bfloat16, device=dev)
+    ln0, ln1 = torch.zeros((B, h), dtype=torch.bfloat16, device=dev), torch.zeros((B, h), dtype=torch.bfloat16, device=dev)
+    items = (B * n + 4095) // 4096
+    imax = torch.full((items,), -1.0, dtype=torch.float32, device=dev)
+    k3g.call("k3g_situ_rms", sp, act0, lat, gam, ln0, n, B, h, B, s)
+    k3g.call("k3g_situ_rms_amax", sp, act1, lat, gam, ln1, n, B, h, B, imax, s)
+    torch.cuda.synchronize()
+    assert torch.equal(act0, act1) and torch.equal(ln0, ln1)
+    flat = np.concatenate([bf16_bits(act1).reshape(-1), np.zeros(items * 4096 - B * n, np.uint16)]).reshape(items, 4096)
+    assert np.array_equal(imax.cpu().numpy(), _rowmax(flat))
+    y0, y1 = torch.zeros(B * n, dtype=torch.uint8, device=dev), torch.zeros(B * n, dtype=torch.uint8, device=dev)
+    sc0, sc1, part = torch.zeros(1, device=dev), torch.zeros(1, device=dev), torch.zeros(32, device=dev)
+    k3g.call("k3g_quant_fp8_tensor", act1, y0, sc0, part, B * n, 32, s)
+    k3g.call("k3g_quant_fp8_apply", act1, y1, sc1, imax, items, B * n, 32, s)
+    torch.cuda.synchronize()
+    assert torch.equal(y0, y1) and torch.equal(sc0, sc1)

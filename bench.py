@@ -247,8 +247,8 @@ def bench_layer(rank, world, timed, iters=20):
     import torch
     from k3g.layer import LayerGlue
     out = {}
-    for kind in ("kda", "mla", "kda_producer_amax", "mla_producer_amax"):
-        lg = LayerGlue(rank, world, TOKENS, kind=kind[:3], producer_amax=kind.endswith("amax"))
+    for kind in ("kda", "mla", "kda_fused", "mla_fused"):
+        lg = LayerGlue(rank, world, TOKENS, kind=kind[:3], fused=kind.endswith("fused"))
         lg.capture()
         graph_us = timed(lg.replay, iters, 3)
         lg.check_status()
@@ -268,11 +268,12 @@ def bench_layer(rank, world, timed, iters=20):
         del lg
         torch.cuda.empty_cache()
     out["weighted_69kda_24mla_us"] = round((69 * out["kda"]["graph_us"] + 24 * out["mla"]["graph_us"]) / 93, 1)
-    out["weighted_69kda_24mla_producer_amax_us"] = round((69 * out["kda_producer_amax"]["graph_us"] + 24 * out["mla_producer_amax"]["graph_us"]) / 93, 1)
+    out["weighted_69kda_24mla_fused_us"] = round((69 * out["kda_fused"]["graph_us"] + 24 * out["mla_fused"]["graph_us"]) / 93, 1)
     out["note"] = ("all non-GEMM calls of one layer of the reference's prefill program at T=16384, world=%d (rows T/%d per rank, %d heads per rank, "
                    "56 local experts); GEMM/attention outputs are seeded random buffers; per-call times are eager launches with events, graph_us "
-                   "is the whole list as one CUDA graph; *_producer_amax = the same program with the three per-tensor FP8 quantisations fed by "
-                   "maxima their producers leave (apply launch only; bit-identical outputs)" % (world, world, 96 // world))
+                   "is the whole list as one CUDA graph; *_fused = the same program with the three per-tensor FP8 quantisations fed by "
+                   "maxima their producers leave (apply launch only) and the attention reduce-scatter pulled inside the residual kernel that consumes it; "
+                   "outputs bit-identical to the reference call list" % (world, world, 96 // world))
     return out
 
 

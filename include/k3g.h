@@ -87,6 +87,17 @@ int k3g_situ_rms_amax(const void* sp, void* act, const void* lat, const void* ga
                       void* stream);
 int k3g_quant_fp8_apply(const void* x, void* y, void* scale_out, const void* partials, int nparts, int n, int grid, void* stream);
 
+/* Pull reduce-scatter folded into the residual kernel that consumes it (no counterpart in the reference, which runs
+ * kern_k3_rs_pull, source/k3_reducescatter_pull_nr4.cu:124, and then kern_k3_land_add_attnres_rms_nbK): partial =
+ * this rank's [nranks * B, H] bf16 partial sums, partial_peer = u64 table of every rank's buffer.  Row b lands the
+ * ring-order chain of row rank * B + b (k3g_rs_pull with order 2 (nranks - 1)) and continues as
+ * k3g_land_add_attnres_rms_stats_amax; outputs are bit-identical to the two calls in sequence, the reduce-scattered
+ * tensor is never written.  Bracket with k3g_rs_arrive as for k3g_rs_pull.  H = 7168; nranks 1, 2, 4 or 8; stats
+ * and rowmax may be null. */
+int k3g_rs_land_add_attnres_rms(const void* partial, const void* partial_peer, int rank, int nranks, const void* prefix,
+                                const void* blocks, const void* sw, const void* gamma, void* prefix2, void* normed, int nb,
+                                int snapshot, int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream);
+
 /* kern_k3_land_add2, source/k3_residual_v2.cu:349 (op land_add2_v2; bf16 partials as in
  * source/k3_land_bf16.cu:96). */
 int k3g_land_add2(const void* p1, const void* p2, int partial_is_bf16, const void* prefix2, void* hidden, int two,

@@ -161,4 +161,37 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
   return r;
 }
 
+// ---- ring-order reduction chain over the ranks' partial buffers (pull reduce-scatter) ------------
+// Chain position k reads base[k]; first hop unrounded, every later hop lands one bf16 rounding:
+// a = f32(bf16(a + f32(v_k))).  bf16x2 add.rn is that operation on a pair.
+template <int NR, int OWNPOS, int DESCEND>
+__device__ __forceinline__ void rs_bases(const __nv_bfloat16* src, const unsigned long long* src_peer, long long off, int rank,
+                                         const uint4* (&base)[NR]) {
+#pragma unroll
+  for (int k = 0; k < NR; ++k) {
+    if (k == OWNPOS) {
+      base[k] = reinterpret_cast<const uint4*>(src + off);
+    } else {
+      const int pi = (k < OWNPOS) ? k : k - 1;
+      const int o = DESCEND ? (NR - 1 - pi) : (1 + pi);
+      base[k] = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src_peer[(rank + o) & (NR - 1)]) + off);
+    }
+  }
+}
+
+template <int NR>
+__device__ __forceinline__ V8 rs_chain(const uint4* const (&base)[NR], long long i) {
+  V8 x[NR];
+#pragma unroll
+  for (int k = 0; k < NR; ++k) x[k] = ld_plain(base[k] + i);     // all hops' loads issued back to back
+  V8 a = x[0];
+#pragma unroll
+  for (int k = 1; k < NR; ++k) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a.w[j] = add_bf2(a.w[j], x[k].w[j]);
+  }
+  return a;
+}
+
+
 }  // namespace k3g

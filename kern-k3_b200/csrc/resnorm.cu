@@ -269,25 +269,59 @@ __device__ __forceinline__ void attnres_rms_body(const __nv_bfloat16* __restrict
 }
 
 // ---- K1b ----------------------------------------------------------------------------------
-template <int VPT, bool LB16>
+// NR > 0: `partial` is this rank's [NR * B, H] bf16 buffer of partial sums and partial_peer the u64 table of every
+// rank's buffer; the landed row is then the ring-order reduce-scatter chain over the NR ranks (peers ascending
+// from rank + 1, own last, one bf16 rounding per hop: k3g::rs_chain) of row rank * B + b -- the pull
+// reduce-scatter folded into the kernel that consumes it, bit-identical to running the two one after the other.
+template <int VPT, bool LB16, int NR = 0>
 __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict__ partial, const __nv_bfloat16* __restrict__ prefix,
                                                           const __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
                                                           const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2,
                                                           __nv_bfloat16* __restrict__ normed, int nb, int snapshot, int B, float eps,
                                                           const float* __restrict__ stats = nullptr, int nb_stats = 0,
-                                                          float* __restrict__ rowmax = nullptr) {
+                                                          float* __restrict__ rowmax = nullptr,
+                                                          const unsigned long long* __restrict__ partial_peer = nullptr, int rank = 0) {
   constexpr int H = VPT * 1024;
   __shared__ float s_red[2][kTeam / 32];
   __shared__ float s_mix[kMixSmem];
   __shared__ unsigned s_amax[2][kTeam / 32];
   const int t = threadIdx.x;
   if (stats == nullptr) nb_stats = 0;
+  constexpr int NRC = NR > 0 ? NR : 1;
+  const uint4* ring[NRC];
+  if constexpr (NR > 0) rs_bases<NR, NR - 1, 0>((const __nv_bfloat16*)partial, partial_peer, (long long)rank * B * H, rank, ring);
   int it = 0;
   for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
     const size_t base = (size_t)b * H;
     V8 x[VPT];
+    if constexpr (NR > 0) {
+      // pull the NR partial rows two vectors at a time (2 NR + 2 loads in flight per thread), land the chain, add
+      constexpr int CH = 2;
 #pragma unroll
-    for (int v = 0; v < VPT; ++v) {
+      for (int v0 = 0; v0 < VPT; v0 += CH) {
+        V8 pr[CH], p[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+          if (v0 + c < VPT && !snapshot) pr[c] = ld_stream(prefix + base + (t + (v0 + c) * kTeam) * 8);
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+          if (v0 + c < VPT) p[c] = rs_chain<NRC>(ring, (long long)((base >> 3) + t + (v0 + c) * kTeam));
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          if (v0 + c >= VPT) continue;
+          const int v = v0 + c;
+          if (snapshot) {
+            x[v] = p[c];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr[c].w[j], p[c].w[j]);
+          }
+          st_stream(prefix2 + base + (t + v * kTeam) * 8, x[v]);
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < (NR > 0 ? 0 : VPT); ++v) {
       const size_t off = base + (t + v * kTeam) * 8;
       V8 p;
       if (LB16) {
@@ -558,6 +592,15 @@ __global__ void __launch_bounds__(128, 4) land_add_attnres_rms_kernel(const void
                                                                      const float* stats, int nb_stats, float* rowmax) {
   land_add_attnres_rms_body<VPT, LB>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps, stats, nb_stats, rowmax);
 }
+template <int VPT, int NR>
+__global__ void __launch_bounds__(128, 4) rs_land_add_attnres_rms_kernel(const __nv_bfloat16* partial, const unsigned long long* partial_peer, int rank,
+                                                                        const __nv_bfloat16* prefix, const __nv_bfloat16* blocks, const float* sw,
+                                                                        const __nv_bfloat16* gamma, __nv_bfloat16* prefix2, __nv_bfloat16* normed,
+                                                                        int nb, int snapshot, int B, float eps, const float* stats, int nb_stats,
+                                                                        float* rowmax) {
+  land_add_attnres_rms_body<VPT, true, NR>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, eps, stats, nb_stats, rowmax,
+                                           partial_peer, rank);
+}
 template <int VPT, bool ADD>
 __global__ void __launch_bounds__(128, 4) attnres_rms_push_kernel(__nv_bfloat16* blocks, const float* sw, const __nv_bfloat16* gamma,
                                                                  __nv_bfloat16* normed_all, const unsigned long long* dst_peer, int nb,
@@ -679,6 +722,41 @@ K3G_API int k3g_land_add_attnres_rms_stats_amax(const void* partial, int partial
 
 // kern_k3_attnres_rms_push (op attnres_rms_push_add2): landing add + snapshot + mix + RMSNorm + push of the
 // normed row into every rank's normed_all [nranks * B, H]; stats (may be null) receives the hand-off.
+// Pull reduce-scatter folded into the residual kernel that consumes it (no counterpart in the reference, which
+// runs kern_k3_rs_pull and then kern_k3_land_add_attnres_rms_nbK): `partial` is this rank's [nranks * B, H] bf16
+// buffer of partial sums, partial_peer the u64 table of every rank's buffer; row b lands the ring-order chain of
+// row rank * B + b over the ranks (as k3g_rs_pull with order 2 (nranks - 1)) and continues as
+// k3g_land_add_attnres_rms_stats_amax on it.  Outputs are bit-identical to the two calls in sequence; the
+// reduce-scattered tensor itself is never written.  Bracket with k3g_rs_arrive as for k3g_rs_pull.  H = 7168,
+// nranks in {1, 2, 4, 8}; stats and rowmax may be null.
+K3G_API int k3g_rs_land_add_attnres_rms(const void* partial, const void* partial_peer, int rank, int nranks, const void* prefix,
+                                        const void* blocks, const void* sw, const void* gamma, void* prefix2, void* normed, int nb,
+                                        int snapshot, int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream) {
+  K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(partial_peer); K3G_REQUIRE_PTR(gamma); K3G_REQUIRE_PTR(prefix2); K3G_REQUIRE_PTR(normed);
+  if (!snapshot) K3G_REQUIRE_PTR(prefix);
+  K3G_REQUIRE(nb >= 0 && nb <= kNbMax && nb_stats >= 0 && nb_stats <= nb, K3G_ERANGE);
+  if (nb > 0) { K3G_REQUIRE_PTR(blocks); K3G_REQUIRE_PTR(sw); }
+  if (nb_stats > 0) K3G_REQUIRE_PTR(stats);
+  K3G_REQUIRE_ALIGNED(partial); K3G_REQUIRE_ALIGNED(prefix); K3G_REQUIRE_ALIGNED(blocks); K3G_REQUIRE_ALIGNED(sw);
+  K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(prefix2); K3G_REQUIRE_ALIGNED(normed);
+  K3G_REQUIRE(B >= 0 && H == 7168 && (nranks == 1 || nranks == 2 || nranks == 4 || nranks == 8), K3G_ESHAPE);
+  K3G_REQUIRE(rank >= 0 && rank < nranks, K3G_ERANGE);
+  if (B == 0) return K3G_OK;
+#define K3G_RS_K1B(NR)                                                                                                                         \
+  rs_land_add_attnres_rms_kernel<7, NR><<<B, kTeam, 0, k3g_stream(stream)>>>(                                                                   \
+      (const __nv_bfloat16*)partial, (const unsigned long long*)partial_peer, rank, (const __nv_bfloat16*)prefix, (const __nv_bfloat16*)blocks, \
+      (const float*)sw, (const __nv_bfloat16*)gamma, (__nv_bfloat16*)prefix2, (__nv_bfloat16*)normed, nb, snapshot, B, eps, (const float*)stats,  \
+      nb_stats, (float*)rowmax)
+  switch (nranks) {
+    case 1: K3G_RS_K1B(1); break;
+    case 2: K3G_RS_K1B(2); break;
+    case 4: K3G_RS_K1B(4); break;
+    default: K3G_RS_K1B(8); break;
+  }
+#undef K3G_RS_K1B
+  return k3g_launch_status();
+}
+
 static int attnres_rms_push_impl(void* blocks, const void* sw, const void* gamma, void* normed_all, const void* dst_peer, int nb,
                                  int snapshot, int B, int rank, int nranks, const void* sw_mlp, void* stats, const void* p1,
                                  const void* p2, const void* prefix2, void* hidden, int two, int H, float eps, void* rowmax_all,

@@ -21,10 +21,10 @@ SHARED = 6144
 
 
 class LayerGlue:
-    def __init__(self, rank, world, tokens=16384, kind="kda", nb=4, seed=1, timeout_us=2_000_000, group=None, producer_amax=False):
+    def __init__(self, rank, world, tokens=16384, kind="kda", nb=4, seed=1, timeout_us=2_000_000, group=None, fused=False):
         assert kind in ("kda", "mla")
         self.rank, self.world, self.T, self.kind, self.nb, self.timeout_us = rank, world, tokens, kind, nb, timeout_us
-        self.producer_amax = producer_amax
+        self.fused = fused
         self.B = shard_rows(tokens, world)
         assert self.B * world == tokens and 96 % world == 0
         self.heads = 96 // world
@@ -160,18 +160,22 @@ class LayerGlue:
                                                                            self.gamma_lat, self.routed_latent_norm, SHARED, B, LATENT, B, s())),
               ("shared_act_quant (fp8 tensor)", lambda: call("k3g_quant_fp8_tensor", self.shared_act, self.shared_q, self.qscale[2:], self.qpart, B * SHARED,
                                                              2048, s()))]
-        if self.producer_amax:
-            # The producers leave the maxima a per-tensor quantisation needs, and the three quantisations run
-            # their apply launch only: same outputs, one pass over each tensor less.
+        if self.fused:
+            # Fusions beyond the reference's call list, all with bit-identical outputs:
+            #  - the producers leave the maxima a per-tensor quantisation needs, so the three quantisations run
+            #    their apply launch only (one pass over each tensor less);
+            #  - the attention reduce-scatter is pulled inside the residual kernel that consumes it, so its HBM
+            #    work hides under the NVLink transfer and the reduce-scattered tensor is never written.
             swap = {
                 "res_in (land_add2 + attnres + rms + push)": ("res_in (land_add2 + attnres + rms + push, row maxima)", lambda: call(
                     "k3g_attnres_rms_push_amax", self.blocks, self.sw, self.gamma, self.normed_all, self.b_normed_all.table, nb, 0, B, r, W,
                     self.sw_mlp, self.stats, self.p1, self.p2, self.prefix2, self.hidden, 1, H, 1e-5, self.rowmax_all, self.b_rowmax.table, s())),
                 "qkvg_quant (fp8 tensor, T rows)": ("qkvg_quant (fp8 apply only, T rows)", lambda: call(
                     "k3g_quant_fp8_apply", self.normed_all, self.fp8_big, self.qscale, self.rowmax_all, T, T * H, 2048, s())),
-                "res_mlp (land + attnres + rms, stats)": ("res_mlp (land + attnres + rms, stats, row maxima)", lambda: call(
-                    "k3g_land_add_attnres_rms_stats_amax", self.attn_own, 1, self.hidden, self.blocks, self.sw_mlp, self.gamma, self.prefix2_next,
-                    self.normed, nb, 0, B, H, 1e-5, self.stats, nb, self.rowmax, s())),
+                "reduce_attn (pull RS)": None,
+                "res_mlp (land + attnres + rms, stats)": ("reduce_attn + res_mlp (pull RS inside land + attnres + rms, stats, row maxima)", lambda: call(
+                    "k3g_rs_land_add_attnres_rms", self.attn_part, self.b_attn_part.table, r, W, self.hidden, self.blocks, self.sw_mlp, self.gamma,
+                    self.prefix2_next, self.normed, nb, 0, B, H, 1e-5, self.stats, nb, self.rowmax, s())),
                 "normed_quant (fp8 tensor, B rows)": ("normed_quant (fp8 apply only, B rows)", lambda: call(
                     "k3g_quant_fp8_apply", self.normed, self.fp8_small, self.qscale[1:], self.rowmax, B, B * H, 2048, s())),
                 "shared_situ (SiTU landing + latent RMSNorm)": ("shared_situ (SiTU landing + latent RMSNorm, item maxima)", lambda: call(
@@ -181,7 +185,7 @@ class LayerGlue:
                     "k3g_quant_fp8_apply", self.shared_act, self.shared_q, self.qscale[2:], self.item_max, self.item_max.numel(), B * SHARED, 2048,
                     s())),
             }
-            c = [swap.get(label, (label, fn)) for label, fn in c]
+            c = [swap.get(label, (label, fn)) for label, fn in c if swap.get(label, 0) is not None]
         return c
 
     def run(self):

@@ -14,7 +14,7 @@ for p in ("kern-k3_b200", "oracle", "tests"):
 import k3g  # noqa: E402
 import k3o  # noqa: E402
 from k3g.peer import PeerGroup, collective_units  # noqa: E402
-from util import bf16_bits, normal_bf16, rng, to_dev_bf16  # noqa: E402
+from util import bf16_bits, normal_bf16, rng, to_dev, to_dev_bf16  # noqa: E402
 
 
 def main():
@@ -72,6 +72,18 @@ def main():
         assert np.array_equal(bf16_bits(res_out), want_res)
         assert np.array_equal(sf_all.cpu().numpy(), wsf)
         assert np.array_equal(q_all.cpu().numpy(), wq)
+        # the same partials pulled inside the residual kernel (reduce-scatter folded into its consumer), world 1/2/4/8
+        if world in (1, 2, 4, 8):
+            nb = 3
+            blocks_h = normal_bf16(rng(4000 + rank), (rows, 8, H)); sw_h = (rng(5).standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32)
+            p2, nrm = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev), torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+            rowmax = torch.zeros(rows, dtype=torch.float32, device=dev)
+            k3g.call("k3g_rs_land_add_attnres_rms", part, b_part.table, rank, world, to_dev_bf16(residual[rank], dev), to_dev_bf16(blocks_h, dev),
+                     to_dev(sw_h, dev), to_dev_bf16(gamma, dev), p2, nrm, nb, 0, rows, H, 1e-5, None, 0, rowmax, s)
+            torch.cuda.synchronize()
+            o_p2, o_n = k3o.land_add_attnres_rms(want_delta.reshape(rows, H), residual[rank], blocks_h, sw_h, gamma, nb, 0, 1e-5)
+            assert np.array_equal(bf16_bits(p2), o_p2) and np.array_equal(bf16_bits(nrm), o_n)
+            assert np.array_equal(rowmax.cpu().numpy(), (((o_n & 0x7fff).max(axis=1).astype(np.uint32)) << 16).view(np.float32))
         # push all-gather of four byte streams with its own barrier tail
         srcs = [torch.from_numpy(rng(50 + rank * 4 + i).integers(0, 256, n, dtype=np.uint8)).to(dev) for i, n in enumerate((rows * 3584, rows * 112, rows * 64, rows * 64))]
         if replay == 0:

@@ -147,3 +147,37 @@ def test_situ_item_maxima(k3g, dev, B, n):
     k3g.call("k3g_quant_fp8_apply", act1, y1, sc1, imax, items, B * n, 32, s)
     torch.cuda.synchronize()
     assert torch.equal(y0, y1) and torch.equal(sc0, sc1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("W,nb,snapshot", [(1, 0, 0), (2, 3, 0), (4, 4, 0), (4, 2, 1), (8, 8, 0)])
+def test_reduce_scatter_folded_into_the_residual_kernel(k3g, dev, W, nb, snapshot):
+    """k3g_rs_land_add_attnres_rms == k3g_rs_pull followed by k3g_land_add_attnres_rms_stats_amax, bit for bit, for
+    every rank of a world emulated on one GPU (data kernels only: nothing waits), and == the oracle chain."""
+    import torch
+    B, H = 11, 7168
+    g = rng(900 + W + nb)
+    s = k3g.current_stream()
+    parts = [normal_bf16(g, (W * B, H), std=0.5 / W) for _ in range(W)]
+    d_parts = [to_dev_bf16(p, dev) for p in parts]
+    tab = torch.tensor([t.data_ptr() for t in d_parts], dtype=torch.int64, device=dev)
+    for rank in range(W):
+        d = _case(1000 + rank, B)
+        blocks, prefix = to_dev_bf16(d["blocks"], dev), to_dev_bf16(d["prefix2"], dev)
+        sw, gamma = to_dev(d["sw_mlp"], dev), to_dev_bf16(d["gamma"], dev)
+        # statistics as the push kernel of the same layer would have left them
+        o_blocks = d["blocks"].copy()
+        _, _, o_stats = k3o.attnres_rms_push(o_blocks, d["sw"], d["gamma"], nb, 0, d["sw_mlp"], d["p1"], d["p2"], d["prefix2"], 1, 1e-5)
+        stats = to_dev(o_stats, dev)
+        own = torch.zeros((B, H), dtype=torch.bfloat16, device=dev)
+        k3g.call("k3g_rs_pull", d_parts[rank], own, tab, B * H, 2 * (W - 1), rank, W, 8, s)
+        a = [torch.zeros((B, H), dtype=torch.bfloat16, device=dev) for _ in range(4)]
+        m0, m1 = torch.zeros(B, device=dev), torch.zeros(B, device=dev)
+        k3g.call("k3g_land_add_attnres_rms_stats_amax", own, 1, prefix, blocks, sw, gamma, a[0], a[1], nb, snapshot, B, H, 1e-5, stats, nb, m0, s)
+        k3g.call("k3g_rs_land_add_attnres_rms", d_parts[rank], tab, rank, W, prefix, blocks, sw, gamma, a[2], a[3], nb, snapshot, B, H, 1e-5,
+                 stats, nb, m1, s)
+        torch.cuda.synchronize()
+        assert torch.equal(a[0], a[2]) and torch.equal(a[1], a[3]) and torch.equal(m0, m1)
+        o_own = k3o.rs_pull(parts, rank, 2 * (W - 1))
+        o_p2, o_n = k3o.land_add_attnres_rms(o_own.reshape(B, H), d["prefix2"], d["blocks"], d["sw_mlp"], d["gamma"], nb, snapshot, 1e-5)
+        assert np.array_equal(bf16_bits(a[2]), o_p2) and np.array_equal(bf16_bits(a[3]), o_n)

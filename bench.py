@@ -272,7 +272,7 @@ def bench_layer(rank, world, timed, iters=20):
     out["note"] = ("all non-GEMM calls of one layer of the reference's prefill program at T=16384, world=%d (rows T/%d per rank, %d heads per rank, "
                    "56 local experts); GEMM/attention outputs are seeded random buffers; per-call times are eager launches with events, graph_us "
                    "is the whole list as one CUDA graph; *_fused = the same program with the three per-tensor FP8 quantisations fed by "
-                   "maxima their producers leave (apply launch only) and the attention reduce-scatter pulled inside the residual kernel that consumes it; "
+                   "maxima their producers leave (apply launch only) and the two reduce-scatters pulled inside the kernels that consume them (residual kernel, latent norm); "
                    "outputs bit-identical to the reference call list" % (world, world, 96 // world))
     return out
 

@@ -98,6 +98,13 @@ int k3g_rs_land_add_attnres_rms(const void* partial, const void* partial_peer, i
                                 const void* blocks, const void* sw, const void* gamma, void* prefix2, void* normed, int nb,
                                 int snapshot, int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream);
 
+/* The same folding for the routed-latent reduce-scatter and the latent norm of k3g_situ_rms (no counterpart in the
+ * reference): partial = this rank's [nranks * L, h] bf16 partial sums, partial_peer = u64 table; ln [L, h] is the norm
+ * of the ring-order chain of rows rank * L + r; act / item_max as k3g_situ_rms_amax (item_max may be null).  Outputs
+ * bit-identical to k3g_rs_pull followed by k3g_situ_rms.  h <= 4096; nranks 1, 2, 4 or 8. */
+int k3g_rs_situ_rms(const void* sp, void* act, const void* partial, const void* partial_peer, int rank, int nranks, const void* gam,
+                    void* ln, int n, int B, int h, int L, void* item_max, void* stream);
+
 /* kern_k3_land_add2, source/k3_residual_v2.cu:349 (op land_add2_v2; bf16 partials as in
  * source/k3_land_bf16.cu:96). */
 int k3g_land_add2(const void* p1, const void* p2, int partial_is_bf16, const void* prefix2, void* hidden, int two,

@@ -208,6 +208,32 @@ __device__ __forceinline__ void situ_item(const __nv_bfloat16* __restrict__ sp, 
 
 }  // namespace
 
+// One latent row whose source is the ring-order reduce-scatter chain over NR ranks' partial buffers (k3g::rs_chain):
+// the pull reduce-scatter folded into the norm that consumes it.  Two vectors (2 NR loads) in flight per thread.
+template <int NR>
+__device__ __forceinline__ void rms_row_pull(const uint4* const (&ring)[NR], const __nv_bfloat16* __restrict__ gam, __nv_bfloat16* __restrict__ ln,
+                                             int h, int row, float* sm) {
+  const int t = threadIdx.x, nvec = h >> 3;
+  V8 v[1][4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    v[0][k] = V8{{0u, 0u, 0u, 0u}};
+    if (t + 128 * k < nvec) v[0][k] = rs_chain<NR>(ring, (long long)row * nvec + t + 128 * k);
+  }
+  float sums[1];
+  rms_rows<1, 4>(v, nvec, sm, sums);
+  const float rs = __frsqrt_rn(__fadd_rn(__fdiv_rn(sums[0], (float)h), 1e-5f));
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (t + 128 * k >= nvec) continue;
+    const V8 g = ld_keep(gam + (t + 128 * k) * 8);
+    V8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o.w[j] = mul_bf2(pack_bf2(__fmul_rn(bf_lo(v[0][k].w[j]), rs), __fmul_rn(bf_hi(v[0][k].w[j]), rs)), g.w[j]);
+    st_stream(ln + (size_t)row * h + (t + 128 * k) * 8, o);
+  }
+}
+
 // Work items: ceil(L / 2) norm items (2 latent rows each) and ceil(B * n / 4096) SiTU items (512 vectors
 // each).  Blocks with blockIdx.x % K3G_SITU_MOD == 0 stride over the norm items, the others over the SiTU
 // items, so that the hardware block scheduler keeps both kinds resident on every SM and the latency-bound
@@ -254,6 +280,28 @@ __global__ void __launch_bounds__(512) situ_rms_amax_kernel(const __nv_bfloat16*
                                                             const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ gam,
                                                             __nv_bfloat16* __restrict__ ln, int n, int B, int h, int L, float* __restrict__ item_max) {
   situ_rms_blocks(sp, act, lat, gam, ln, n, B, h, L, item_max);
+}
+
+// SiTU landing + latent RMSNorm with the latent rows pulled from every rank's partial buffer [NR * L, h] (row
+// rank * L + r, ring order, one bf16 rounding per hop): every other block pulls and normalises one row per item,
+// the others run SiTU items, so the activation hides under the NVLink transfer.  h <= 4096.
+template <int NR>
+__global__ void __launch_bounds__(128) rs_situ_rms_kernel(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
+                                                          const __nv_bfloat16* __restrict__ partial, const unsigned long long* __restrict__ partial_peer,
+                                                          int rank, const __nv_bfloat16* __restrict__ gam, __nv_bfloat16* __restrict__ ln, int n, int B,
+                                                          int h, int L, float* __restrict__ item_max) {
+  __shared__ float sm[kRmsRows * 32];
+  const unsigned nv = (unsigned)n >> 3, total = (unsigned)B * nv;
+  const unsigned SC = (total + kSituVec * 128u - 1) / (kSituVec * 128u);
+  const unsigned q = blockIdx.x >> 1, pull_blocks = (gridDim.x + 1) >> 1;
+  if ((blockIdx.x & 1) == 0) {
+    const uint4* ring[NR];
+    rs_bases<NR, NR - 1, 0>(partial, partial_peer, (long long)rank * L * h, rank, ring);
+    for (unsigned r = q; r < (unsigned)L; r += pull_blocks) rms_row_pull<NR>(ring, gam, ln, h, (int)r, sm);
+  } else {
+    const unsigned situ_blocks = gridDim.x - pull_blocks;
+    for (unsigned c = q; c < SC; c += situ_blocks) situ_item(sp, act, nv, total, c, item_max, reinterpret_cast<unsigned*>(sm));
+  }
 }
 
 // ---- f32 landings (module k3_land) -----------------------------------------------------------------
@@ -443,6 +491,37 @@ K3G_API int k3g_situ_rms_amax(const void* sp, void* act, const void* lat, const 
                               void* stream) {
   K3G_REQUIRE_PTR(item_max);
   return situ_rms_impl(sp, act, lat, gam, ln, n, B, h, L, item_max, stream);
+}
+
+// Pull reduce-scatter folded into the latent norm (no counterpart in the reference, which runs kern_k3_rs_pull and then
+// kern_k3_situ_rms_bf16): partial = this rank's [nranks * L, h] bf16 partial sums, partial_peer = u64 table of every
+// rank's buffer; ln [L, h] is the norm of the ring-order chain of rows rank * L + r, bit-identical to the two calls in
+// sequence.  Bracket with k3g_rs_arrive as for k3g_rs_pull.  h <= 4096; nranks 1, 2, 4 or 8; item_max may be null.
+K3G_API int k3g_rs_situ_rms(const void* sp, void* act, const void* partial, const void* partial_peer, int rank, int nranks, const void* gam,
+                            void* ln, int n, int B, int h, int L, void* item_max, void* stream) {
+  K3G_REQUIRE_PTR(sp); K3G_REQUIRE_PTR(act); K3G_REQUIRE_PTR(partial); K3G_REQUIRE_PTR(partial_peer); K3G_REQUIRE_PTR(gam); K3G_REQUIRE_PTR(ln);
+  K3G_REQUIRE_ALIGNED(sp); K3G_REQUIRE_ALIGNED(act); K3G_REQUIRE_ALIGNED(partial); K3G_REQUIRE_ALIGNED(gam); K3G_REQUIRE_ALIGNED(ln);
+  K3G_REQUIRE(n > 0 && n % 8 == 0 && h > 0 && h % 8 == 0 && h <= 4096 && B >= 0 && L >= 0, K3G_ESHAPE);
+  K3G_REQUIRE(nranks == 1 || nranks == 2 || nranks == 4 || nranks == 8, K3G_ESHAPE);
+  K3G_REQUIRE(rank >= 0 && rank < nranks, K3G_ERANGE);
+  if (B == 0 && L == 0) return K3G_OK;
+  K3G_REQUIRE((long long)B * (n / 8) < (1ll << 31), K3G_ESHAPE);
+  const long long sc = ((long long)B * (n / 8) + kSituVec * 128 - 1) / (kSituVec * 128);
+  long long q = 2 * (L > sc ? L : sc);
+  if (q < 2) q = 2;
+  K3G_REQUIRE(q < (1ll << 31), K3G_ESHAPE);
+#define K3G_RS_SITU(NR)                                                                                                                      \
+  rs_situ_rms_kernel<NR><<<(unsigned)q, 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)sp, (__nv_bfloat16*)act, (const __nv_bfloat16*)partial, \
+                                                                     (const unsigned long long*)partial_peer, rank, (const __nv_bfloat16*)gam,   \
+                                                                     (__nv_bfloat16*)ln, n, B, h, L, (float*)item_max)
+  switch (nranks) {
+    case 1: K3G_RS_SITU(1); break;
+    case 2: K3G_RS_SITU(2); break;
+    case 4: K3G_RS_SITU(4); break;
+    default: K3G_RS_SITU(8); break;
+  }
+#undef K3G_RS_SITU
+  return k3g_launch_status();
 }
 
 K3G_API int k3g_land_situ(const void* p, void* act, int n, int B, void* stream) {

@@ -164,8 +164,9 @@ class LayerGlue:
             # Fusions beyond the reference's call list, all with bit-identical outputs:
             #  - the producers leave the maxima a per-tensor quantisation needs, so the three quantisations run
             #    their apply launch only (one pass over each tensor less);
-            #  - the attention reduce-scatter is pulled inside the residual kernel that consumes it, so its HBM
-            #    work hides under the NVLink transfer and the reduce-scattered tensor is never written.
+            #  - the attention reduce-scatter is pulled inside the residual kernel that consumes it and the routed-latent
+            #    reduce-scatter inside the latent norm, so their HBM / special-function work hides under the NVLink
+            #    transfer and the reduce-scattered tensors are never written.
             swap = {
                 "res_in (land_add2 + attnres + rms + push)": ("res_in (land_add2 + attnres + rms + push, row maxima)", lambda: call(
                     "k3g_attnres_rms_push_amax", self.blocks, self.sw, self.gamma, self.normed_all, self.b_normed_all.table, nb, 0, B, r, W,
@@ -178,9 +179,11 @@ class LayerGlue:
                     self.prefix2_next, self.normed, nb, 0, B, H, 1e-5, self.stats, nb, self.rowmax, s())),
                 "normed_quant (fp8 tensor, B rows)": ("normed_quant (fp8 apply only, B rows)", lambda: call(
                     "k3g_quant_fp8_apply", self.normed, self.fp8_small, self.qscale[1:], self.rowmax, B, B * H, 2048, s())),
-                "shared_situ (SiTU landing + latent RMSNorm)": ("shared_situ (SiTU landing + latent RMSNorm, item maxima)", lambda: call(
-                    "k3g_situ_rms_amax", self.shared_partial, self.shared_act, self.routed_latent, self.gamma_lat, self.routed_latent_norm, SHARED,
-                    B, LATENT, B, self.item_max, s())),
+                "scatter_moe (pull RS)": None,
+                "shared_situ (SiTU landing + latent RMSNorm)": ("scatter_moe + shared_situ (pull RS inside the latent RMSNorm, SiTU landing, item maxima)",
+                                                                lambda: call(
+                    "k3g_rs_situ_rms", self.shared_partial, self.shared_act, self.moe_partial, self.b_moe_partial.table, r, W, self.gamma_lat,
+                    self.routed_latent_norm, SHARED, B, LATENT, B, self.item_max, s())),
                 "shared_act_quant (fp8 tensor)": ("shared_act_quant (fp8 apply only)", lambda: call(
                     "k3g_quant_fp8_apply", self.shared_act, self.shared_q, self.qscale[2:], self.item_max, self.item_max.numel(), B * SHARED, 2048,
                     s())),

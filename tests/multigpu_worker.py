@@ -84,6 +84,15 @@ def main():
             o_p2, o_n = k3o.land_add_attnres_rms(want_delta.reshape(rows, H), residual[rank], blocks_h, sw_h, gamma, nb, 0, 1e-5)
             assert np.array_equal(bf16_bits(p2), o_p2) and np.array_equal(bf16_bits(nrm), o_n)
             assert np.array_equal(rowmax.cpu().numpy(), (((o_n & 0x7fff).max(axis=1).astype(np.uint32)) << 16).view(np.float32))
+            # ... and inside the latent norm: the same buffer seen as [world * 2 rows, 3584]
+            L2, h2 = 2 * rows, H // 2
+            gam2 = normal_bf16(rng(6), (h2,), mean=1.0, std=0.02)
+            sp_h = normal_bf16(rng(7000 + rank), (5, 2 * 256), std=3.0)
+            act, ln = torch.zeros((5, 256), dtype=torch.bfloat16, device=dev), torch.zeros((L2, h2), dtype=torch.bfloat16, device=dev)
+            k3g.call("k3g_rs_situ_rms", to_dev_bf16(sp_h, dev), act, part, b_part.table, rank, world, to_dev_bf16(gam2, dev), ln, 256, 5, h2, L2, None, s)
+            torch.cuda.synchronize()
+            o_act, o_ln = k3o.situ_rms(sp_h, want_delta.reshape(L2, h2), gam2, 256, h2)
+            assert np.array_equal(bf16_bits(ln), o_ln)
         # push all-gather of four byte streams with its own barrier tail
         srcs = [torch.from_numpy(rng(50 + rank * 4 + i).integers(0, 256, n, dtype=np.uint8)).to(dev) for i, n in enumerate((rows * 3584, rows * 112, rows * 64, rows * 64))]
         if replay == 0:

@@ -97,3 +97,28 @@ def test_span_state_roundtrip_and_latent_gather(k3g, dev):
         o = table[t // 64] * page_stride + (t % 64) * 576
         want[t] = slab[o:o + 576]
     assert np.array_equal(bf16_bits(out), want)
+
+
+@pytest.mark.parametrize("W,L,h", [(1, 5, 3584), (2, 9, 3584), (4, 13, 3584), (8, 6, 512), (4, 3, 4096)])
+def test_reduce_scatter_folded_into_the_latent_norm(k3g, dev, W, L, h):
+    """k3g_rs_situ_rms == k3g_rs_pull followed by k3g_situ_rms_amax, bit for bit, for every rank of a world emulated
+    on one GPU (data kernels only: nothing waits)."""
+    import torch
+    g = rng(70 + W + L)
+    s = k3g.current_stream()
+    B, n = 7, 6144
+    sp = to_dev_bf16(normal_bf16(g, (B, 2 * n), std=3.0), dev)
+    gam = to_dev_bf16(normal_bf16(g, (h,), mean=1.0, std=0.02), dev)
+    parts = [to_dev_bf16(normal_bf16(g, (W * L, h), std=1.0 / W), dev) for _ in range(W)]
+    tab = torch.tensor([t.data_ptr() for t in parts], dtype=torch.int64, device=dev)
+    items = (B * n + 4095) // 4096
+    for rank in range(W):
+        own = torch.zeros((L, h), dtype=torch.bfloat16, device=dev)
+        k3g.call("k3g_rs_pull", parts[rank], own, tab, L * h, 2 * (W - 1), rank, W, 8, s)
+        act0, act1 = torch.zeros((B, n), dtype=torch.bfloat16, device=dev), torch.zeros((B, n), dtype=torch.bfloat16, device=dev)
+        ln0, ln1 = torch.zeros((L, h), dtype=torch.bfloat16, device=dev), torch.zeros((L, h), dtype=torch.bfloat16, device=dev)
+        m0, m1 = torch.zeros(items, device=dev), torch.zeros(items, device=dev)
+        k3g.call("k3g_situ_rms_amax", sp, act0, own, gam, ln0, n, B, h, L, m0, s)
+        k3g.call("k3g_rs_situ_rms", sp, act1, parts[rank], tab, rank, W, gam, ln1, n, B, h, L, m1, s)
+        torch.cuda.synchronize()
+        assert torch.equal(ln0, ln1) and torch.equal(act0, act1) and torch.equal(m0, m1)

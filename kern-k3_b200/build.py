@@ -3,7 +3,7 @@
   lib/libk3g.so        all sm_100a kernels + the C ABI (include/k3g.h)
   lib/cubin/*.cubin    one module per reference module name: the same `extern "C"` entry
                        names and parameter lists as the reference's cubins, so a manifest's
-                       `modules` table can point at them (see INTEGRATION.md)
+                       `modules` table can point at them
 
 Compilation is plain nvcc for sm_100a only; objects are rebuilt when a source or header is
 newer.  Usage: python kern-k3_b200/build.py [--force] [--verbose] [--no-cubins]

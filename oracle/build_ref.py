@@ -8,7 +8,7 @@ oracle and with this library's kernels, and tests/golden/make_golden.py records 
 outputs as golden vectors.
 
 The reference is device code only (no CPU path), so there is nothing to build for the host.
-Usage: python oracle/build_ref.py [reference_root]   (default /root/reference)
+Usage: python oracle/build_ref.py [reference_root]   (default: K3_REFERENCE_ROOT, else the `reference` directory beside this repository)
 """
 import os
 import subprocess
@@ -16,6 +16,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
+REF_ROOT = os.environ.get("K3_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 # module -> (source relative to the reference root, defines, needs the ulonglong4_16a shim)
 MODULES = {
@@ -45,7 +46,7 @@ MODULES = {
 }
 
 
-def build(ref_root="/root/reference", force=False):
+def build(ref_root=REF_ROOT, force=False):
     """Returns the list of cubins built or already present; [] when the reference is absent."""
     if not os.path.isdir(ref_root):
         return [os.path.join(OUT, f) for f in sorted(os.listdir(OUT))] if os.path.isdir(OUT) else []

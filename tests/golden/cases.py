@@ -3,8 +3,7 @@
 tests/golden/reference_outputs.npz; tests/test_golden.py checks (b) against the record on any
 machine; tests/test_reference_ab.py re-runs (a) live on a GPU box and compares it with this library.
 
-Every case names the reference module / entry / launch dims it uses (manifest geometry, SURVEY.md
-Appendix A).  `exact` lists the outputs that must match bit for bit; the others use approximate
+Every case names the reference module / entry / launch dims it uses (the default manifest's geometry).  `exact` lists the outputs that must match bit for bit; the others use approximate
 device instructions in the reference (rsqrtf, expf, ex2.approx) and are compared at `ulp` bf16 ulps
 on at most `frac` of the elements.
 """

@@ -71,7 +71,7 @@ def test_flag_protocol_world1(k3g, dev):
 
 def test_bounded_wait_reports_and_returns(k3g, dev):
     """Rank 0 of an emulated world of 2 waits on a peer counter that nothing advances: the wait runs
-    out after the 1 ms budget, records {1, slot, peer, observed} and the kernel returns normally."""
+    out after the 1 ms limit, records {1, slot, peer, observed} and the kernel returns normally."""
     import torch
     mine, peer = _flags(dev), _flags(dev)
     tab = _table([mine, peer], dev)

@@ -9,7 +9,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
-REF_MANIFEST = "/root/reference/manifests/k3-tp4-prefill-16k.json"
+REF_MANIFEST = os.path.join(os.environ.get("K3_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference")), "manifests", "k3-tp4-prefill-16k.json")
 
 
 @pytest.fixture(scope="module")

@@ -91,11 +91,18 @@ extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_apply_v2(con
   const int nv = n >> 3;
   const int total = gridDim.x * K3G_QT;
   // backwards: start with the part of x the amax pass touched last
-  for (int i = nv - 1 - (blockIdx.x * K3G_QT + threadIdx.x); i >= 0; i -= total) {
+  for (int i = nv - 1 - (blockIdx.x * K3G_QT + threadIdx.x); i >= 0; i -= 2 * total) {   // two vectors in flight per thread
+    const int i1 = i - total;
     const V8 v = ld_stream(x + (size_t)i * 8);
+    V8 w = v;
+    if (i1 >= 0) w = ld_stream(x + (size_t)i1 * 8);
     unsigned q0, q1;
     quant8(v, inv, q0, q1);
     st_stream8(y + (size_t)i * 8, q0, q1);
+    if (i1 >= 0) {
+      quant8(w, inv, q0, q1);
+      st_stream8(y + (size_t)i1 * 8, q0, q1);
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
     const int i = nv * 8 + threadIdx.x;

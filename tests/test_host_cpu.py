@@ -90,3 +90,28 @@ def test_peer_group_exchange_with_gloo_ranks():
                         "--master-port", "29533", os.path.join(ROOT, "tests", "gloo_worker.py")], capture_output=True, text=True, timeout=300)
     sys.stdout.write(r.stdout[-3000:]); sys.stderr.write(r.stderr[-3000:])
     assert r.returncode == 0 and r.stdout.count("GLOO_OK") == 2
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(tmp_path):
+    """include/k3g.h must be usable from C (what cgo / JNI / any FFI binds): compile a C translation unit that
+    takes the address of every declared entry point with gcc and link it against libk3g.so.  Nothing is launched;
+    the argument-validation path is exercised with a null pointer (rejected before any CUDA call)."""
+    import shutil
+    import subprocess
+    import k3g
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    names = sorted(k3g.PROTOTYPES)
+    src = tmp_path / "abi.c"
+    src.write_text('#include "k3g.h"\n#include <stdio.h>\n'
+                   "static void* table[] = {%s};\n" % ", ".join("(void*)%s" % n for n in names) +
+                   "int main(void) {\n"
+                   "  int rc = k3g_moe_quant(0, 0, 0, 1, 32, 0, 0);          /* null input: K3G_ENULL, no launch */\n"
+                   '  printf("%d %d\\n", (int)(sizeof table / sizeof table[0]), rc);\n'
+                   "  return 0;\n}\n")
+    exe = tmp_path / "abi"
+    libdir = os.path.dirname(k3g.LIB_PATH)
+    subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                           "-L", libdir, "-lk3g", "-Wl,-rpath," + libdir])
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
+    assert int(out[0]) == len(names) and int(out[1]) == -1

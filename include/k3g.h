@@ -254,6 +254,28 @@ int k3g_moe_sf_shuffle(const void* src, void* dst, int experts, int n, int kg, i
  * are the caller's scratch for the two stages. */
 int k3g_argmax_f32(const void* logits, void* pmax, void* pidx, void* out, int B, int n, int parts, void* stream);
 
+/* ---- load-time derived tables (source/k3_weight_prep.cu, source/weight_prep.cu; run once after load) ----------- */
+
+/* kern_fill_bf16 (k3_weight_prep.cu:32), kern_fill_f32 / _i32 / _i64 / _u8 (weight_prep.cu:47-65): p[i] = value, i < n.
+ * kind 0 bf16 (v), 1 f32 (v), 2 i32 (iv), 3 i64 (iv), 4 u8 (iv). */
+int k3g_fill(void* p, long long n, int kind, float v, long long iv, void* stream);
+/* kern_iota_i32, weight_prep.cu:67: p[i * stride] = start + i * step. */
+int k3g_iota_i32(void* p, int n, int start, int step, int stride, void* stream);
+/* kern_cast_bf16_f32 / kern_weight_p1_bf16_f32, weight_prep.cu:24-32: out[i] = f32(w[i]) (+ 1 when plus_one). */
+int k3g_cast_bf16_f32(const void* w, void* out, int n, int plus_one, void* stream);
+/* kern_rope_table_bf16, weight_prep.cu:34: cos / sin [rows][stride], columns j < half: angle = r / base^(j / half). */
+int k3g_rope_table(void* cos_t, void* sin_t, int rows, int half, int stride, float base, void* stream);
+/* kern_k3_conv_taps, k3_weight_prep.cu:37: cw [3][4][inner] f32 from the q, k, v conv weights [inner][4] f32. */
+int k3g_conv_taps(const void* q, const void* k, const void* v, void* cw, int inner, void* stream);
+/* kern_k3_scoring, k3_weight_prep.cu:48: sw[j] = f32(norm[j]) * f32(proj[j]). */
+int k3g_scoring(const void* norm, const void* proj, void* sw, int n, void* stream);
+/* kern_k3_wsm, k3_weight_prep.cu:54: [256, h] block, rows 0..heads = b, rows 96..224 = f_a, others zero. */
+int k3g_wsm(const void* b, const void* f_a, void* wsm, int heads, int h, void* stream);
+/* kern_k3_mega_sf_pack, k3_weight_prep.cu:71: scale bytes [experts][n][kg] -> i32 [experts][kg / 4][n], rows permuted. */
+int k3g_mega_sf_pack(const void* raw, void* out, int experts, int n, int kg, int interleave, void* stream);
+/* kern_k3_kvb_aug, k3_weight_prep.cu:81: [heads * 320, 576] expansion weight from kv_b_proj [heads * 256, 512]. */
+int k3g_kvb_aug(const void* w_kv_b, void* out, int heads, void* stream);
+
 /* ---- once-per-prefill helpers (byte movement) ---------------------------------------------------------- */
 
 /* kern_k3_rank_rows, source/k3_prefill.cu:28 (op rank_rows): dst[j] = src[min(rank * own + j, rows - 1)], j < own. */

@@ -24,7 +24,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr"]
 
 SOURCES = ["resnorm.cu", "quant.cu", "router.cu", "moe_route.cu", "collectives.cu", "mla_prep.cu", "kda.cu",
-           "peer.cu", "quant_noalloc.cu", "glue_small.cu", "prefill_misc.cu"]
+           "peer.cu", "quant_noalloc.cu", "glue_small.cu", "prefill_misc.cu", "weight_prep.cu"]
 
 # reference module name -> (source, defines).  Names follow kernels.toml of the reference.
 CUBINS = {
@@ -50,6 +50,8 @@ CUBINS = {
     "k3_prefill": ("prefill_misc.cu", []),
     "embedding": ("prefill_misc.cu", []),
     "copy_rows": ("prefill_misc.cu", []),
+    "k3_weight_prep": ("weight_prep.cu", []),
+    "weight_prep": ("weight_prep.cu", []),
     "sigmoid_mul": ("glue_small.cu", []),
     "k3_span_state+HEADS=24": ("glue_small.cu", ["-DHEADS=24"]),
     "k3_mla_v2": ("glue_small.cu", []),

@@ -8,8 +8,7 @@ Every launch whose (module, entry) pair this library provides is moved to a new 
 list and the argument mapping are left untouched, because the kernels take exactly the reference's
 parameters.  Launch dims are kept unless this library has a better geometry for the kernel (all
 kernels are grid-stride, so the reference's dims stay valid); `--keep-grids` disables the overrides.
-Launches of kernels outside the glue path (GEMM, FMHA, FlashKDA, load-time weight preparation) are not
-touched.  Prints a summary; exits non-zero if a provided entry is missing from its cubin.
+Launches of kernels outside the glue path (GEMM, grouped GEMM, FMHA, FlashKDA) are not touched.  Prints a summary; exits non-zero if a provided entry is missing from its cubin.
 """
 import argparse
 import hashlib
@@ -41,6 +40,9 @@ PROVIDED = {
     "k3_prefill": ("k3_prefill", ["kern_k3_rank_rows", "kern_k3_zero_rows", "kern_k3_fmha_lens"]),
     "embedding": ("embedding", ["kern_embedding_i64_bf16"]),
     "copy_rows": ("copy_rows", ["kern_copy_rows_bf16", "kern_last_row_bf16", "kern_own_rows"]),
+    "k3_weight_prep": ("k3_weight_prep", ["kern_fill_bf16", "kern_k3_conv_taps", "kern_k3_scoring", "kern_k3_wsm", "kern_k3_mega_sf_pack", "kern_k3_kvb_aug"]),
+    "weight_prep": ("weight_prep", ["kern_weight_p1_bf16_f32", "kern_cast_bf16_f32", "kern_rope_table_bf16", "kern_fill_f32", "kern_fill_i32",
+                                    "kern_fill_i64", "kern_fill_u8", "kern_iota_i32"]),
     "k3_collectives": ("k3_collectives", ["kern_k3_flags_init", "kern_k3_epoch_bump"]),
     "k3_rs_arrive_v2": ("k3_rs_arrive_v2", ["kern_k3_rs_arrive1"]),
     "k3_reducescatter_pull_nr4": ("k3_reducescatter_pull_nr4", ["kern_k3_rs_pull"]),

@@ -39,6 +39,8 @@ MODULES = {
     "k3_prefill": ("source/k3_prefill.cu", [], False),
     "embedding": ("source/embedding.cu", [], False),
     "copy_rows": ("source/copy_rows.cu", [], False),
+    "k3_weight_prep": ("source/k3_weight_prep.cu", [], False),
+    "weight_prep": ("source/weight_prep.cu", [], False),
     "k3_residual_push_v3": ("source/k3_residual_push_v3.cu", [], False),
     "sigmoid_mul": ("source/sigmoid_mul.cu", [], False),
     "k3_span_gather_v3+HEADS=24": ("source/k3_span_gather_v3.cu", ["-DHEADS=24"], False),

@@ -366,5 +366,55 @@ def moe_sf_shuffle(src, gated):
     return out.reshape(experts, n, kg)
 
 
+# ---- load-time derived tables (source/k3_weight_prep.cu, source/weight_prep.cu) ------------------------------
+def rope_table(rows, half, base):
+    """kern_rope_table_bf16 (source/weight_prep.cu:34-45): f32 arithmetic as written, landed to bf16 (cos, sin)."""
+    j = np.arange(half, dtype=np.float32)
+    inv = (np.float32(1.0) / np.power(np.float32(base), (np.float32(2.0) * j) / np.float32(2 * half), dtype=np.float32)).astype(np.float32)
+    ang = (np.arange(rows, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    return f32_to_bf16(np.cos(ang.astype(np.float64)).astype(np.float32)), f32_to_bf16(np.sin(ang.astype(np.float64)).astype(np.float32))
+
+
+def conv_taps(q, k, v):
+    """kern_k3_conv_taps (source/k3_weight_prep.cu:37-46): [inner, 4] x 3 -> [3, 4, inner]."""
+    return np.ascontiguousarray(np.stack([q, k, v]).transpose(0, 2, 1))
+
+
+def scoring(norm, proj):
+    """kern_k3_scoring (source/k3_weight_prep.cu:48-52)."""
+    return (bf16_to_f32(norm) * bf16_to_f32(proj)).astype(np.float32)
+
+
+def wsm(b, f_a, heads):
+    """kern_k3_wsm (source/k3_weight_prep.cu:54-60)."""
+    h = b.shape[1]
+    out = np.zeros((256, h), np.uint16)
+    out[:heads] = b[:heads]
+    out[96:224] = f_a[:128]
+    return out
+
+
+def mega_sf_pack(raw, interleave):
+    """kern_k3_mega_sf_pack (source/k3_weight_prep.cu:62-79): raw [experts, n, kg] u8 -> i32 [experts, kg / 4, n]."""
+    experts, n, kg = raw.shape
+    r = np.arange(n)
+    u = (r // 128) * 128 + (r % 4) * 32 + (r % 128) // 4
+    src = np.where((u >> 3) & 1 == 1, n // 2, 0) + (u >> 4) * 8 + (u & 7) if interleave else u
+    words = np.ascontiguousarray(raw[:, src, :]).view("<u4")            # [experts, n, kg / 4], LSB-first bytes
+    return np.ascontiguousarray(words.transpose(0, 2, 1)).view(np.int32)
+
+
+def kvb_aug(w_kv_b, heads):
+    """kern_k3_kvb_aug (source/k3_weight_prep.cu:81-93): [heads * 256, 512] bf16 -> [heads * 320, 576] bf16."""
+    w = w_kv_b.reshape(heads, 256, 512)
+    out = np.zeros((heads, 320, 576), np.uint16)
+    out[:, :128, :512] = w[:, :128]
+    out[:, 192:, :512] = w[:, 128:]
+    one = f32_to_bf16(np.ones(1, np.float32))[0]
+    for d in range(64):
+        out[:, 128 + d, 512 + d] = one
+    return out.reshape(heads * 320, 576)
+
+
 def num_threads():
     return int(lib().k3o_num_threads())

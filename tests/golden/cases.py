@@ -25,7 +25,7 @@ def _bf(g, shape, mean=0.0, std=1.0):
 def inputs(name):
     g = _g({"k1b_nb0": 1, "k1b_nb3": 2, "k1a_nb2": 3, "k1c": 4, "moe_quant": 5, "quant_pair": 6, "router": 7, "route": 8, "rs_pull": 9,
             "mla_prep": 10, "span_gather": 11, "out_gate": 12, "push_add2": 13, "situ_rms": 14, "sigmoid_mul": 15,
-            "land_situ": 16, "rms": 17, "argmax": 18, "push_first": 19, "copies": 20, "moe_shuffle": 21}[name])
+            "land_situ": 16, "rms": 17, "argmax": 18, "push_first": 19, "copies": 20, "moe_shuffle": 21, "weight_prep": 22}[name])
     H = 7168
     if name in ("k1b_nb0", "k1b_nb3", "k1a_nb2"):
         B = 3
@@ -53,6 +53,10 @@ def inputs(name):
         B = 3
         return dict(prefix=_bf(g, (B, H)), blocks=_bf(g, (B, 8, H)), sw=(g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32),
                     gamma=_bf(g, (H,), 1.0, 0.02))
+    if name == "weight_prep":
+        return dict(q=g.standard_normal((256, 4), dtype=np.float32), k=g.standard_normal((256, 4), dtype=np.float32),
+                    v=g.standard_normal((256, 4), dtype=np.float32), norm=_bf(g, (512,)), proj=_bf(g, (512,)), b=_bf(g, (24, 64)), fa=_bf(g, (128, 64)),
+                    raw=g.integers(0, 256, (2, 256, 8), dtype=np.uint8), wkv=_bf(g, (2 * 256, 512)))
     if name == "moe_shuffle":
         return dict(w=g.integers(0, 256, (3, 128, 48), dtype=np.uint8), sf=g.integers(0, 256, (3, 256, 12), dtype=np.uint8))
     if name == "copies":
@@ -96,12 +100,13 @@ def inputs(name):
     raise KeyError(name)
 
 
-NAMES = ["moe_shuffle", "land_situ", "rms", "argmax", "push_first", "copies", "situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
+NAMES = ["weight_prep", "moe_shuffle", "land_situ", "rms", "argmax", "push_first", "copies", "situ_rms", "sigmoid_mul", "push_add2", "k1b_nb0", "k1b_nb3", "k1a_nb2", "k1c", "moe_quant", "quant_pair", "router", "route", "rs_pull", "mla_prep", "span_gather", "out_gate"]
 
 # outputs that must be bit-identical between the reference cubin and the CPU oracle
 EXACT = {
     "land_situ": [], "rms": [], "argmax": ["out"], "push_first": ["blocks"],
     "copies": ["rank_rows", "zero_rows", "lens", "embedding", "last_row"], "moe_shuffle": ["w_plain", "w_gated", "sf_plain", "sf_gated"],
+    "weight_prep": ["cw", "sw", "wsm", "sf_pack", "sf_pack_interleaved", "kvb_aug"],
     "situ_rms": [], "sigmoid_mul": [],
     "push_add2": ["hidden", "blocks", "res_mlp_prefix2"],
     "k1b_nb0": ["prefix2"], "k1b_nb3": ["prefix2"], "k1a_nb2": ["blocks"], "k1c": ["hidden"], "moe_quant": ["q", "sf"],
@@ -111,6 +116,7 @@ EXACT = {
 }
 # bf16 outputs compared at tolerance: name -> (max ulp, max fraction of differing elements)
 TOLERANT = {
+    "weight_prep": {"cos": (1, 0.05), "sin": (1, 0.05)},
     "land_situ": {"act": (2, 0.2)}, "rms": {"o": (1, 2e-3)}, "push_first": {"normed_all": (1, 2e-3)},
     "situ_rms": {"act": (2, 0.2), "ln": (1, 2e-3)}, "sigmoid_mul": {"out": (1, 5e-3)},
     "push_add2": {"normed_all": (4, 5e-3), "res_mlp_normed": (4, 5e-3)},   # mixed rows: a cancelling mix amplifies the 1e-7 softmax difference
@@ -139,6 +145,11 @@ def run_oracle(name, inp):
         normed_all = np.zeros((4 * B, H), np.uint16)
         normed_all[B:2 * B] = normed
         return dict(blocks=blocks, normed_all=normed_all)
+    if name == "weight_prep":
+        cos, sin = k3o.rope_table(64, 32, 50000.0)
+        return dict(cw=k3o.conv_taps(inp["q"], inp["k"], inp["v"]), sw=k3o.scoring(inp["norm"], inp["proj"]), wsm=k3o.wsm(inp["b"], inp["fa"], 24),
+                    sf_pack=k3o.mega_sf_pack(inp["raw"], 0), sf_pack_interleaved=k3o.mega_sf_pack(inp["raw"], 1), kvb_aug=k3o.kvb_aug(inp["wkv"], 2),
+                    cos=cos, sin=sin)
     if name == "moe_shuffle":
         return dict(w_plain=k3o.moe_w_shuffle(inp["w"], 0), w_gated=k3o.moe_w_shuffle(inp["w"], 1),
                     sf_plain=k3o.moe_sf_shuffle(inp["sf"], 0), sf_gated=k3o.moe_sf_shuffle(inp["sf"], 1))

@@ -68,6 +68,27 @@ def run_reference(name, inp, dev):
         for o in others:
             assert torch.equal(o, normed_all)
         return dict(blocks=_bits(blocks), normed_all=_bits(normed_all))
+    if name == "weight_prep":
+        cw = z((3, 4, 256), torch.float32)
+        refcubin.run("k3_weight_prep", "kern_k3_conv_taps", 1, 256, [_up(inp["q"], dev), _up(inp["k"], dev), _up(inp["v"], dev), cw, 256])
+        sw = z((512,), torch.float32)
+        refcubin.run("k3_weight_prep", "kern_k3_scoring", 2, 256, [_up(inp["norm"], dev), _up(inp["proj"], dev), sw, 512])
+        wsm = z((256, 64), bf)
+        refcubin.run("k3_weight_prep", "kern_k3_wsm", 64, 256, [_up(inp["b"], dev), _up(inp["fa"], dev), wsm, 24, 64])
+        raw = _up(inp["raw"], dev)
+        packs = []
+        for il in (0, 1):
+            o = z((2, 2, 256), torch.int32)
+            refcubin.run("k3_weight_prep", "kern_k3_mega_sf_pack", 4, 256, [raw, o, 2, 256, 8, il])
+            packs.append(o)
+        aug = z((2 * 320, 576), bf)
+        refcubin.run("k3_weight_prep", "kern_k3_kvb_aug", (2 * 320 * 576 + 255) // 256, 256, [_up(inp["wkv"], dev), aug, 2 * 320 * 576])
+        cs = z((64, 64), bf)
+        refcubin.run("weight_prep", "kern_rope_table_bf16", 64, 32, [cs, cs.view(-1)[32:], 64, 32, 64, 50000.0])
+        torch.cuda.synchronize()
+        csb = _bits(cs)
+        return dict(cw=cw.cpu().numpy(), sw=sw.cpu().numpy(), wsm=_bits(wsm), sf_pack=packs[0].cpu().numpy(), sf_pack_interleaved=packs[1].cpu().numpy(),
+                    kvb_aug=_bits(aug), cos=np.ascontiguousarray(csb[:, :32]), sin=np.ascontiguousarray(csb[:, 32:]))
     if name == "moe_shuffle":
         w, sf = _up(inp["w"], dev), _up(inp["sf"], dev)
         res = {}

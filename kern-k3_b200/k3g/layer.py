@@ -64,7 +64,7 @@ class LayerGlue:
         # per-tensor fp8 operands
         self.fp8_big = torch.empty((T, H), dtype=torch.uint8, device=dev)
         self.fp8_small = torch.empty((B, H), dtype=torch.uint8, device=dev)
-        self.qpart = torch.empty(2048, dtype=torch.float32, device=dev); self.qscale = torch.empty(4, dtype=torch.float32, device=dev)
+        self.qpart = torch.zeros(2048, dtype=torch.float32, device=dev); self.qscale = torch.zeros(4, dtype=torch.float32, device=dev)
         self.shared_partial = rnd(B, 2 * SHARED, std=2.0); self.shared_act = torch.empty((B, SHARED), dtype=bf, device=dev)
         self.shared_q = torch.empty((B, SHARED), dtype=torch.uint8, device=dev)
         self.gamma_lat = self.gamma[:LATENT].contiguous(); self.routed_latent_norm = torch.empty((B, LATENT), dtype=bf, device=dev)

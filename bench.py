@@ -400,6 +400,7 @@ def run_gpu(args, rank, world, local_rank):
     roof = {"bound": "hbm", "kernel": "rs_resnorm_mxfp8_ag_kernel", "achieved": round(alg_hbm / kern_us / 1e3, 1), "peak": peak_gbs, "unit": "GB/s",
             "frac": round(alg_hbm / kern_us / 1e3 / peak_gbs, 4), "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_W1 if W == 1 else None,
             "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, profiles/rs_resnorm_mxfp8_ag_kernel_config1_world1.md" if W == 1 else None,
+            "note": None if W == 1 else "at world > 1 the kernel is NVLink-bound, not HBM-bound: the nvlink object carries its achieved / peak figures",
             "kernel_us": round(kern_us, 2),
             "algorithmic_bytes_per_launch": alg_hbm}
     nv = None

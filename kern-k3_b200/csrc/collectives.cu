@@ -334,6 +334,52 @@ __global__ void __launch_bounds__(1024) allgather4_kernel(const unsigned char* s
                   status ? status : g_wait_status);
 }
 
+// MXFP8 quantisation of this rank's latent rows written straight into every rank's gathered buffers, then two plain
+// payloads (the router's indices and weights) and the barrier tail: kern_k3_moe_quant + kern_k3_allgather4_push in one
+// launch (the codes are never written locally and read back).  One 32-element group per thread-step, as kern_k3_moe_quant.
+__global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bfloat16* __restrict__ x, long long ngroups, unsigned char* q_all,
+                                                                   const unsigned long long* __restrict__ q_peer, unsigned char* sf_all,
+                                                                   const unsigned long long* __restrict__ sf_peer, const unsigned char* s2,
+                                                                   unsigned char* d2, const unsigned long long* p2, long long n2,
+                                                                   const unsigned char* s3, unsigned char* d3, const unsigned long long* p3,
+                                                                   long long n3, unsigned long long* flags, const unsigned long long* flags_peer,
+                                                                   int slot, int rank, int nranks, long long timeout_ns, unsigned* status) {
+  const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+  for (long long g = tid; g < ngroups; g += stride) {
+    const __nv_bfloat16* src = x + g * 32;
+    V8 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = ld_plain(src + 8 * j);
+    unsigned am = absmax8(v[0]);
+#pragma unroll
+    for (int j = 1; j < 4; ++j) am = max_bf16_bits(am, absmax8(v[j]));
+    const int e = ue8m0_exp_from_bf16(am);
+    const float sc = pow2_neg(e);
+    V8 o0, o1;
+    quant8(v[0], sc, o0.w[0], o0.w[1]);
+    quant8(v[1], sc, o0.w[2], o0.w[3]);
+    quant8(v[2], sc, o1.w[0], o1.w[1]);
+    quant8(v[3], sc, o1.w[2], o1.w[3]);
+    const long long at = (long long)rank * ngroups + g;          // group index in the gathered buffers
+    st_plain(q_all + at * 32, o0);
+    st_plain(q_all + at * 32 + 16, o1);
+    sf_all[at] = (unsigned char)(e + 127);
+#pragma unroll
+    for (int q = 0; q < K3G_MAX_RANKS; ++q) {
+      if (q < nr && q != rank) {
+        unsigned char* qd = reinterpret_cast<unsigned char*>(q_peer[q]);
+        st_stream(qd + at * 32, o0);
+        st_stream(qd + at * 32 + 16, o1);
+        reinterpret_cast<unsigned char*>(sf_peer[q])[at] = (unsigned char)(e + 127);
+      }
+    }
+  }
+  if (n2 > 0) push_span(s2, d2, p2, n2, rank, nr, tid, stride);
+  if (n3 > 0) push_span(s3, d3, p3, n3, rank, nr, tid, stride);
+  block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status ? status : g_wait_status);
+}
+
 }  // namespace
 
 // ---- manifest entry points -------------------------------------------------------------------------
@@ -452,6 +498,33 @@ K3G_API int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long l
       (const unsigned long long*)p1, n1, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2,
       (const unsigned char*)s3, (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags,
       (const unsigned long long*)flags_peer, slot, rank, nranks, timeout_us * 1000LL, (unsigned*)status);
+  return k3g_launch_status();
+}
+
+// kern_k3_moe_quant followed by kern_k3_allgather4_push in one launch (no counterpart in the reference): the MXFP8 codes
+// and scale bytes of x [rows, cols] bf16 go straight to rows rank * rows .. of every rank's q_all [nranks * rows, cols] /
+// sf_all [nranks * rows, cols / 32]; two more byte payloads (s2 -> d2, s3 -> d3: the router's indices and weights) are
+// gathered as by k3g_allgather4_push, and the same barrier tail follows.  Gathered bytes identical to the two calls.
+K3G_API int k3g_moe_quant_allgather_push(const void* x, int rows, int cols, void* q_all, const void* q_peer, void* sf_all, const void* sf_peer,
+                                         const void* s2, void* d2, const void* p2, long long n2, const void* s3, void* d3, const void* p3,
+                                         long long n3, void* flags, const void* flags_peer, int slot, int rank, int nranks, int units,
+                                         long long timeout_us, void* status, void* stream) {
+  K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(q_all); K3G_REQUIRE_PTR(q_peer); K3G_REQUIRE_PTR(sf_all); K3G_REQUIRE_PTR(sf_peer);
+  K3G_REQUIRE_PTR(flags); K3G_REQUIRE_PTR(flags_peer);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE_ALIGNED(q_all);
+  K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0 && nranks >= 1 && nranks <= K3G_MAX_RANKS && units > 0, K3G_ESHAPE);
+  K3G_REQUIRE(rank >= 0 && rank < nranks && slot >= 1 && timeout_us > 0, K3G_ERANGE);
+  const void* ss[2] = {s2, s3}; void* dd[2] = {d2, d3}; const void* pp[2] = {p2, p3};
+  const long long nn[2] = {n2, n3};
+  for (int i = 0; i < 2; ++i) {
+    K3G_REQUIRE(nn[i] >= 0 && nn[i] % 16 == 0, K3G_ESHAPE);
+    if (nn[i] > 0) { K3G_REQUIRE_PTR(ss[i]); K3G_REQUIRE_PTR(dd[i]); K3G_REQUIRE_PTR(pp[i]); K3G_REQUIRE_ALIGNED(ss[i]); K3G_REQUIRE_ALIGNED(dd[i]); }
+  }
+  moe_quant_allgather_kernel<<<units, 1024, 0, k3g_stream(stream)>>>(
+      (const __nv_bfloat16*)x, (long long)rows * cols / 32, (unsigned char*)q_all, (const unsigned long long*)q_peer, (unsigned char*)sf_all,
+      (const unsigned long long*)sf_peer, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2, (const unsigned char*)s3,
+      (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags, (const unsigned long long*)flags_peer, slot, rank, nranks,
+      timeout_us * 1000LL, (unsigned*)status);
   return k3g_launch_status();
 }
 

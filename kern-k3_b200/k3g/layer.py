@@ -164,6 +164,8 @@ class LayerGlue:
             # Fusions beyond the reference's call list, all with bit-identical outputs:
             #  - the producers leave the maxima a per-tensor quantisation needs, so the three quantisations run
             #    their apply launch only (one pass over each tensor less);
+            #  - the latent MXFP8 quantisation writes straight into every rank's gathered buffers (one launch with the
+            #    small all-gather);
             #  - the attention reduce-scatter is pulled inside the residual kernel that consumes it and the routed-latent
             #    reduce-scatter inside the latent norm, so their HBM / special-function work hides under the NVLink
             #    transfer and the reduce-scattered tensors are never written.
@@ -179,6 +181,12 @@ class LayerGlue:
                     self.prefix2_next, self.normed, nb, 0, B, H, 1e-5, self.stats, nb, self.rowmax, s())),
                 "normed_quant (fp8 tensor, B rows)": ("normed_quant (fp8 apply only, B rows)", lambda: call(
                     "k3g_quant_fp8_apply", self.normed, self.fp8_small, self.qscale[1:], self.rowmax, B, B * H, 2048, s())),
+                "moe_quant (MXFP8 latent)": None,
+                "gather_small (AG4 push + barrier)": ("moe_quant + gather_small (MXFP8 written straight into every rank's gathered buffers + barrier)",
+                                                      lambda: call(
+                    "k3g_moe_quant_allgather_push", self.latent, B, LATENT, self.latent_q_all, self.b_lq.table, self.latent_sf_all, self.b_lsf.table,
+                    self.idx, self.idx_all, self.b_idx.table, B * TOPK * 4, self.wts, self.wts_all, self.b_w.table, B * TOPK * 4, fl, ft, 3, r, W, un,
+                    to, st, s())),
                 "scatter_moe (pull RS)": None,
                 "shared_situ (SiTU landing + latent RMSNorm)": ("scatter_moe + shared_situ (pull RS inside the latent RMSNorm, SiTU landing, item maxima)",
                                                                 lambda: call(

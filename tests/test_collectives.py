@@ -227,3 +227,37 @@ def test_glue_step_host_paths_agree(k3g, dev):
         assert np.array_equal(bf16_bits(ho), want_res), mode
         assert np.array_equal(hq.numpy(), want_q) and np.array_equal(hs.numpy(), want_sf), mode
     glue.close()
+
+
+@pytest.mark.parametrize("W", [1, 2, 4, 8])
+def test_moe_quant_allgather_push_emulated(k3g, dev, W):
+    """One launch == k3g_moe_quant followed by k3g_allgather4_push: identical gathered codes, scales and payloads on every
+    rank (ranks emulated on one GPU with the epoch at 0, so nothing waits)."""
+    import torch
+    g = rng(40 + W)
+    rows, cols = 19, 3584
+    xs = [to_dev_bf16(normal_bf16(g, (rows, cols), std=3.0), dev) for _ in range(W)]
+    pay = [[to_dev(g.integers(0, 256, rows * 64, dtype=np.uint8), dev) for _ in range(2)] for _ in range(W)]
+    q_all = [torch.zeros((W * rows, cols), dtype=torch.uint8, device=dev) for _ in range(W)]
+    sf_all = [torch.zeros((W * rows, cols // 32), dtype=torch.uint8, device=dev) for _ in range(W)]
+    d2 = [torch.zeros(W * rows * 64, dtype=torch.uint8, device=dev) for _ in range(W)]
+    d3 = [torch.zeros(W * rows * 64, dtype=torch.uint8, device=dev) for _ in range(W)]
+    tq, tsf, t2, t3 = _table(q_all, dev), _table(sf_all, dev), _table(d2, dev), _table(d3, dev)
+    flags = [_flags(dev) for _ in range(W)]
+    ftab = _table(flags, dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    s = k3g.current_stream()
+    want_q, want_sf = [], []
+    for r in range(W):
+        k3g.call("k3g_moe_quant_allgather_push", xs[r], rows, cols, q_all[r], tq, sf_all[r], tsf, pay[r][0], d2[r], t2, rows * 64, pay[r][1], d3[r], t3,
+                 rows * 64, flags[r], ftab, 2, r, W, 13, 1000, status, s)
+        q, sf = torch.zeros((rows, cols), dtype=torch.uint8, device=dev), torch.zeros((rows, cols // 32), dtype=torch.uint8, device=dev)
+        k3g.call("k3g_moe_quant", xs[r], q, sf, rows, cols, 0, s)
+        want_q.append(q); want_sf.append(sf)
+    torch.cuda.synchronize()
+    assert not status.cpu().numpy().any()
+    want_q, want_sf = torch.cat(want_q), torch.cat(want_sf)
+    for r in range(W):
+        assert torch.equal(q_all[r], want_q) and torch.equal(sf_all[r], want_sf)
+        assert torch.equal(d2[r], torch.cat([pay[k][0] for k in range(W)])) and torch.equal(d3[r], torch.cat([pay[k][1] for k in range(W)]))
+    assert all(int(f[2]) == 13 for f in flags)

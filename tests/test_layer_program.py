@@ -10,7 +10,7 @@ sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
 
 pytestmark = pytest.mark.gpu
 
-OUTPUTS = ["hidden", "normed_all", "fp8_big", "qscale", "prefix2_next", "normed", "fp8_small", "idx", "wts", "latent_q", "latent_sf", "latent_q_all",
+OUTPUTS = ["hidden", "normed_all", "fp8_big", "qscale", "prefix2_next", "normed", "fp8_small", "idx", "wts", "latent_q_all", "latent_sf_all", "wts_all",
            "idx_all", "route_map", "exp2perm", "moe_partial", "routed_latent_norm", "shared_act", "shared_q", "stats", "blocks"]
 
 

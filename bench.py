@@ -196,21 +196,21 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     idx = torch.empty((T, 8), dtype=torch.int32, device=dev); wts = torch.empty((T, 8), dtype=torch.float32, device=dev)
     add("config2 router_topk 16384x224 k=8", lambda: k3g.call("k3g_router_topk", S, bias, rs, idx, wts, T, 224, 8, s), T * 224 * 4 + T * 8 * 8)
     torch.cuda.synchronize()
-    ids64 = (idx % 64).contiguous()     # one rank's 64 local experts stand in for EP = 1 (tables are per rank)
+    NE = 224                           # EP = 1: all 224 experts are local (wide routing kernels)
     blocks = T // 256
-    bc = torch.zeros((blocks, 64), dtype=torch.int32, device=dev); bo = torch.zeros_like(bc)
+    bc = torch.zeros((blocks, NE), dtype=torch.int32, device=dev); bo = torch.zeros_like(bc)
     tile = 128                         # the reference's CTA tile: offsets padded to 128 rows per expert
-    nct = T * 8 // tile + 64
+    nct = T * 8 // tile + NE
     cb = torch.zeros(nct, dtype=torch.int32, device=dev); cl = torch.zeros_like(cb); nne = torch.zeros(1, dtype=torch.int32, device=dev)
     tot = torch.zeros(1, dtype=torch.int32, device=dev); rm = torch.zeros(nct * tile, dtype=torch.int32, device=dev)
     e2p = torch.zeros((T, 8), dtype=torch.int32, device=dev)
 
     def route():
-        k3g.call("k3g_moe_route_count", ids64, T, 0, 64, 8, 1, 0, bc, s)
-        k3g.call("k3g_moe_route_tables", bc, blocks, 64, tile, bo, cb, cl, nne, tot, rm, s)
-        k3g.call("k3g_moe_route_scatter", ids64, bo, T, 0, 64, 8, 1, 0, rm, e2p, s)
+        k3g.call("k3g_moe_route_count", idx, T, 0, NE, 8, 1, 0, bc, s)
+        k3g.call("k3g_moe_route_tables", bc, blocks, NE, tile, bo, cb, cl, nne, tot, rm, s)
+        k3g.call("k3g_moe_route_scatter", idx, bo, T, 0, NE, 8, 1, 0, rm, e2p, s)
     route()
-    add("config2 route count+tables+scatter (3 launches)", route, T * 8 * 4 * 4)
+    add("config2 route count+tables+scatter (3 launches), EP=1: 224 local experts", route, T * 8 * 4 * 4)
     torch.cuda.synchronize()
     rows = int(tot.item())             # tile-padded permuted rows (padding rows route token 0)
     pq = torch.empty((rows, H), dtype=torch.uint8, device=dev); psf = torch.empty((rows, H // 32), dtype=torch.uint8, device=dev)

@@ -144,8 +144,10 @@ int k3g_quant_fp8_tensor_noalloc(const void* x, void* y, void* scale_out, int n,
 int k3g_router_topk(const void* S, const void* bias, const void* rs, void* idx, void* wts, int B, int experts,
                     int topk, void* stream);
 
-/* kern_k3_moe_route_count, source/k3_moe_prefill_v4.cu:142 (op moe_route_count).  E local experts;
- * placement strided (id % ep_ranks == rank, slot id / ep_ranks) or blocked (source :100-109). */
+/* kern_k3_moe_route_count, source/k3_moe_prefill_v4.cu:142 (op moe_route_count).  E local experts (up to 256: the
+ * drop-in kernels cover 64, as the reference's 56; expert-parallel groups of 1 or 2 -- 224 / 112 local experts -- take
+ * wider kernels behind the same three calls); placement strided (id % ep_ranks == rank, slot id / ep_ranks) or
+ * blocked (source :100-109). */
 int k3g_moe_route_count(const void* ids, int T, int rank, int E, int topk, int ep_ranks, int strided, void* blockcount,
                         void* stream);
 

@@ -22,7 +22,8 @@ using namespace k3g;
 
 namespace {
 
-constexpr int kMaxE = 64;          // local experts per rank (224 / 4 = 56 in the reference deployment)
+constexpr int kMaxE = 64;          // local experts per rank of the drop-in kernels (224 / 4 = 56 in the reference deployment)
+constexpr int kMaxEWide = 256;     // C-ABI kernels for expert-parallel groups of 1 or 2 (224 / 112 local experts)
 constexpr int kRouteBlock = 256;   // tokens per routing block
 constexpr int kMaxTopk = 16;
 constexpr int kMaxGroups = kRouteBlock * kMaxTopk / 32;   // 128 groups of 32 expanded ids
@@ -37,9 +38,10 @@ __device__ __forceinline__ int local_expert(int id, int rank, int E, int ep_rank
   return (e >= 0 && e < E) ? e : -1;
 }
 
+template <int MAXE = kMaxE>
 __device__ __forceinline__ void route_count_body(const int* __restrict__ ids, int T, int rank, int E, int topk, int ep_ranks,
                                                  int strided, int* __restrict__ blockcount) {
-  __shared__ int cnt[kMaxE];
+  __shared__ int cnt[MAXE];
   for (int b = blockIdx.x; b * kRouteBlock < T; b += gridDim.x) {
     if (threadIdx.x < E) cnt[threadIdx.x] = 0;
     __syncthreads();
@@ -55,11 +57,12 @@ __device__ __forceinline__ void route_count_body(const int* __restrict__ ids, in
   }
 }
 
+template <int MAXE = kMaxE>
 __device__ __forceinline__ void route_tables_body(const int* __restrict__ blockcount, int blocks, int E, int tile,
                                                   int* __restrict__ blockoff, int* __restrict__ cta_batch, int* __restrict__ cta_limit,
                                                   int* __restrict__ num_non_exiting, int* __restrict__ total_padded,
                                                   int* __restrict__ route_map) {
-  __shared__ int count[kMaxE], off[kMaxE + 1];
+  __shared__ int count[MAXE], off[MAXE + 1];
   // count[e]: one warp per expert, lanes over blocks (integer sums: order-free)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarps) {
@@ -69,19 +72,28 @@ __device__ __forceinline__ void route_tables_body(const int* __restrict__ blockc
     if (lane == 0) count[e] = run;
   }
   __syncthreads();
-  if (warp == 0) {   // exclusive scan of ceil(count / tile) over up to 64 experts: two per lane
-    const int e0 = 2 * lane, e1 = 2 * lane + 1;
-    const int c0 = e0 < E ? (count[e0] + tile - 1) / tile : 0;
-    const int c1 = e1 < E ? (count[e1] + tile - 1) / tile : 0;
-    int incl = c0 + c1;
+  if (warp == 0) {   // exclusive scan of ceil(count / tile) over up to MAXE experts: MAXE / 32 consecutive experts per lane
+    constexpr int PER = MAXE / 32;
+    int c[PER], mine = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = PER * lane + j;
+      c[j] = e < E ? (count[e] + tile - 1) / tile : 0;
+      mine += c[j];
+    }
+    int incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int v = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += v;
     }
-    const int excl = incl - (c0 + c1);
-    if (e0 < E) off[e0] = excl;
-    if (e1 < E) off[e1] = excl + c0;
+    int run = incl - mine;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = PER * lane + j;
+      if (e < E) off[e] = run;
+      run += c[j];
+    }
     const int total = __shfl_sync(0xffffffffu, incl, 31);
     if (lane == 0) {
       off[E] = total;
@@ -117,29 +129,30 @@ __device__ __forceinline__ void route_tables_body(const int* __restrict__ blockc
   }
 }
 
+// hist: kMaxGroups x MAXE counters in shared memory (a count is at most 32 and a running offset at most 4096, so 16 bits do).
+template <int MAXE, typename HistT>
 __device__ __forceinline__ void route_scatter_body(const int* __restrict__ ids, const int* __restrict__ blockoff, int T, int rank,
                                                    int E, int topk, int ep_ranks, int strided, int* __restrict__ route_map,
-                                                   int* __restrict__ exp2perm) {
-  __shared__ int hist[kMaxGroups][kMaxE];
+                                                   int* __restrict__ exp2perm, HistT (*hist)[MAXE]) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const unsigned below = (1u << lane) - 1u;
   const int groups = kRouteBlock * topk / 32;
   for (int blk = blockIdx.x; blk * kRouteBlock < T; blk += gridDim.x) {
     const long long base = (long long)blk * kRouteBlock * topk;
     const long long end = (long long)T * topk;
-    for (int i = threadIdx.x; i < groups * kMaxE; i += blockDim.x) (&hist[0][0])[i] = 0;
+    for (int i = threadIdx.x; i < groups * MAXE; i += blockDim.x) (&hist[0][0])[i] = 0;
     __syncthreads();
     for (int g = warp; g < groups; g += nwarps) {
       const long long i = base + g * 32 + lane;
       int e = -1;
       if (i < end) e = local_expert(ids[i], rank, E, ep_ranks, strided);
       const unsigned peers = __match_any_sync(0xffffffffu, e);
-      if (e >= 0 && (peers & below) == 0) hist[g][e] = __popc(peers);
+      if (e >= 0 && (peers & below) == 0) hist[g][e] = (HistT)__popc(peers);
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
       int run = 0;
-      for (int g = 0; g < groups; ++g) { const int c = hist[g][e]; hist[g][e] = run; run += c; }
+      for (int g = 0; g < groups; ++g) { const int c = hist[g][e]; hist[g][e] = (HistT)run; run += c; }
     }
     __syncthreads();
     for (int g = warp; g < groups; g += nwarps) {
@@ -270,17 +283,27 @@ __global__ void __launch_bounds__(256) permute_gather_kernel(const uint8_t* __re
   }
 }
 
+template <int MAXE>
 __global__ void __launch_bounds__(256) route_count_kernel(const int* ids, int T, int rank, int E, int topk, int ep_ranks,
                                                           int strided, int* blockcount) {
-  route_count_body(ids, T, rank, E, topk, ep_ranks, strided, blockcount);
+  route_count_body<MAXE>(ids, T, rank, E, topk, ep_ranks, strided, blockcount);
 }
+template <int MAXE>
 __global__ void __launch_bounds__(1024) route_tables_kernel(const int* blockcount, int blocks, int E, int tile, int* blockoff,
                                                             int* cta_batch, int* cta_limit, int* nne, int* total, int* route_map) {
-  route_tables_body(blockcount, blocks, E, tile, blockoff, cta_batch, cta_limit, nne, total, route_map);
+  route_tables_body<MAXE>(blockcount, blocks, E, tile, blockoff, cta_batch, cta_limit, nne, total, route_map);
 }
 __global__ void __launch_bounds__(512) route_scatter_kernel(const int* ids, const int* blockoff, int T, int rank, int E, int topk,
                                                             int ep_ranks, int strided, int* route_map, int* exp2perm) {
-  route_scatter_body(ids, blockoff, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm);
+  __shared__ int hist[kMaxGroups][kMaxE];
+  route_scatter_body<kMaxE, int>(ids, blockoff, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm, hist);
+}
+// up to 256 local experts: 16-bit counters in 64 KB of dynamic shared memory (opt-in above 48 KB)
+__global__ void __launch_bounds__(512) route_scatter_wide_kernel(const int* ids, const int* blockoff, int T, int rank, int E, int topk,
+                                                                 int ep_ranks, int strided, int* route_map, int* exp2perm) {
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  route_scatter_body<kMaxEWide, unsigned short>(ids, blockoff, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm,
+                                                reinterpret_cast<unsigned short(*)[kMaxEWide]>(dyn_smem));
 }
 template <bool RESIDUAL>
 __global__ void __launch_bounds__(128) finalize_kernel(const __nv_bfloat16* fc2, const int* exp2perm, const float* wts,
@@ -303,18 +326,19 @@ __global__ void __launch_bounds__(128) finalize_kernel(const __nv_bfloat16* fc2,
 
 extern "C" __global__ void __launch_bounds__(256) kern_k3_moe_route_count(const int* __restrict__ ids, int T, int rank, int E,
                                                                          int* __restrict__ blockcount) {
-  route_count_body(ids, T, rank, E, 16, EP_RANKS, K3G_EP_STRIDED, blockcount);
+  route_count_body<kMaxE>(ids, T, rank, E, 16, EP_RANKS, K3G_EP_STRIDED, blockcount);
 }
 extern "C" __global__ void __launch_bounds__(1024) kern_k3_moe_route_tables(const int* __restrict__ blockcount, int blocks, int E, int tile,
                                                                            int* __restrict__ blockoff, int* __restrict__ cta_batch,
                                                                            int* __restrict__ cta_limit, int* __restrict__ num_non_exiting,
                                                                            int* __restrict__ total_padded, int* __restrict__ route_map) {
-  route_tables_body(blockcount, blocks, E, tile, blockoff, cta_batch, cta_limit, num_non_exiting, total_padded, route_map);
+  route_tables_body<kMaxE>(blockcount, blocks, E, tile, blockoff, cta_batch, cta_limit, num_non_exiting, total_padded, route_map);
 }
 extern "C" __global__ void __launch_bounds__(512) kern_k3_moe_route_scatter(const int* __restrict__ ids, const int* __restrict__ blockoff,
                                                                            int T, int rank, int E, int* __restrict__ route_map,
                                                                            int* __restrict__ exp2perm) {
-  route_scatter_body(ids, blockoff, T, rank, E, 16, EP_RANKS, K3G_EP_STRIDED, route_map, exp2perm);
+  __shared__ int hist[kMaxGroups][kMaxE];
+  route_scatter_body<kMaxE, int>(ids, blockoff, T, rank, E, 16, EP_RANKS, K3G_EP_STRIDED, route_map, exp2perm, hist);
 }
 extern "C" __global__ void __launch_bounds__(128) kern_k3_moe_finalize(const __nv_bfloat16* __restrict__ fc2, const int* __restrict__ exp2perm,
                                                                       const float* __restrict__ wts, __nv_bfloat16* __restrict__ out,
@@ -386,7 +410,7 @@ extern "C" __global__ void __launch_bounds__(1024) kern_k3_moe_sf_shuffle(const 
 
 #ifndef K3G_CUBIN_ONLY
 static int check_route(int T, int E, int topk, int ep_ranks) {
-  K3G_REQUIRE(T >= 0 && E > 0 && E <= kMaxE, K3G_ESHAPE);
+  K3G_REQUIRE(T >= 0 && E > 0 && E <= kMaxEWide, K3G_ESHAPE);
   K3G_REQUIRE(topk > 0 && topk <= kMaxTopk && (kRouteBlock * topk) % 32 == 0, K3G_ESHAPE);
   K3G_REQUIRE(ep_ranks > 0, K3G_ESHAPE);
   return K3G_OK;
@@ -398,8 +422,12 @@ K3G_API int k3g_moe_route_count(const void* ids, int T, int rank, int E, int top
   if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
   K3G_REQUIRE(rank >= 0 && rank < ep_ranks, K3G_ERANGE);
   if (T == 0) return K3G_OK;
-  route_count_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 256, 0, k3g_stream(stream)>>>((const int*)ids, T, rank, E, topk, ep_ranks,
-                                                                                        strided, (int*)blockcount);
+  if (E <= kMaxE)
+    route_count_kernel<kMaxE><<<(T + kRouteBlock - 1) / kRouteBlock, 256, 0, k3g_stream(stream)>>>((const int*)ids, T, rank, E, topk, ep_ranks,
+                                                                                                 strided, (int*)blockcount);
+  else
+    route_count_kernel<kMaxEWide><<<(T + kRouteBlock - 1) / kRouteBlock, 256, 0, k3g_stream(stream)>>>((const int*)ids, T, rank, E, topk,
+                                                                                                     ep_ranks, strided, (int*)blockcount);
   return k3g_launch_status();
 }
 
@@ -407,9 +435,13 @@ K3G_API int k3g_moe_route_tables(const void* blockcount, int blocks, int E, int 
                                  void* cta_limit, void* num_non_exiting, void* total_padded, void* route_map, void* stream) {
   K3G_REQUIRE_PTR(blockcount); K3G_REQUIRE_PTR(blockoff); K3G_REQUIRE_PTR(cta_batch); K3G_REQUIRE_PTR(cta_limit);
   K3G_REQUIRE_PTR(num_non_exiting); K3G_REQUIRE_PTR(total_padded); K3G_REQUIRE_PTR(route_map);
-  K3G_REQUIRE(blocks >= 0 && E > 0 && E <= kMaxE && tile > 0, K3G_ESHAPE);
-  route_tables_kernel<<<1, 1024, 0, k3g_stream(stream)>>>((const int*)blockcount, blocks, E, tile, (int*)blockoff, (int*)cta_batch,
-                                                         (int*)cta_limit, (int*)num_non_exiting, (int*)total_padded, (int*)route_map);
+  K3G_REQUIRE(blocks >= 0 && E > 0 && E <= kMaxEWide && tile > 0, K3G_ESHAPE);
+  if (E <= kMaxE)
+    route_tables_kernel<kMaxE><<<1, 1024, 0, k3g_stream(stream)>>>((const int*)blockcount, blocks, E, tile, (int*)blockoff, (int*)cta_batch,
+                                                                  (int*)cta_limit, (int*)num_non_exiting, (int*)total_padded, (int*)route_map);
+  else
+    route_tables_kernel<kMaxEWide><<<1, 1024, 0, k3g_stream(stream)>>>((const int*)blockcount, blocks, E, tile, (int*)blockoff, (int*)cta_batch,
+                                                                      (int*)cta_limit, (int*)num_non_exiting, (int*)total_padded, (int*)route_map);
   return k3g_launch_status();
 }
 
@@ -419,8 +451,22 @@ K3G_API int k3g_moe_route_scatter(const void* ids, const void* blockoff, int T, 
   if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
   K3G_REQUIRE(rank >= 0 && rank < ep_ranks, K3G_ERANGE);
   if (T == 0) return K3G_OK;
-  route_scatter_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 512, 0, k3g_stream(stream)>>>(
-      (const int*)ids, (const int*)blockoff, T, rank, E, topk, ep_ranks, strided, (int*)route_map, (int*)exp2perm);
+  if (E <= kMaxE) {
+    route_scatter_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 512, 0, k3g_stream(stream)>>>(
+        (const int*)ids, (const int*)blockoff, T, rank, E, topk, ep_ranks, strided, (int*)route_map, (int*)exp2perm);
+  } else {
+    constexpr int kWideSmem = kMaxGroups * kMaxEWide * (int)sizeof(unsigned short);      // 64 KB
+    static bool opted[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !opted[dev]) {
+      if (cudaFuncSetAttribute(route_scatter_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem) != cudaSuccess)
+        return k3g_launch_status();
+      opted[dev] = true;
+    }
+    route_scatter_wide_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 512, kWideSmem, k3g_stream(stream)>>>(
+        (const int*)ids, (const int*)blockoff, T, rank, E, topk, ep_ranks, strided, (int*)route_map, (int*)exp2perm);
+  }
   return k3g_launch_status();
 }
 

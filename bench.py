@@ -255,7 +255,7 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     return out
 
 
-def bench_layer(rank, world, timed, iters=20):
+def bench_layer(rank, world, timed, iters=20, peak_gbs=6529.7):
     """Per-layer glue: every non-GEMM call of one KDA layer and one MLA layer of the reference's prefill
     program (k3g/layer.py), replayed as a CUDA graph, with a per-call breakdown from events."""
     import torch
@@ -277,7 +277,15 @@ def bench_layer(rank, world, timed, iters=20):
                     acc[label] = 0.0; order.append(label)
                 acc[label] += a.elapsed_time(b) * 1e3 / 5
         lg.check_status()
-        out[kind] = {"graph_us": round(graph_us, 1), "launches": len(order) + 3, "calls": [{"call": l, "us": round(acc[l], 1)} for l in order]}
+        calls = []
+        for l in order:
+            nbytes, bound = lg.traffic_of(l)
+            row = {"call": l, "us": round(acc[l], 1), "bound": bound}
+            if nbytes and bound != "latency":
+                peak = peak_gbs if bound == "hbm" else 770.0
+                row.update({"bytes": nbytes, "gbs": round(nbytes / acc[l] / 1e3, 1), "frac": round(nbytes / acc[l] / 1e3 / peak, 3)})
+            calls.append(row)
+        out[kind] = {"graph_us": round(graph_us, 1), "launches": len(order) + 3, "calls": calls}
         lg.close()
         del lg
         torch.cuda.empty_cache()
@@ -285,7 +293,8 @@ def bench_layer(rank, world, timed, iters=20):
     out["weighted_69kda_24mla_fused_us"] = round((69 * out["kda_fused"]["graph_us"] + 24 * out["mla_fused"]["graph_us"]) / 93, 1)
     out["note"] = ("all non-GEMM calls of one layer of the reference's prefill program at T=16384, world=%d (rows T/%d per rank, %d heads per rank, "
                    "56 local experts); GEMM/attention outputs are seeded random buffers; per-call times are eager launches with events, graph_us "
-                   "is the whole list as one CUDA graph; *_fused = the same program with the three per-tensor FP8 quantisations fed by "
+                   "is the whole list as one CUDA graph; per call: bytes = algorithmic bytes per rank, frac = bytes / us against the measured HBM copy "
+                   "bandwidth (bound hbm) or the 770 GB/s peer copy (bound nvlink: bytes received or sent per direction); *_fused = the same program with the three per-tensor FP8 quantisations fed by "
                    "maxima their producers leave (apply launch only) and the two reduce-scatters pulled inside the kernels that consume them (residual kernel, latent norm); "
                    "outputs bit-identical to the reference call list" % (world, world, 96 // world))
     return out
@@ -423,7 +432,7 @@ def run_gpu(args, rank, world, local_rank):
     if not args.no_ops:
         glue.close(); glue = None
         torch.cuda.empty_cache()
-        line["layer_glue"] = bench_layer(rank, world, timed)
+        line["layer_glue"] = bench_layer(rank, world, timed, peak_gbs=peak_gbs)
     if rank == 0 and world == 1:
         us, cores = cpu_oracle_us(20, 2, 1)
         line["cpu_baseline"] = {"value": round(us, 1), "unit": UNIT, "cores": cores, "kind": "port", "sample": CPU_SAMPLE % (TOKENS, 1, 20)}

@@ -199,6 +199,43 @@ class LayerGlue:
             c = [swap.get(label, (label, fn)) for label, fn in c if swap.get(label, 0) is not None]
         return c
 
+    def traffic(self):
+        """label prefix -> (algorithmic bytes per rank, bound): the unique bytes a call must move through HBM ("hbm") or
+        receive / send over NVLink ("nvlink", world > 1 only); small table kernels are "latency"."""
+        W, T, B, inner, nb = self.world, self.T, self.B, self.inner, self.nb
+        EB, ET = B * H * 2, T * H * 2                       # one bf16 pass over the shard / over all rows
+        link = lambda nbytes: ((W - 1) * nbytes, "nvlink")
+        t = {
+            "coll_epoch": (0, "latency"), "normed_sync": (0, "latency"), "reduce_attn (arrive)": (0, "latency"), "scatter_moe (arrive)": (0, "latency"),
+            "res_in": link(EB) if W > 1 else ((3 + 2 * nb + 2) * EB, "hbm"),
+            "qkvg_quant": (3 * ET // 2, "hbm"),
+            "span_gather": (T * 3 * inner * 4 + T * 256 * 4, "hbm"), "span_state_in": (2 * 2 * self.heads * 128 * 128 * 4, "latency"),
+            "span_out_gate": (T * inner * 6, "hbm"),
+            "mla_prep": (T * ((2112 + inner) * 2 + (1536 + 576 + inner) * 2), "hbm"), "latent_gather": (T * 576 * 4, "hbm"),
+            "mla_gate": (T * inner * 6, "hbm"),
+            "reduce_attn (pull RS)": link(EB) if W > 1 else (2 * EB, "hbm"),
+            "res_mlp": ((4 + nb) * EB, "hbm"),
+            "reduce_attn + res_mlp": link(EB) if W > 1 else ((4 + nb) * EB, "hbm"),
+            "normed_quant": (3 * EB // 2, "hbm"), "topk": (B * EXPERTS * 4 + B * TOPK * 8, "latency"),
+            "moe_quant (": (B * LATENT * 3 + B * LATENT // 32, "hbm"),
+            "gather_small": link(B * (LATENT + LATENT // 32 + 2 * TOPK * 4)) if W > 1 else (2 * B * (LATENT + LATENT // 32 + 2 * TOPK * 4), "hbm"),
+            "moe_quant + gather_small": link(B * (LATENT + LATENT // 32 + 2 * TOPK * 4)) if W > 1 else (B * LATENT * 3, "hbm"),
+            "route_count": (0, "latency"), "route_tables": (0, "latency"), "route_scatter": (0, "latency"),
+            "finalize": ((T * TOPK // EP + T) * LATENT * 2, "hbm"),
+            "scatter_moe (pull RS)": link(B * LATENT * 2) if W > 1 else (2 * B * LATENT * 2, "hbm"),
+            "shared_situ": (B * (SHARED * 6 + LATENT * 4), "hbm"),
+            "scatter_moe + shared_situ": link(B * LATENT * 2) if W > 1 else (B * (SHARED * 6 + LATENT * 4), "hbm"),
+            "shared_act_quant": (3 * B * SHARED, "hbm"),
+        }
+        return t
+
+    def traffic_of(self, label):
+        best = None
+        for k, v in self.traffic().items():
+            if label.startswith(k) and (best is None or len(k) > len(best[0])):
+                best = (k, v)
+        return best[1] if best else (0, "latency")
+
     def run(self):
         for _, fn in self.calls():
             fn()

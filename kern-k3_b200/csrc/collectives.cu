@@ -97,8 +97,10 @@ __device__ __forceinline__ void arrive_and_wait(unsigned long long* flags, const
 // peer q); it is resident from the start, and no other block ever waits, so the grid always drains.
 __device__ unsigned g_tail_ticket[64];   // one ticket counter per slot (mod 64): launches on different slots may overlap
 
+// `arrivals` is what the launch publishes on its slot (the epoch counts units, which the reference ties to gridDim.x;
+// the C-ABI launches run a smaller, resident grid and publish the caller's `units`).
 __device__ __forceinline__ void block_arrive_tail(unsigned long long* flags, const unsigned long long* flags_peer, int slot, int nranks,
-                                                  long long timeout_ns, unsigned* status) {
+                                                  long long timeout_ns, unsigned* status, unsigned arrivals) {
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -107,7 +109,7 @@ __device__ __forceinline__ void block_arrive_tail(unsigned long long* flags, con
     if (ticket == gridDim.x - 1) {
       *tk = 0u;                                   // stream order keeps the next launch behind this store
       __threadfence();
-      red_release_sys_add(flags + slot, (unsigned long long)gridDim.x);
+      red_release_sys_add(flags + slot, (unsigned long long)arrivals);
     }
   }
   if (blockIdx.x == 0 && threadIdx.x < 32) {
@@ -191,7 +193,7 @@ __device__ __forceinline__ void allgather4_body(const unsigned char* s0, unsigne
                                                 const unsigned char* s2, unsigned char* d2, const unsigned long long* p2, long long n2,
                                                 const unsigned char* s3, unsigned char* d3, const unsigned long long* p3, long long n3,
                                                 unsigned long long* flags, const unsigned long long* flags_peer, int slot, int rank,
-                                                int nranks, long long timeout_ns, unsigned* status) {
+                                                int nranks, long long timeout_ns, unsigned* status, unsigned arrivals) {
   const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -199,7 +201,7 @@ __device__ __forceinline__ void allgather4_body(const unsigned char* s0, unsigne
   if (n1 > 0) push_span(s1, d1, p1, n1, rank, nr, tid, stride);
   if (n2 > 0) push_span(s2, d2, p2, n2, rank, nr, tid, stride);
   if (n3 > 0) push_span(s3, d3, p3, n3, rank, nr, tid, stride);
-  block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status);
+  block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status, arrivals);
 }
 
 // ---- fused: pull reduce-scatter -> residual add -> RMSNorm -> MXFP8 -> push all-gather ----------
@@ -329,9 +331,9 @@ __global__ void __launch_bounds__(1024) allgather4_kernel(const unsigned char* s
                                                           const unsigned char* s2, unsigned char* d2, const unsigned long long* p2, long long n2,
                                                           const unsigned char* s3, unsigned char* d3, const unsigned long long* p3, long long n3,
                                                           unsigned long long* flags, const unsigned long long* flags_peer, int slot, int rank,
-                                                          int nranks, long long timeout_ns, unsigned* status) {
+                                                          int nranks, long long timeout_ns, unsigned* status, unsigned arrivals) {
   allgather4_body(s0, d0, p0, n0, s1, d1, p1, n1, s2, d2, p2, n2, s3, d3, p3, n3, flags, flags_peer, slot, rank, nranks, timeout_ns,
-                  status ? status : g_wait_status);
+                  status ? status : g_wait_status, arrivals);
 }
 
 // MXFP8 quantisation of this rank's latent rows written straight into every rank's gathered buffers, then two plain
@@ -343,7 +345,7 @@ __global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bf
                                                                    unsigned char* d2, const unsigned long long* p2, long long n2,
                                                                    const unsigned char* s3, unsigned char* d3, const unsigned long long* p3,
                                                                    long long n3, unsigned long long* flags, const unsigned long long* flags_peer,
-                                                                   int slot, int rank, int nranks, long long timeout_ns, unsigned* status) {
+                                                                   int slot, int rank, int nranks, long long timeout_ns, unsigned* status, unsigned arrivals) {
   const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
   for (long long g = tid; g < ngroups; g += stride) {
@@ -377,7 +379,7 @@ __global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bf
   }
   if (n2 > 0) push_span(s2, d2, p2, n2, rank, nr, tid, stride);
   if (n3 > 0) push_span(s3, d3, p3, n3, rank, nr, tid, stride);
-  block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status ? status : g_wait_status);
+  block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status ? status : g_wait_status, arrivals);
 }
 
 }  // namespace
@@ -424,10 +426,15 @@ extern "C" __global__ void __launch_bounds__(1024) kern_k3_allgather4_push(
     const unsigned char* __restrict__ s3, unsigned char* __restrict__ d3, const unsigned long long* __restrict__ p3, long long n3,
     unsigned long long* __restrict__ flags, const unsigned long long* __restrict__ flags_peer, int slot, int rank, int nranks) {
   allgather4_body(s0, d0, p0, n0, s1, d1, p1, n1, s2, d2, p2, n2, s3, d3, p3, n3, flags, flags_peer, slot, rank, nranks, K3G_SPIN_NS,
-                  g_wait_status);
+                  g_wait_status, gridDim.x);
 }
 
 #ifndef K3G_CUBIN_ONLY
+// Grid of a push kernel launched through the C ABI: at most two 1024-thread blocks per SM of a 148-SM part, all
+// resident at once (the blocks stride over the payload), instead of `units` short-lived blocks; the launch still
+// publishes `units` arrivals, so the counter protocol is the reference's.
+static inline unsigned push_grid(int units) { return (unsigned)(units < 296 ? units : 296); }
+
 static int check_world(int rank, int nranks) {
   K3G_REQUIRE(nranks == 1 || nranks == 2 || nranks == 4 || nranks == 8, K3G_ESHAPE);
   K3G_REQUIRE(rank >= 0 && rank < nranks, K3G_ERANGE);
@@ -493,11 +500,11 @@ K3G_API int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long l
     K3G_REQUIRE(nn[i] >= 0 && nn[i] % 16 == 0, K3G_ESHAPE);
     if (nn[i] > 0) { K3G_REQUIRE_PTR(ss[i]); K3G_REQUIRE_PTR(dd[i]); K3G_REQUIRE_PTR(pp[i]); K3G_REQUIRE_ALIGNED(ss[i]); K3G_REQUIRE_ALIGNED(dd[i]); }
   }
-  allgather4_kernel<<<units, 1024, 0, k3g_stream(stream)>>>(
+  allgather4_kernel<<<push_grid(units), 1024, 0, k3g_stream(stream)>>>(
       (const unsigned char*)s0, (unsigned char*)d0, (const unsigned long long*)p0, n0, (const unsigned char*)s1, (unsigned char*)d1,
       (const unsigned long long*)p1, n1, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2,
       (const unsigned char*)s3, (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags,
-      (const unsigned long long*)flags_peer, slot, rank, nranks, timeout_us * 1000LL, (unsigned*)status);
+      (const unsigned long long*)flags_peer, slot, rank, nranks, timeout_us * 1000LL, (unsigned*)status, (unsigned)units);
   return k3g_launch_status();
 }
 
@@ -520,11 +527,11 @@ K3G_API int k3g_moe_quant_allgather_push(const void* x, int rows, int cols, void
     K3G_REQUIRE(nn[i] >= 0 && nn[i] % 16 == 0, K3G_ESHAPE);
     if (nn[i] > 0) { K3G_REQUIRE_PTR(ss[i]); K3G_REQUIRE_PTR(dd[i]); K3G_REQUIRE_PTR(pp[i]); K3G_REQUIRE_ALIGNED(ss[i]); K3G_REQUIRE_ALIGNED(dd[i]); }
   }
-  moe_quant_allgather_kernel<<<units, 1024, 0, k3g_stream(stream)>>>(
+  moe_quant_allgather_kernel<<<push_grid(units), 1024, 0, k3g_stream(stream)>>>(
       (const __nv_bfloat16*)x, (long long)rows * cols / 32, (unsigned char*)q_all, (const unsigned long long*)q_peer, (unsigned char*)sf_all,
       (const unsigned long long*)sf_peer, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2, (const unsigned char*)s3,
       (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags, (const unsigned long long*)flags_peer, slot, rank, nranks,
-      timeout_us * 1000LL, (unsigned*)status);
+      timeout_us * 1000LL, (unsigned*)status, (unsigned)units);
   return k3g_launch_status();
 }
 

@@ -295,8 +295,8 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
     const size_t base = (size_t)b * H;
     V8 x[VPT];
     if constexpr (NR > 0) {
-      // pull the NR partial rows two vectors at a time (2 NR + 2 loads in flight per thread), land the chain, add
-      constexpr int CH = 2;
+      // pull the NR partial rows a few vectors at a time (CH (NR + 1) loads in flight per thread), land the chain, add
+      constexpr int CH = NR == 1 ? VPT : NR == 2 ? 4 : NR == 4 ? 2 : 1;
 #pragma unroll
       for (int v0 = 0; v0 < VPT; v0 += CH) {
         V8 pr[CH], p[CH];

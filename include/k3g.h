@@ -11,7 +11,11 @@
  *
  * Conventions
  *   - every pointer is a DEVICE pointer owned by the caller unless its name starts with
- *     `host_`; nothing here allocates, frees or synchronises; launchers are graph-capturable;
+ *     `host_`; the launchers neither allocate, free nor synchronise and can be captured into a CUDA
+ *     graph.  The exceptions are named where they are declared: k3g_wait_status (copies 16 bytes
+ *     to the host and synchronises the stream), the k3g_peer_* set-up helpers (allocate / map),
+ *     the first k3g_moe_route_scatter call with more than 64 local experts on a device (raises the
+ *     kernel's shared-memory limit once) and the first k3g_quant_fp8_tensor_noalloc call on a device;
  *   - bf16 / e4m3 / ue8m0 buffers are passed as void*;
  *   - `stream` is a cudaStream_t (void* 0 = the legacy default stream);
  *   - return value: 0 ok; < 0 argument rejected before any launch (K3G_E*); > 0 cudaError_t.
@@ -134,7 +138,8 @@ int k3g_quant_fp8_tensor(const void* x, void* y, void* scale_out, void* partials
  * 8 KB device array inside the library, so grid is limited to 2048 (K3G_ELIMIT beyond), each GPU that
  * loads the library holds the array until exit, calls that overlap on one GPU race on it, and the
  * first call on a device does a one-time host-side address lookup (make it before any stream
- * capture).  Results equal k3g_quant_fp8_tensor's for the same grid. */
+ * capture) whose result is kept until the process exits: the device's primary context has to live
+ * as long (no cudaDeviceReset between calls).  Results equal k3g_quant_fp8_tensor's for the same grid. */
 int k3g_quant_fp8_tensor_noalloc(const void* x, void* y, void* scale_out, int n, int grid, void* stream);
 
 /* ---- router and MoE routing ------------------------------------------------------------------ */
@@ -147,7 +152,9 @@ int k3g_router_topk(const void* S, const void* bias, const void* rs, void* idx, 
 /* kern_k3_moe_route_count, source/k3_moe_prefill_v4.cu:142 (op moe_route_count).  E local experts (up to 256: the
  * drop-in kernels cover 64, as the reference's 56; expert-parallel groups of 1 or 2 -- 224 / 112 local experts -- take
  * wider kernels behind the same three calls); placement strided (id % ep_ranks == rank, slot id / ep_ranks) or
- * blocked (source :100-109). */
+ * blocked (source :100-109).  rank = -1 (all three routing calls; no counterpart in the reference) builds the tables
+ * of every owner at once: E is then the TOTAL expert count, owner o's experts take slots o * E / ep_ranks ..., so
+ * owner o's own tables are these shifted by the constant row blockoff[o * E / ep_ranks] (k3g_permute_dispatch). */
 int k3g_moe_route_count(const void* ids, int T, int rank, int E, int topk, int ep_ranks, int strided, void* blockcount,
                         void* stream);
 
@@ -155,9 +162,19 @@ int k3g_moe_route_count(const void* ids, int T, int rank, int E, int topk, int e
 int k3g_moe_route_tables(const void* blockcount, int blocks, int E, int tile, void* blockoff, void* cta_batch,
                          void* cta_limit, void* num_non_exiting, void* total_padded, void* route_map, void* stream);
 
-/* kern_k3_moe_route_scatter, source/k3_moe_prefill_v4.cu:205 (op moe_route_scatter). */
+/* kern_k3_moe_route_scatter, source/k3_moe_prefill_v4.cu:205 (op moe_route_scatter).  With E > 64 the first
+ * call on a device raises the wide kernel's dynamic shared-memory limit (a host-side attribute call): make
+ * it before any stream capture. */
 int k3g_moe_route_scatter(const void* ids, const void* blockoff, int T, int rank, int E, int topk, int ep_ranks,
                           int strided, void* route_map, void* exp2perm, void* stream);
+
+/* k3g_moe_route_tables followed by k3g_moe_route_scatter in ONE launch (no counterpart in the reference, whose
+ * tables kernel is a one-block launch of its own, source/k3_moe_prefill_v4.cu:159): each scatter block derives its own
+ * row of blockoff from blockcount, block 0 also writes cta_batch / cta_limit / the two scalars / the padding rows.
+ * Every output is bit-identical to the two calls.  T > 0. */
+int k3g_moe_route_tables_scatter(const void* ids, const void* blockcount, int T, int rank, int E, int topk, int ep_ranks, int strided,
+                                 int tile, void* blockoff, void* cta_batch, void* cta_limit, void* num_non_exiting, void* total_padded,
+                                 void* route_map, void* exp2perm, void* stream);
 
 /* kern_k3_moe_finalize, source/k3_moe_prefill_v4.cu:254 (op moe_finalize). */
 int k3g_moe_finalize(const void* fc2, const void* exp2perm, const void* wts, void* out, int T, int cols, int topk,
@@ -173,6 +190,19 @@ int k3g_finalize_residual(const void* fc2, const void* exp2perm, const void* wts
  * which reads route_map (source/k3_moe_prefill_v4.cu:36-46). */
 int k3g_permute_gather(const void* q, const void* sf, const void* route_map, long long rows, int cols, void* out_q,
                        void* out_sf, void* stream);
+
+/* Dispatch to the owning ranks over NVLink (benchmark configuration 2 at EP > 1; no counterpart in the reference,
+ * which all-gathers every token to every rank -- source/k3_allgather4_v3.cu:61 -- and lets its grouped GEMM select).
+ * q [B, cols] / sf [B, cols / 32]: the MXFP8 rows of this rank's tokens token_begin .. token_begin + B of the T gathered
+ * tokens; ids / exp2perm [T, topk] and blockoff: the gathered expert ids and the all-owner routing tables
+ * (k3g_moe_route_* with rank = -1, E = experts).  The row of token t is stored once per slot k into row
+ * exp2perm[t, k] - blockoff[owner * experts / ep_ranks] of the owner's out_q / out_sf (out_*_peer: u64 tables of every
+ * rank's buffer, own included), owner = ids % ep_ranks (strided) or ids / (experts / ep_ranks).  Destination rows are
+ * exactly the live rows of the owner's own expert-sorted order (k3g_permute_gather on its route_map); the tile-padding
+ * rows are not written.  Plain peer stores; follow with k3g_rs_arrive before the owner reads. */
+int k3g_permute_dispatch(const void* q, const void* sf, const void* ids, const void* exp2perm, const void* blockoff, int B,
+                         long long token_begin, int topk, int cols, int experts, int ep_ranks, int strided, const void* out_q_peer,
+                         const void* out_sf_peer, void* stream);
 
 /* ---- collectives over NVLink peer pointers ---------------------------------------------------- */
 /* Peer tables (`*_peer`) are device arrays of u64 addresses, one per rank, own rank included, as the
@@ -191,13 +221,24 @@ int k3g_epoch_bump(void* flags, int units, void* stream);
 int k3g_rs_arrive(void* flags, const void* flags_peer, int units, int slot, int nranks, long long timeout_us, void* status,
                   void* stream);
 
+/* k3g_epoch_bump followed by k3g_rs_arrive in one launch (no counterpart in the reference, which always bumps the
+ * epoch with its own kern_k3_epoch_bump launch, source/k3_collectives.cu:74): for a replay whose first waiting
+ * call is a plain barrier.  Calls of the replay that publish arrivals without waiting (a push kernel's stores) may
+ * come before it; nothing that WAITS may. */
+int k3g_epoch_arrive(void* flags, const void* flags_peer, int units, int slot, int nranks, long long timeout_us, void* status,
+                     void* stream);
+
 /* kern_k3_rs_pull, source/k3_reducescatter_pull_nr4.cu:124 (second launch of k3_reducescatter_bf16).
  * order = 2 * ownpos + descend (source/k3_collectives.cu:222-236); 2 * (nranks - 1) is the ring order. */
 int k3g_rs_pull(const void* src, void* dst, const void* src_peer, long long count, int order, int rank, int nranks, int grid,
                 void* stream);
 
-/* kern_k3_allgather4_push, source/k3_allgather4_v3.cu:61 (op k3_allgather4_push).  Launches `units`
- * blocks; every block contributes one arrival, so `units` must be the epoch increment. */
+/* kern_k3_allgather4_push, source/k3_allgather4_v3.cu:61 (op k3_allgather4_push).  The launch publishes
+ * `units` arrivals on its slot, so `units` must be the epoch increment.  The blocks of a push launch count
+ * themselves on a per-device ticket word chosen by slot % 64 (the last one publishes the arrivals): at most
+ * ONE push launch (this entry, k3g_moe_quant_allgather_push, the drop-in kern_k3_allgather4_push) per slot
+ * modulo 64 may be in flight on a device at a time; launches on one stream, or the nodes of one graph chain,
+ * satisfy that by construction. */
 int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long long n0, const void* s1, void* d1, const void* p1,
                         long long n1, const void* s2, void* d2, const void* p2, long long n2, const void* s3, void* d3,
                         const void* p3, long long n3, void* flags, const void* flags_peer, int slot, int rank, int nranks,
@@ -213,7 +254,8 @@ int k3g_rs_resnorm_mxfp8_ag(const void* partial, const void* partial_peer, const
                             int rows, int H, float eps, int rank, int nranks, int grid_hint, int row_begin, int shard_rows,
                             void* stream);
 
-/* Status of the last expired wait of a launch that had no status pointer (host_status: 4 x u32). */
+/* Status of the last expired wait of a launch that had no status pointer (host_status: 4 x u32).  Copies
+ * the record to the host and SYNCHRONISES `stream`; not capturable. */
 int k3g_wait_status(void* host_status, int clear, void* stream);
 
 /* Set-up helpers standing in for the reference's external runtime (allocation + peer mapping with CUDA
@@ -321,11 +363,6 @@ int k3g_land(const void* p, void* o, int n, int off, int ldc, int B, void* strea
 /* kern_k3_rms, source/k3_land.cu:107: o [B, h] = bf16(x * rs) (x) gamma, rs = rsqrt(mean(x^2) + 1e-5); the sum in
  * the order of the reference's 1024-thread block.  h % 8 == 0, h <= 8192. */
 int k3g_rms(const void* x, const void* gamma, void* o, int h, int B, void* stream);
-
-/* Diagnostic: out[i] = bf16(SiTU(g[i], u[i])) for n bf16 pairs, with the kernel's formula (literal = 0) or the
- * reference's formula written out operation for operation (literal = 1, source/k3_land_fused.cu:88).  The two
- * must agree bit for bit on every input; the tests sweep all 65536 values of g and of u. */
-int k3g_situ_probe(const void* g, const void* u, void* out, long long n, int literal, void* stream);
 
 /* kern_sigmoid_mul_bf16, source/sigmoid_mul.cu:15 (op mla_gate): out = bf16(attn * bf16(sigmoid(gate))),
  * gate(t, h, d) = gate + t * gate_tstride + h * gate_hstride + d. */

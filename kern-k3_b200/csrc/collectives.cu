@@ -50,23 +50,25 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 __device__ __forceinline__ void red_release_sys_add(unsigned long long* p, unsigned long long v) {
   asm volatile("red.release.sys.global.add.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ unsigned ld_relaxed_sys_u32(const void* p) {
-  unsigned v;
-  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
-// Spin until the low 32 bits of *counter reach target; false (and a status record) on expiry.
-__device__ __forceinline__ bool bounded_wait(const void* counter, unsigned target, long long timeout_ns, unsigned* status,
+// Spin until *counter (the full 64-bit arrival count: counters are never reset, and a 32-bit compare would
+// pass without waiting for one replay after 2^32 arrivals) reaches target; false and a status record on
+// expiry.  The record keeps the low 32 bits of the observed count.
+__device__ __forceinline__ bool bounded_wait(const void* counter, unsigned long long target, long long timeout_ns, unsigned* status,
                                              int slot, int peer) {
   const unsigned long long t0 = globaltimer_ns();
   const long long max_iters = (timeout_ns / 1000 + 1) * K3G_SPIN_ITERS_PER_US;
   long long it = 0;
-  unsigned v;
-  while ((v = ld_relaxed_sys_u32(counter)) < target) {
+  unsigned long long v;
+  while ((v = ld_relaxed_sys_u64(counter)) < target) {
     if (++it > max_iters || (long long)(globaltimer_ns() - t0) > timeout_ns) {
-      if (atomicCAS(&status[0], 0u, 1u) == 0u) { status[1] = (unsigned)slot; status[2] = (unsigned)peer; status[3] = v; }
+      if (atomicCAS(&status[0], 0u, 1u) == 0u) { status[1] = (unsigned)slot; status[2] = (unsigned)peer; status[3] = (unsigned)v; }
       return false;
     }
     __nanosleep(64);
@@ -81,7 +83,7 @@ __device__ __forceinline__ void arrive_and_wait(unsigned long long* flags, const
   if (threadIdx.x == 0) red_release_sys_add(flags + slot, (unsigned long long)units);
   const int q = threadIdx.x;
   if (q < nr) {
-    const unsigned target = (unsigned)flags[0];
+    const unsigned long long target = flags[0];
     bounded_wait((const void*)(flags_peer[q] + (unsigned long long)slot * 8ull), target, timeout_ns, status, slot, q);
   }
   __syncwarp();
@@ -116,7 +118,7 @@ __device__ __forceinline__ void block_arrive_tail(unsigned long long* flags, con
     const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
     const int q = threadIdx.x;
     if (q < nr) {
-      const unsigned target = (unsigned)flags[0];
+      const unsigned long long target = flags[0];
       bounded_wait((const void*)(flags_peer[q] + (unsigned long long)slot * 8ull), target, timeout_ns, status, slot, q);
     }
     __syncwarp();
@@ -210,6 +212,9 @@ __device__ __forceinline__ void allgather4_body(const unsigned char* s0, unsigne
 // fusion (same team layout and reduction order as resnorm.cu); codes and scales are stored to
 // every rank's gathered buffers.  The caller brackets this kernel with two arrive launches.
 constexpr int kTeam = 128;
+#ifndef K3G_FUSED_PAIR16
+#define K3G_FUSED_PAIR16 1
+#endif
 
 template <int VPT, int NR>
 __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
@@ -218,7 +223,17 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
     uint8_t* __restrict__ q_all, const unsigned long long* __restrict__ q_all_peer, uint8_t* __restrict__ sf_all,
     const unsigned long long* __restrict__ sf_all_peer, int rows, int rank, float eps, int row_begin, int shard_rows) {
   constexpr int H = VPT * 1024;
+  // Over NVLink a store of a few bytes costs a whole packet.  With peers (NR > 1) the row's H / 32 scale bytes
+  // are therefore collected in shared memory and leave as 16-byte stores, H / 512 per rank, issued by the
+  // first threads of the team; a single rank keeps the direct 4-byte stores (free in local HBM, and no extra
+  // block barrier per row).
+  constexpr bool kStageScales = NR > 1 && (H / 32) % 16 == 0;
+  constexpr int kSfVecs = H / 512;                      // 16-byte vectors of scale bytes per row
+  // ... and the codes leave as 16-byte stores: a thread's vector is 8 codes, so neighbouring lanes swap halves of a
+  // pair of vectors (K3G_FUSED_PAIR16 = 0 keeps the 8-byte stores, for comparison runs).
+  constexpr bool kPairCodes = kStageScales && K3G_FUSED_PAIR16;
   __shared__ float s_red[2][kTeam / 32];
+  __shared__ __align__(16) unsigned s_sf[2][kStageScales ? H / 128 : 1];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const uint4* base[NR];
   rs_bases<NR, NR - 1, 0>(partial, partial_peer, (long long)rank * shard_rows * H, rank, base);
@@ -293,6 +308,7 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
 #pragma unroll
     for (int w = 0; w < kTeam / 32; ++w) tot = __fadd_rn(tot, red[w]);
     const float rr = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
+    unsigned hq0 = 0u, hq1 = 0u;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int u = (t + v * kTeam) * 8;
@@ -310,10 +326,36 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
       unsigned sfb = (unsigned)(e + 127);
       sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
       sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
+      if (kStageScales && (lane & 15) == 0) s_sf[it & 1][u >> 7] = sfb;
+      if (kPairCodes && (v & 1) == 0 && v + 1 < VPT) {
+        hq0 = q0; hq1 = q1;                              // wait for vector v + 1
+      } else if (kPairCodes && (v & 1) == 1) {
+        // vectors v - 1 and v: the even lane stores its own vector v - 1 and the odd neighbour's (16 contiguous
+        // bytes), the odd lane the even neighbour's vector v and its own; each lane hands over the other half
+        const bool odd = (lane & 1) != 0;
+        const unsigned g0 = __shfl_xor_sync(0xffffffffu, odd ? hq0 : q0, 1), g1 = __shfl_xor_sync(0xffffffffu, odd ? hq1 : q1, 1);
+        const V8 w = odd ? V8{{g0, g1, q0, q1}} : V8{{hq0, hq1, g0, g1}};
+        const int uu = odd ? u - 8 : u - kTeam * 8;
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        st_stream8(qdst[r] + rowoff + u, q0, q1);
-        if ((lane & 15) == 0) *reinterpret_cast<unsigned*>(sfdst[r] + (size_t)b * (H / 32) + (u >> 5)) = sfb;
+        for (int r = 0; r < NR; ++r) st_stream(qdst[r] + rowoff + uu, w);
+      } else {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+          st_stream8(qdst[r] + rowoff + u, q0, q1);
+          if (!kStageScales && (lane & 15) == 0) *reinterpret_cast<unsigned*>(sfdst[r] + (size_t)b * (H / 32) + (u >> 5)) = sfb;
+        }
+      }
+    }
+    if (kStageScales) {
+      __syncthreads();                                  // the row's scale words are all in s_sf[it & 1]; its next writer is two rows away
+      if (t < kSfVecs * NR) {
+        const int r = t / kSfVecs, v = t - r * kSfVecs;
+        const uint4 w = reinterpret_cast<const uint4*>(s_sf[it & 1])[v];
+        uint8_t* row = sfdst[0];
+#pragma unroll
+        for (int k = 1; k < NR; ++k) row = r == k ? sfdst[k] : row;      // select, so the pointer array stays in registers
+        uint4* d = reinterpret_cast<uint4*>(row + (size_t)b * (H / 32)) + v;
+        if (r == rank) *d = w; else __stcs(d, w);
       }
     }
   }
@@ -324,6 +366,14 @@ __global__ void epoch_add_kernel(unsigned long long* flags, int units) {
 }
 __global__ void __launch_bounds__(32) arrive_kernel(unsigned long long* flags, const unsigned long long* flags_peer, int units, int slot,
                                                     int nranks, long long timeout_ns, unsigned* status) {
+  arrive_and_wait(flags, flags_peer, units, slot, nranks, timeout_ns, status ? status : g_wait_status);
+}
+// Epoch bump and barrier in one launch, for a replay whose first waiting call is a plain barrier: thread 0 advances
+// the epoch before anything of this launch reads it.
+__global__ void __launch_bounds__(32) epoch_arrive_kernel(unsigned long long* flags, const unsigned long long* flags_peer, int units, int slot,
+                                                          int nranks, long long timeout_ns, unsigned* status) {
+  if (threadIdx.x == 0) atomicAdd(&flags[0], (unsigned long long)units);
+  __syncwarp();
   arrive_and_wait(flags, flags_peer, units, slot, nranks, timeout_ns, status ? status : g_wait_status);
 }
 __global__ void __launch_bounds__(1024) allgather4_kernel(const unsigned char* s0, unsigned char* d0, const unsigned long long* p0, long long n0,
@@ -460,6 +510,16 @@ K3G_API int k3g_rs_arrive(void* flags, const void* flags_peer, int units, int sl
   K3G_REQUIRE(slot >= 1 && timeout_us > 0, K3G_ERANGE);
   arrive_kernel<<<1, 32, 0, k3g_stream(stream)>>>((unsigned long long*)flags, (const unsigned long long*)flags_peer, units, slot, nranks,
                                                  timeout_us * 1000LL, (unsigned*)status);
+  return k3g_launch_status();
+}
+
+K3G_API int k3g_epoch_arrive(void* flags, const void* flags_peer, int units, int slot, int nranks, long long timeout_us, void* status,
+                             void* stream) {
+  K3G_REQUIRE_PTR(flags); K3G_REQUIRE_PTR(flags_peer);
+  K3G_REQUIRE(nranks >= 1 && nranks <= K3G_MAX_RANKS && units > 0, K3G_ESHAPE);
+  K3G_REQUIRE(slot >= 1 && timeout_us > 0, K3G_ERANGE);
+  epoch_arrive_kernel<<<1, 32, 0, k3g_stream(stream)>>>((unsigned long long*)flags, (const unsigned long long*)flags_peer, units, slot, nranks,
+                                                       timeout_us * 1000LL, (unsigned*)status);
   return k3g_launch_status();
 }
 

@@ -24,40 +24,12 @@
 // reference's 1:2 job split.
 #include "k3g_device.cuh"
 #include "k3g_host.h"
+#include "situ_math.cuh"
 
 using namespace k3g;
 
 namespace {
 
-__device__ __forceinline__ float mufu_tanh(float x) {
-  float r;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-// The reference's formula, operation for operation (source/k3_land_fused.cu:88-92).
-__device__ __forceinline__ float situ_reference_form(float g, float u) {
-  const float a = 4.0f * mufu_tanh(g * 0.25f);
-  const float s = __frcp_rn(1.0f + __expf(-g));
-  const float c = 25.0f * mufu_tanh(u * 0.04f);
-  return (a * s) * c;
-}
-// The same function with fewer instructions; every step below is value-preserving:
-//  - __expf(-g) is ex2.approx(-g * log2 e); flushing a subnormal exponential to zero cannot change 1 + e;
-//  - x = 1 + e >= 1, where one Newton step on rcp.approx is the correctly rounded reciprocal as long as the
-//    result is a normal number (x <= 2^126); larger x (g < -87) takes the full-range reciprocal;
-//  - scaling by 4 is exact and commutes with rounding, so (4 t s) c = (t s)(4 c) and 4 (25 th) = 100 th.
-// tests/test_glue_small.py compares the two on every bf16 value of g and of u.
-__device__ __forceinline__ float situ_value(float g, float u) {
-  const float t = mufu_tanh(g * 0.25f);
-  float e, r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(g, -1.4426950408889634f)));
-  const float x = 1.0f + e;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  r = __fmaf_rn(r, __fmaf_rn(-x, r, 1.0f), r);
-  if (x > 0x1p126f) r = __frcp_rn(x);
-  const float c4 = 100.0f * mufu_tanh(u * 0.04f);
-  return (t * r) * c4;
-}
 __device__ __forceinline__ V8 situ_vec(const V8& g, const V8& u) {
   V8 o;
 #pragma unroll
@@ -396,15 +368,6 @@ extern "C" __global__ void __launch_bounds__(1024) kern_k3_rms(const __nv_bfloat
   }
 }
 
-// Element-wise SiTU of n (g, u) pairs with the production formula (literal = 0) or the reference's literal
-// formula (literal = 1): lets a test prove that the two agree on every bf16 input.
-__global__ void __launch_bounds__(256) situ_probe_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
-                                                         __nv_bfloat16* __restrict__ out, long long n, int literal) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const float gf = __bfloat162float(g[i]), uf = __bfloat162float(u[i]);
-    out[i] = __float2bfloat16_rn(literal ? situ_reference_form(gf, uf) : situ_value(gf, uf));
-  }
-}
 
 // out = bf16(attn * bf16(sigmoid(gate))), gate a strided per-head view: gate(t, h, d) = gate + t * tstride + h * hstride + d.
 extern "C" __global__ void __launch_bounds__(256) kern_sigmoid_mul_bf16(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ attn,
@@ -555,16 +518,6 @@ K3G_API int k3g_rms(const void* x, const void* gamma, void* o, int h, int B, voi
   if (B == 0) return K3G_OK;
   kern_k3_rms<<<(unsigned)((B + kRmsRows - 1) / kRmsRows), 128, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)gamma,
                                                                                         (__nv_bfloat16*)o, h, B);
-  return k3g_launch_status();
-}
-
-K3G_API int k3g_situ_probe(const void* g, const void* u, void* out, long long n, int literal, void* stream) {
-  K3G_REQUIRE_PTR(g); K3G_REQUIRE_PTR(u); K3G_REQUIRE_PTR(out);
-  K3G_REQUIRE(n >= 0, K3G_ESHAPE);
-  if (n == 0) return K3G_OK;
-  const long long blocks = (n + 255) / 256;
-  situ_probe_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, k3g_stream(stream)>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
-                                                                                              (__nv_bfloat16*)out, n, literal);
   return k3g_launch_status();
 }
 

@@ -10,8 +10,10 @@
 // x_{i-2} * w1))) (the reference build's contraction of its four-term sum); sb = bf16(y); out = bf16(sb * sigmoid(sb)); the new window is the last three
 // INPUT rows.  A thread owns 4 consecutive columns (8 bytes) and walks a run of rows with the three
 // previous inputs sliding in registers, four row loads in flight at a time, eight blocks per SM;
-// rows per block = ceil(span / gridDim.z), so the reference launch (16 rows) and a coarser one
-// (fewer halo re-reads) are both valid.  The sigmoid is ex2.approx + rcp.approx, as in the
+// rows per block = max(3, ceil(span / gridDim.z)), so the reference launch (16 rows) and a coarser one
+// (fewer halo re-reads) are both valid.  Three is the floor because only the block that starts at row 0
+// may read the stored window: it also overwrites it, and a block starting at row 1 or 2 would race with
+// that store.  The sigmoid is ex2.approx + rcp.approx, as in the
 // reference: two MUFU ops per element is what a 6.5 TB/s stream leaves room for.
 //
 // output gate.  16 lanes per head, 8 consecutive d per lane: ss = fma chain, xor-butterfly over
@@ -118,7 +120,8 @@ __device__ __forceinline__ void span_stream(const __nv_bfloat16* __restrict__ pa
   }
   if (row0 == 0) {
     // new window = inputs span-3 .. span-1 (old window rows when span < 3); this thread has
-    // already read every old tap it needs, and no other thread touches these columns
+    // already read every old tap it needs, and no other thread reads these columns of the window
+    // (blocks that start later begin at row >= 3: see the rows-per-block floor in span_gather_body)
     uint2 nw[3];
 #pragma unroll
     for (int t = 0; t < 3; ++t) {
@@ -156,7 +159,9 @@ __device__ __forceinline__ void span_gather_body(const __nv_bfloat16* __restrict
                                                  __nv_bfloat16* span_k, __nv_bfloat16* span_v, __nv_bfloat16* span_beta,
                                                  __nv_bfloat16* span_flow, int heads, int at, int span) {
   const int inner = heads * 128;
-  const int rpb = (span + gridDim.z - 1) / gridDim.z;
+  // at least three rows per block: blocks z >= 1 then start at row >= 3 and never read the window that the
+  // row-0 block of the same launch overwrites (a short span under a wide grid leaves the extra blocks idle)
+  const int rpb = max(3, (span + (int)gridDim.z - 1) / (int)gridDim.z);
   const int row0 = blockIdx.z * rpb, row1 = min(span, row0 + rpb);
   if (row0 >= span) return;
   if (blockIdx.y == 3) {
@@ -287,7 +292,8 @@ extern "C" __global__ void __launch_bounds__(128) kern_k3_kda_out_gate(const __n
 // Conv + SiLU on the three streams.  win: [3 streams][3 rows][inner] bf16, read as the initial
 // state and overwritten with the final one (zero-fill it for a zero initial state).  cw:
 // [3][4][inner] taps, f32 or bf16.  wsm_partial (f32 [rows, 256]) may be null: then span_beta /
-// span_flow are not produced.  rows_per_block <= 0 selects 64.
+// span_flow are not produced.  rows_per_block <= 0 selects 64; values below 3 are raised to 3 (the
+// window hand-over needs every block but the first to start at row >= 3).
 K3G_API int k3g_span_gather(const void* partial, long long row_stride, const void* cw, int taps_bf16, void* win, const void* wsm_partial,
                             void* span_q, void* span_k, void* span_v, void* span_beta, void* span_flow, int heads, int at, int span,
                             int rows_per_block, void* stream) {
@@ -297,7 +303,7 @@ K3G_API int k3g_span_gather(const void* partial, long long row_stride, const voi
   K3G_REQUIRE_ALIGNED(span_v);
   K3G_REQUIRE(heads > 0 && heads <= 512 && span >= 0 && at >= 0 && row_stride >= 3LL * heads * 128 && row_stride % 8 == 0, K3G_ESHAPE);
   if (span == 0) return K3G_OK;
-  const int rpb = rows_per_block > 0 ? rows_per_block : 64;
+  const int rpb = rows_per_block > 0 ? (rows_per_block < 3 ? 3 : rows_per_block) : 64;
   const int inner = heads * 128;
   const dim3 grid((inner + 511) / 512, wsm_partial ? 4 : 3, (span + rpb - 1) / rpb);
   K3G_REQUIRE(grid.z <= 65535, K3G_ELIMIT);

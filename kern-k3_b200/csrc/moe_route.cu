@@ -18,6 +18,8 @@
 #include "k3g_device.cuh"
 #include "k3g_host.h"
 
+#include <atomic>
+
 using namespace k3g;
 
 namespace {
@@ -28,7 +30,15 @@ constexpr int kRouteBlock = 256;   // tokens per routing block
 constexpr int kMaxTopk = 16;
 constexpr int kMaxGroups = kRouteBlock * kMaxTopk / 32;   // 128 groups of 32 expanded ids
 
+// rank >= 0: the slot of expert `id` among rank's E local experts, or -1 (source/k3_moe_prefill_v4.cu:100-109).
+// rank < 0 (C ABI only): every owner's experts at once, in owner-major order -- E is then the total expert count,
+// owner o holds E / ep_ranks of them and its slots are o * (E / ep_ranks) + its local slot, so the tables of the
+// ep_ranks owners come out of one pass, stacked, each equal to that owner's own table shifted by a constant row.
 __device__ __forceinline__ int local_expert(int id, int rank, int E, int ep_ranks, int strided) {
+  if (rank < 0) {
+    if (id < 0 || id >= E) return -1;
+    return strided ? (id % ep_ranks) * (E / ep_ranks) + id / ep_ranks : id;
+  }
   if (strided) {
     if (id % ep_ranks != rank) return -1;
     const int e = id / ep_ranks;
@@ -129,15 +139,102 @@ __device__ __forceinline__ void route_tables_body(const int* __restrict__ blockc
   }
 }
 
+// Shared-memory tables of one scatter block when the tables launch is folded into it.
+template <int MAXE>
+struct TablesInBlock {
+  int count[MAXE];       // tokens per expert over all blocks
+  int pre[MAXE];         // ... over the blocks before this one
+  int off[MAXE + 1];     // exclusive scan of ceil(count / tile)
+  int boff[MAXE];        // this block's row of blockoff
+};
+
+// What kern_k3_moe_route_tables computes, restricted to what block `blk` of the scatter needs (its row of
+// blockoff), with block 0 also producing the outputs that do not depend on the block: the CTA work list, the
+// two scalars and the padding rows of route_map.  Every value equals the stand-alone tables kernel's.
+template <int MAXE>
+__device__ __forceinline__ void block_tables(TablesInBlock<MAXE>& tb, const int* __restrict__ blockcount, int blocks, int blk, int E,
+                                             int tile, int* __restrict__ blockoff, int* __restrict__ cta_batch, int* __restrict__ cta_limit,
+                                             int* __restrict__ num_non_exiting, int* __restrict__ total_padded,
+                                             int* __restrict__ route_map) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, pre = 0;
+    for (int b = 0; b < blocks; ++b) {
+      const int c = blockcount[(size_t)b * E + e];      // threads walk adjacent experts: coalesced rows
+      pre += b < blk ? c : 0;
+      tot += c;
+    }
+    tb.count[e] = tot; tb.pre[e] = pre;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    constexpr int PER = MAXE / 32;
+    int c[PER], mine = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = PER * lane + j;
+      c[j] = e < E ? (tb.count[e] + tile - 1) / tile : 0;
+      mine += c[j];
+    }
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - mine;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = PER * lane + j;
+      if (e < E) tb.off[e] = run;
+      run += c[j];
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (lane == 0) {
+      tb.off[E] = total;
+      if (blk == 0) { num_non_exiting[0] = total; total_padded[0] = total * tile; }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int v = tb.off[e] * tile + tb.pre[e];
+    tb.boff[e] = v;
+    blockoff[(size_t)blk * E + e] = v;
+  }
+  if (blk == 0) {
+    const int nwarps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nwarps)              // padding rows of the expert's last tile route token 0
+      for (int r = tb.off[e] * tile + tb.count[e] + lane; r < tb.off[e + 1] * tile; r += 32) route_map[r] = 0;
+    for (int i = threadIdx.x; i < tb.off[E]; i += blockDim.x) {
+      int lo = 0, hi = E;
+      while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (tb.off[mid] <= i) lo = mid; else hi = mid; }
+      while (tb.off[lo + 1] <= i) ++lo;
+      cta_batch[i] = lo;
+      cta_limit[i] = min((i + 1) * tile, tb.off[lo] * tile + tb.count[lo]);
+    }
+  }
+  __syncthreads();
+}
+
 // hist: kMaxGroups x MAXE counters in shared memory (a count is at most 32 and a running offset at most 4096, so 16 bits do).
 template <int MAXE, typename HistT>
 __device__ __forceinline__ void route_scatter_body(const int* __restrict__ ids, const int* __restrict__ blockoff, int T, int rank,
                                                    int E, int topk, int ep_ranks, int strided, int* __restrict__ route_map,
-                                                   int* __restrict__ exp2perm, HistT (*hist)[MAXE]) {
+                                                   int* __restrict__ exp2perm, HistT (*hist)[MAXE], TablesInBlock<MAXE>* tb = nullptr,
+                                                   const int* __restrict__ blockcount = nullptr, int tile = 0, int* blockoff_out = nullptr,
+                                                   int* cta_batch = nullptr, int* cta_limit = nullptr, int* num_non_exiting = nullptr,
+                                                   int* total_padded = nullptr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const unsigned below = (1u << lane) - 1u;
   const int groups = kRouteBlock * topk / 32;
+  const int nblocks = (T + kRouteBlock - 1) / kRouteBlock;
   for (int blk = blockIdx.x; blk * kRouteBlock < T; blk += gridDim.x) {
+    if (tb != nullptr) {
+      // the tables launch folded in: this block derives its own row of block offsets from the per-block counts
+      // (and block 0 also writes the work list and the padding rows), so nothing waits on a one-block kernel
+      block_tables<MAXE>(*tb, blockcount, nblocks, blk, E, tile, blockoff_out, cta_batch, cta_limit, num_non_exiting, total_padded, route_map);
+    }
+    const int* boff_row = tb != nullptr ? tb->boff : blockoff + (size_t)blk * E;
     const long long base = (long long)blk * kRouteBlock * topk;
     const long long end = (long long)T * topk;
     for (int i = threadIdx.x; i < groups * MAXE; i += blockDim.x) (&hist[0][0])[i] = 0;
@@ -162,7 +259,7 @@ __device__ __forceinline__ void route_scatter_body(const int* __restrict__ ids, 
       const unsigned peers = __match_any_sync(0xffffffffu, e);
       if (i >= end) continue;
       if (e < 0) { exp2perm[i] = -1; continue; }
-      const int row = blockoff[(size_t)blk * E + e] + hist[g][e] + __popc(peers & below);
+      const int row = boff_row[e] + hist[g][e] + __popc(peers & below);
       route_map[row] = (int)(i / topk);
       exp2perm[i] = row;
     }
@@ -305,6 +402,96 @@ __global__ void __launch_bounds__(512) route_scatter_wide_kernel(const int* ids,
   route_scatter_body<kMaxEWide, unsigned short>(ids, blockoff, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm,
                                                 reinterpret_cast<unsigned short(*)[kMaxEWide]>(dyn_smem));
 }
+// tables + scatter in one launch (the per-block counts come from route_count_kernel)
+__global__ void __launch_bounds__(512) route_tables_scatter_kernel(const int* ids, const int* blockcount, int T, int rank, int E, int topk,
+                                                                   int ep_ranks, int strided, int tile, int* blockoff, int* cta_batch,
+                                                                   int* cta_limit, int* nne, int* total, int* route_map, int* exp2perm) {
+  __shared__ int hist[kMaxGroups][kMaxE];
+  __shared__ TablesInBlock<kMaxE> tb;
+  route_scatter_body<kMaxE, int>(ids, nullptr, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm, hist, &tb, blockcount, tile, blockoff,
+                                 cta_batch, cta_limit, nne, total);
+}
+__global__ void __launch_bounds__(512) route_tables_scatter_wide_kernel(const int* ids, const int* blockcount, int T, int rank, int E, int topk,
+                                                                        int ep_ranks, int strided, int tile, int* blockoff, int* cta_batch,
+                                                                        int* cta_limit, int* nne, int* total, int* route_map, int* exp2perm) {
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  __shared__ TablesInBlock<kMaxEWide> tb;
+  route_scatter_body<kMaxEWide, unsigned short>(ids, nullptr, T, rank, E, topk, ep_ranks, strided, route_map, exp2perm,
+                                                reinterpret_cast<unsigned short(*)[kMaxEWide]>(dyn_smem), &tb, blockcount, tile, blockoff,
+                                                cta_batch, cta_limit, nne, total);
+}
+
+// Dispatch to the owning ranks (benchmark configuration 2): the MXFP8 row of every token of this rank's shard is
+// stored, once per expert it routes to, straight into the expert-sorted buffer of the rank that owns the expert
+// -- a peer address over NVLink, or this rank's own buffer.  One warp per token: the row (cols code bytes and
+// cols / 32 scale bytes) is read from HBM once, in chunks of eight 16-byte vectors per lane, and each chunk is
+// stored to the token's topk destination rows, 512 contiguous bytes per warp instruction; the scale bytes leave
+// as 16-byte stores.  Destination of slot k: owner = rank that holds expert ids[t, k]; row = exp2perm[t, k] of
+// the all-owner tables minus the owner's first row (blockoff[owner * per], block 0 of the offsets table).
+// Plain stores only: no TMA, no multicast, nothing waits.  The caller follows with a barrier (k3g_rs_arrive).
+__global__ void __launch_bounds__(256) permute_dispatch_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                                               const int* __restrict__ ids, const int* __restrict__ exp2perm,
+                                                               const int* __restrict__ blockoff, int B, long long token_begin, int topk,
+                                                               int cols, int per, int ep_ranks, int strided,
+                                                               const unsigned long long* __restrict__ q_peer,
+                                                               const unsigned long long* __restrict__ sf_peer) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int qv = cols >> 4, sfb = cols >> 5;
+  const bool sf_vec = (sfb & 15) == 0;
+  // lane o keeps owner o's buffer addresses and first row
+  unsigned long long my_q = 0ull, my_sf = 0ull;
+  int my_base = 0;
+  if (lane < ep_ranks) { my_q = q_peer[lane]; my_sf = sf_peer[lane]; my_base = blockoff[lane * per]; }
+  for (long long b = warp; b < B; b += nwarps) {
+    const long long t = token_begin + b;
+    int owner = -1, row = -1;
+    if (lane < topk) {
+      const int id = ids[t * topk + lane];
+      row = exp2perm[t * topk + lane];
+      if (row >= 0) owner = strided ? id % ep_ranks : id / per;
+    }
+    const int base = __shfl_sync(0xffffffffu, my_base, owner < 0 ? 0 : owner);
+    const unsigned long long dq = __shfl_sync(0xffffffffu, my_q, owner < 0 ? 0 : owner);
+    const unsigned long long dsf = __shfl_sync(0xffffffffu, my_sf, owner < 0 ? 0 : owner);
+    const long long local_row = row >= 0 ? (long long)(row - base) : -1;
+    const uint4* src = reinterpret_cast<const uint4*>(q + b * cols);
+    for (int c0 = 0; c0 < qv; c0 += 8 * 32) {             // warp-uniform trip count: the shuffles below need every lane
+      const int v0 = c0 + lane;
+      uint4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (v0 + 32 * u < qv) x[u] = __ldcs(src + v0 + 32 * u);
+      for (int k = 0; k < topk; ++k) {
+        const long long r = __shfl_sync(0xffffffffu, local_row, k);
+        const unsigned long long d = __shfl_sync(0xffffffffu, dq, k);
+        if (r < 0) continue;
+        uint4* dst = reinterpret_cast<uint4*>(d + (unsigned long long)r * cols);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (v0 + 32 * u < qv) __stcs(dst + v0 + 32 * u, x[u]);
+      }
+    }
+    if (sf_vec) {
+      uint4 s4 = make_uint4(0u, 0u, 0u, 0u);
+      if (lane < (sfb >> 4)) s4 = __ldcs(reinterpret_cast<const uint4*>(sf + b * sfb) + lane);
+      for (int k = 0; k < topk; ++k) {
+        const long long r = __shfl_sync(0xffffffffu, local_row, k);
+        const unsigned long long d = __shfl_sync(0xffffffffu, dsf, k);
+        if (r >= 0 && lane < (sfb >> 4)) __stcs(reinterpret_cast<uint4*>(d + (unsigned long long)r * sfb) + lane, s4);
+      }
+    } else {
+      for (int k = 0; k < topk; ++k) {
+        const long long r = __shfl_sync(0xffffffffu, local_row, k);
+        const unsigned long long d = __shfl_sync(0xffffffffu, dsf, k);
+        if (r < 0) continue;
+        for (int i = lane; i < sfb; i += 32) reinterpret_cast<uint8_t*>(d)[r * sfb + i] = sf[b * sfb + i];
+      }
+    }
+  }
+}
+
 template <bool RESIDUAL>
 __global__ void __launch_bounds__(128) finalize_kernel(const __nv_bfloat16* fc2, const int* exp2perm, const float* wts,
                                                        const __nv_bfloat16* residual, __nv_bfloat16* out, int T, int cols, int topk) {
@@ -416,11 +603,32 @@ static int check_route(int T, int E, int topk, int ep_ranks) {
   return K3G_OK;
 }
 
+// rank in [0, ep_ranks), or -1 = every owner's experts in owner-major order (E is then the total and must divide evenly)
+static int check_route_rank(int rank, int E, int ep_ranks) {
+  K3G_REQUIRE(rank >= -1 && rank < ep_ranks, K3G_ERANGE);
+  if (rank < 0) K3G_REQUIRE(E % ep_ranks == 0, K3G_ESHAPE);
+  return K3G_OK;
+}
+
+// Raise the dynamic shared-memory limit of a wide (64 KB histogram) kernel once per device.
+template <typename Kernel>
+static int opt_in_wide_smem(Kernel kernel, std::atomic<bool>* opted, int bytes) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !opted[dev].load(std::memory_order_acquire)) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    opted[dev].store(true, std::memory_order_release);      // setting the attribute twice is harmless; the flag only saves the call
+  }
+  return K3G_OK;
+}
+constexpr int kWideSmem = kMaxGroups * kMaxEWide * (int)sizeof(unsigned short);      // 64 KB
+
 K3G_API int k3g_moe_route_count(const void* ids, int T, int rank, int E, int topk, int ep_ranks, int strided, void* blockcount,
                                 void* stream) {
   K3G_REQUIRE_PTR(ids); K3G_REQUIRE_PTR(blockcount);
   if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
-  K3G_REQUIRE(rank >= 0 && rank < ep_ranks, K3G_ERANGE);
+  if (int rc = check_route_rank(rank, E, ep_ranks)) return rc;
   if (T == 0) return K3G_OK;
   if (E <= kMaxE)
     route_count_kernel<kMaxE><<<(T + kRouteBlock - 1) / kRouteBlock, 256, 0, k3g_stream(stream)>>>((const int*)ids, T, rank, E, topk, ep_ranks,
@@ -449,23 +657,42 @@ K3G_API int k3g_moe_route_scatter(const void* ids, const void* blockoff, int T, 
                                   int strided, void* route_map, void* exp2perm, void* stream) {
   K3G_REQUIRE_PTR(ids); K3G_REQUIRE_PTR(blockoff); K3G_REQUIRE_PTR(route_map); K3G_REQUIRE_PTR(exp2perm);
   if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
-  K3G_REQUIRE(rank >= 0 && rank < ep_ranks, K3G_ERANGE);
+  if (int rc = check_route_rank(rank, E, ep_ranks)) return rc;
   if (T == 0) return K3G_OK;
   if (E <= kMaxE) {
     route_scatter_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 512, 0, k3g_stream(stream)>>>(
         (const int*)ids, (const int*)blockoff, T, rank, E, topk, ep_ranks, strided, (int*)route_map, (int*)exp2perm);
   } else {
-    constexpr int kWideSmem = kMaxGroups * kMaxEWide * (int)sizeof(unsigned short);      // 64 KB
-    static bool opted[64];
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !opted[dev]) {
-      if (cudaFuncSetAttribute(route_scatter_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmem) != cudaSuccess)
-        return k3g_launch_status();
-      opted[dev] = true;
-    }
+    static std::atomic<bool> opted[64];
+    if (int rc = opt_in_wide_smem(route_scatter_wide_kernel, opted, kWideSmem)) return rc;
     route_scatter_wide_kernel<<<(T + kRouteBlock - 1) / kRouteBlock, 512, kWideSmem, k3g_stream(stream)>>>(
         (const int*)ids, (const int*)blockoff, T, rank, E, topk, ep_ranks, strided, (int*)route_map, (int*)exp2perm);
+  }
+  return k3g_launch_status();
+}
+
+// route_tables + route_scatter in one launch: every scatter block derives its own row of block offsets from the
+// per-block counts, block 0 also writes the work list, the scalars and the padding rows.  All outputs bit-identical
+// to k3g_moe_route_tables followed by k3g_moe_route_scatter.
+K3G_API int k3g_moe_route_tables_scatter(const void* ids, const void* blockcount, int T, int rank, int E, int topk, int ep_ranks, int strided,
+                                         int tile, void* blockoff, void* cta_batch, void* cta_limit, void* num_non_exiting,
+                                         void* total_padded, void* route_map, void* exp2perm, void* stream) {
+  K3G_REQUIRE_PTR(ids); K3G_REQUIRE_PTR(blockcount); K3G_REQUIRE_PTR(blockoff); K3G_REQUIRE_PTR(cta_batch); K3G_REQUIRE_PTR(cta_limit);
+  K3G_REQUIRE_PTR(num_non_exiting); K3G_REQUIRE_PTR(total_padded); K3G_REQUIRE_PTR(route_map); K3G_REQUIRE_PTR(exp2perm);
+  if (int rc = check_route(T, E, topk, ep_ranks)) return rc;
+  if (int rc = check_route_rank(rank, E, ep_ranks)) return rc;
+  K3G_REQUIRE(tile > 0 && T > 0, K3G_ESHAPE);               // T = 0 has no block to write the scalars: use k3g_moe_route_tables
+  const int grid = (T + kRouteBlock - 1) / kRouteBlock;
+  if (E <= kMaxE) {
+    route_tables_scatter_kernel<<<grid, 512, 0, k3g_stream(stream)>>>((const int*)ids, (const int*)blockcount, T, rank, E, topk, ep_ranks,
+                                                                     strided, tile, (int*)blockoff, (int*)cta_batch, (int*)cta_limit,
+                                                                     (int*)num_non_exiting, (int*)total_padded, (int*)route_map, (int*)exp2perm);
+  } else {
+    static std::atomic<bool> opted[64];
+    if (int rc = opt_in_wide_smem(route_tables_scatter_wide_kernel, opted, kWideSmem)) return rc;
+    route_tables_scatter_wide_kernel<<<grid, 512, kWideSmem, k3g_stream(stream)>>>(
+        (const int*)ids, (const int*)blockcount, T, rank, E, topk, ep_ranks, strided, tile, (int*)blockoff, (int*)cta_batch, (int*)cta_limit,
+        (int*)num_non_exiting, (int*)total_padded, (int*)route_map, (int*)exp2perm);
   }
   return k3g_launch_status();
 }
@@ -503,6 +730,23 @@ K3G_API int k3g_permute_gather(const void* q, const void* sf, const void* route_
   if (grid > 148 * 64) grid = 148 * 64;            // then rows are walked with a warp stride
   permute_gather_kernel<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
                                                                        cols, (uint8_t*)out_q, (uint8_t*)out_sf);
+  return k3g_launch_status();
+}
+K3G_API int k3g_permute_dispatch(const void* q, const void* sf, const void* ids, const void* exp2perm, const void* blockoff, int B,
+                                 long long token_begin, int topk, int cols, int experts, int ep_ranks, int strided, const void* out_q_peer,
+                                 const void* out_sf_peer, void* stream) {
+  K3G_REQUIRE_PTR(q); K3G_REQUIRE_PTR(sf); K3G_REQUIRE_PTR(ids); K3G_REQUIRE_PTR(exp2perm); K3G_REQUIRE_PTR(blockoff);
+  K3G_REQUIRE_PTR(out_q_peer); K3G_REQUIRE_PTR(out_sf_peer);
+  K3G_REQUIRE_ALIGNED(q);
+  K3G_REQUIRE(B >= 0 && token_begin >= 0 && cols > 0 && cols % 32 == 0 && topk > 0 && topk <= kMaxTopk, K3G_ESHAPE);
+  K3G_REQUIRE(ep_ranks >= 1 && ep_ranks <= 8 && experts > 0 && experts <= kMaxEWide && experts % ep_ranks == 0, K3G_ESHAPE);
+  if ((cols >> 5) % 16 == 0) K3G_REQUIRE_ALIGNED(sf);
+  if (B == 0) return K3G_OK;
+  long long grid = (B + 7) / 8;                    // eight warps per block, one token per warp pass
+  if (grid > 148 * 8) grid = 148 * 8;
+  permute_dispatch_kernel<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>(
+      (const uint8_t*)q, (const uint8_t*)sf, (const int*)ids, (const int*)exp2perm, (const int*)blockoff, B, token_begin, topk, cols,
+      experts / ep_ranks, ep_ranks, strided, (const unsigned long long*)out_q_peer, (const unsigned long long*)out_sf_peer);
   return k3g_launch_status();
 }
 K3G_API int k3g_moe_w_shuffle(const void* src, void* dst, int experts, int n, int row_bytes, int gated, void* stream) {

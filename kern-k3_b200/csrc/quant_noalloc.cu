@@ -11,7 +11,8 @@
 //   * the array exists once per GPU that loads the library and lives until the process exits;
 //   * its size is a compile-time maximum (2048 block maxima = 8 KB), larger grids are refused;
 //   * every call on a device shares it, so two calls whose kernels overlap on that GPU race;
-//   * the first call on each device looks the array's address up (a host-side set-up step).
+//   * the first call on each device looks the array's address up (a host-side set-up step) and keeps it
+//     for the life of the process, so the device's primary context must live that long too.
 #include "k3g_device.cuh"
 #include "k3g_host.h"
 
@@ -119,7 +120,10 @@ int workspace_for_current_device(float** out) {
 //     must be serialised by the caller;
 //   * the first call on each device does a one-time host-side set-up (it looks up the device
 //     address of the workspace, with that device current).  Make that first call before starting
-//     any stream capture.
+//     any stream capture.  The address is cached per device ordinal until the process exits: a
+//     process that destroys the device's primary context and creates a new one (cudaDeviceReset, a
+//     test harness that tears contexts down) must not call this entry point again on that device,
+//     because the cached address belongs to the context that is gone.
 // The function itself calls no cudaMalloc / cudaFree and no allocating library routine.
 K3G_API int k3g_quant_fp8_tensor_noalloc(const void* x, void* y, void* scale_out, int n, int grid, void* stream) {
   K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(y);

@@ -9,9 +9,18 @@
 // Layout for B200: one WARP per token row (eight rows per 256-thread block, grid-stride), not
 // one block per row.  The row's 224 logits are loaded coalesced (7 x 128 B), each lane
 // evaluates the sigmoid of the expert it loaded and parks (sig, key) in shared memory, then
-// re-reads the 7 experts it owns for selection (expert = 7 * lane + j, a stride-7 pattern that
-// is bank-conflict free), so "smallest lane, then smallest slot" is "smallest expert id".
-// Each pick is one REDUX.MAX on the monotone u32 key and one REDUX.MIN on the expert id.
+// re-reads the keys of the 7 consecutive experts it owns (expert = 7 * lane + j, a stride-7
+// pattern that is bank-conflict free).
+//
+// Selection = a K-way merge of 32 sorted runs.  A candidate is one 64-bit word: the monotone
+// image of its biased score in the high half, 255 - expert id in the low half, so unsigned order
+// is "larger score first, then smaller expert id" and no two candidates compare equal.  Each
+// lane sorts its seven candidates once with a 16-exchange network; after that its best
+// remaining candidate always sits in run[0].  A pick is then: one REDUX.MAX over the lanes'
+// run[0] scores, one ballot of the lanes that hold that score -- the lowest such lane owns the
+// smallest expert id, because lanes own ascending id ranges and a run is already ordered by id
+// among equal scores -- one shuffle of the winner's id, and the winner shifts its run up by one.
+// The picked experts' sigmoids are fetched from shared memory after the last pick.
 //
 // The sigmoid is evaluated with IEEE-only operations (k3g::det_sigmoid): the indices depend on
 // it, and this makes them reproducible bit for bit by any IEEE host.
@@ -26,9 +35,16 @@ constexpr int kExperts = 224;
 constexpr int kPerLane = kExperts / 32;   // 7
 constexpr int kRowsPerBlock = 8;
 
+// Order-preserving map from float to u32: negative values have all bits flipped, the others only the sign bit.
 __device__ __forceinline__ unsigned ord_f32(float f) {
-  const unsigned b = __float_as_uint(f);
-  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  const int b = __float_as_int(f);
+  return (unsigned)b ^ ((unsigned)(b >> 31) | 0x80000000u);
+}
+
+__device__ __forceinline__ void sort2_desc(unsigned long long& hi, unsigned long long& lo) {
+  const unsigned long long a = hi, b = lo;
+  hi = a > b ? a : b;
+  lo = a > b ? b : a;
 }
 
 template <int K>
@@ -48,6 +64,7 @@ __device__ __forceinline__ void router_rows(const float* __restrict__ S, const f
     float lg[kPerLane];
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) lg[i] = __ldcs(Sr + 32 * i + lane);
+    __syncwarp();                                    // the previous row's sigmoids have been read by every lane
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
       const float sg = det_sigmoid(lg[i]);
@@ -55,39 +72,36 @@ __device__ __forceinline__ void router_rows(const float* __restrict__ S, const f
       s_key[warp][32 * i + lane] = ord_f32(__fadd_rn(sg, bia[i]));
     }
     __syncwarp();
-    unsigned o[kPerLane];
-    float g[kPerLane];
+    unsigned long long run[kPerLane];
 #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
-      o[j] = s_key[warp][lane * kPerLane + j];
-      g[j] = s_sig[warp][lane * kPerLane + j];
+      const int e = lane * kPerLane + j;
+      run[j] = ((unsigned long long)s_key[warp][e] << 32) | (unsigned)(255 - e);
     }
-    __syncwarp();
+    // seven candidates, descending: optimal 16-exchange network
+    sort2_desc(run[0], run[6]); sort2_desc(run[2], run[3]); sort2_desc(run[4], run[5]);
+    sort2_desc(run[0], run[2]); sort2_desc(run[1], run[4]); sort2_desc(run[3], run[6]);
+    sort2_desc(run[0], run[1]); sort2_desc(run[2], run[5]); sort2_desc(run[3], run[4]);
+    sort2_desc(run[1], run[2]); sort2_desc(run[4], run[6]);
+    sort2_desc(run[2], run[3]); sort2_desc(run[4], run[5]);
+    sort2_desc(run[1], run[2]); sort2_desc(run[3], run[4]); sort2_desc(run[5], run[6]);
 
-    int my_e = 0;       // lane r keeps pick r
-    float my_w = 0.f;
+    int my_e = 0;                                    // lane r keeps pick r
 #pragma unroll
     for (int r = 0; r < K; ++r) {
-      unsigned m = o[0];
+      const unsigned head = (unsigned)(run[0] >> 32);            // 0 once a run is used up: below the image of every float
+      const unsigned best = __reduce_max_sync(0xffffffffu, head);
+      const int winner = __ffs(__ballot_sync(0xffffffffu, head == best)) - 1;
+      const int e = 255 - (int)__shfl_sync(0xffffffffu, (unsigned)run[0], winner);
+      if (lane == r) my_e = e;
+      if (lane == winner) {
 #pragma unroll
-      for (int j = 1; j < kPerLane; ++j) m = max(m, o[j]);
-      m = __reduce_max_sync(0xffffffffu, m);
-      unsigned mine = 0xffffffffu;
-#pragma unroll
-      for (int j = kPerLane - 1; j >= 0; --j)
-        if (o[j] == m) mine = (unsigned)(lane * kPerLane + j);
-      const unsigned ew = __reduce_min_sync(0xffffffffu, mine);
-      float gw = 0.f;
-      if (mine == ew) {
-        const int jw = (int)ew - lane * kPerLane;
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j)
-          if (j == jw) { gw = g[j]; o[j] = 0u; }     // 0 is below the key of every real float
+        for (int j = 0; j + 1 < kPerLane; ++j) run[j] = run[j + 1];
+        run[kPerLane - 1] = 0ull;
       }
-      gw = __shfl_sync(0xffffffffu, gw, (int)(ew / kPerLane));
-      if (lane == r) { my_e = (int)ew; my_w = gw; }
     }
-    float den = (lane < K) ? my_w : 0.f;
+    const float my_w = lane < K ? s_sig[warp][my_e] : 0.f;
+    float den = my_w;
 #pragma unroll
     for (int off = K / 2; off > 0; off >>= 1) den = __fadd_rn(den, __shfl_xor_sync(0xffffffffu, den, off));
     if (lane < K) {

@@ -69,6 +69,27 @@ def test_flag_protocol_world1(k3g, dev):
     assert not status.cpu().numpy().any()
 
 
+def test_epoch_bump_folded_into_the_first_barrier(k3g, dev):
+    """k3g_epoch_arrive = epoch bump + arrive in one launch: same counters as the two calls."""
+    import torch
+    flags = _flags(dev)
+    tab = _table([flags], dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    s = k3g.current_stream()
+    for replay in range(3):
+        k3g.call("k3g_epoch_arrive", flags, tab, 896, 1, 1, 1000, status, s)
+        k3g.call("k3g_rs_arrive", flags, tab, 896, 2, 1, 1000, status, s)
+    torch.cuda.synchronize()
+    f = flags.cpu().numpy()
+    assert f[0] == f[1] == f[2] == 3 * 896 and not status.cpu().numpy().any()
+    # a peer that has not arrived in this epoch makes it expire like k3g_rs_arrive
+    peer = _flags(dev)
+    tab2 = _table([flags, peer], dev)
+    k3g.call("k3g_epoch_arrive", flags, tab2, 896, 3, 2, 1000, status, s)
+    torch.cuda.synchronize()
+    assert list(status.cpu().numpy()[:3]) == [1, 3, 1] and int(flags[0]) == 4 * 896
+
+
 def test_bounded_wait_reports_and_returns(k3g, dev):
     """Rank 0 of an emulated world of 2 waits on a peer counter that nothing advances: the wait runs
     out after the 1 ms limit, records {1, slot, peer, observed} and the kernel returns normally."""
@@ -100,6 +121,33 @@ def test_bounded_wait_reports_and_returns(k3g, dev):
     assert list(host) == [1, 4, 1, 0]
     k3g.call("k3g_wait_status", host, 0, s)
     assert not host.any()
+
+
+def test_wait_compares_full_64_bit_counters(k3g, dev):
+    """Counters are never reset, so a long-lived process crosses 2^32 arrivals.  With the epoch just above
+    2^32 and the peer's counter just below it, the low 32 bits of the peer (0xfffffffc) exceed those of the
+    epoch (4): a 32-bit compare would pass at once.  The wait must expire; once the peer really arrives it passes."""
+    import torch
+    mine, peer = _flags(dev), _flags(dev)
+    tab = _table([mine, peer], dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    s = k3g.current_stream()
+    mine[0] = (1 << 32) + 4; mine[3] = (1 << 32)                 # own slot one step behind its epoch
+    peer[3] = (1 << 32) - 4
+    k3g.call("k3g_rs_arrive", mine, tab, 4, 3, 2, 1000, status, s)
+    torch.cuda.synchronize()
+    st = status.cpu().numpy().view(np.uint32)
+    assert list(st) == [1, 3, 1, 0xfffffffc]
+    assert int(mine[3]) == (1 << 32) + 4
+    peer[3] = (1 << 32) + 4
+    status.zero_()
+    k3g.call("k3g_rs_arrive", mine, tab, 4, 4, 2, 1000, status, s)   # slot 4: both sides at zero, epoch far ahead -> expires
+    torch.cuda.synchronize()
+    assert status.cpu().numpy()[0] == 1
+    status.zero_(); mine[4] = (1 << 32); peer[4] = (1 << 32) + 4
+    k3g.call("k3g_rs_arrive", mine, tab, 4, 4, 2, 1000, status, s)
+    torch.cuda.synchronize()
+    assert not status.cpu().numpy().any()
 
 
 @pytest.mark.parametrize("W", [1, 2, 4, 8])

@@ -35,13 +35,26 @@ def test_situ_formula_equals_the_reference_form_on_every_bf16_input(k3g, dev):
     sigmoid's reciprocal is subnormal included.  NaN results only have to be NaN in both."""
     import torch
     bits = lambda lo, hi: (torch.arange(lo, hi, dtype=torch.int32, device=dev) << 16 >> 16).to(torch.int16)   # sign-extend 16 bits
+    import ctypes
+    import os
+    so = os.path.join(os.path.dirname(os.path.abspath(__file__)), "native", "libk3g_probe.so")
+    if not os.path.exists(so):
+        import sys
+        sys.path.insert(0, os.path.dirname(so))
+        import build_probe
+        build_probe.build()
+    probe_fn = ctypes.CDLL(so).k3g_test_situ_probe                # test-only probe: both formulas from the library's own header
+    probe_fn.restype = ctypes.c_int
+    probe_fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p]
+
+    def probe(gt, ut, ot, literal):
+        assert probe_fn(gt.data_ptr(), ut.data_ptr(), ot.data_ptr(), ut.numel(), literal, k3g.current_stream()) == 0
     u = bits(0, 65536).repeat(1024).view(torch.bfloat16)
     o0 = torch.empty(u.numel(), dtype=torch.bfloat16, device=dev); o1 = torch.empty_like(o0)
-    s = k3g.current_stream()
     for c in range(64):
         g = bits(c * 1024, (c + 1) * 1024).repeat_interleave(65536).view(torch.bfloat16)
-        k3g.call("k3g_situ_probe", g, u, o0, u.numel(), 0, s)
-        k3g.call("k3g_situ_probe", g, u, o1, u.numel(), 1, s)
+        probe(g, u, o0, 0)
+        probe(g, u, o1, 1)
         a, b = o0.view(torch.int16), o1.view(torch.int16)
         bad = (a != b) & ~(torch.isnan(o0) & torch.isnan(o1))
         if bool(bad.any()):

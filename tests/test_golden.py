@@ -44,15 +44,14 @@ def test_stats_handoff_oracle_vs_reference(golden):
 
 
 def test_router_oracle_vs_reference_indices(golden):
-    """The reference uses libdevice expf, the oracle an IEEE-only exp: picks may only differ where two
-    biased scores are within a few ulps; weights agree to 1e-6 relative where the picks agree."""
+    """The reference uses libdevice expf, the oracle an IEEE-only exp, so a pick can differ only where two biased
+    scores are within a few f32 ulps of each other.  On the recorded 96 rows no row differs; the bar allows one
+    row, requires every differing pick to be such a near-tie, and the weights to agree where the picks agree."""
+    from util import router_picks_differ_only_at_near_ties
     inp = cases.inputs("router")
     out = cases.run_oracle("router", inp)
     ref_idx, ref_w = golden["router/idx"], golden["router/wts"]
+    differing, _ = router_picks_differ_only_at_near_ties(inp["S"], inp["bias"], out["idx"], ref_idx, ulps=4)
+    assert differing <= 1
     same = (out["idx"] == ref_idx).all(axis=1)
-    assert same.mean() >= 0.97
     assert np.allclose(out["wts"][same], ref_w[same], rtol=2e-6, atol=0)
-    sig = 1.0 / (1.0 + np.exp(-inp["S"].astype(np.float64))) + inp["bias"]
-    for b in np.nonzero(~same)[0]:
-        for r in np.nonzero(out["idx"][b] != ref_idx[b])[0]:
-            assert abs(sig[b, out["idx"][b, r]] - sig[b, ref_idx[b, r]]) < 1e-6   # an exact near-tie

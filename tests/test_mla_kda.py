@@ -63,7 +63,8 @@ def test_mla_prep_rope_pack(k3g, dev, T, heads):
 
 
 @pytest.mark.parametrize("taps_bf16", [False, True])
-@pytest.mark.parametrize("heads,rows,at,span,rpb", [(24, 40, 0, 40, 16), (24, 70, 3, 61, 32), (2, 9, 0, 2, 32), (2, 5, 1, 1, 4), (24, 300, 0, 300, 0)])
+@pytest.mark.parametrize("heads,rows,at,span,rpb", [(24, 40, 0, 40, 16), (24, 70, 3, 61, 32), (2, 9, 0, 2, 32), (2, 5, 1, 1, 4), (24, 300, 0, 300, 0),
+                                                    (2, 9, 0, 9, 1), (24, 40, 0, 40, 2), (2, 70, 0, 70, 1)])
 def test_span_conv_silu(k3g, dev, taps_bf16, heads, rows, at, span, rpb):
     import torch
     g = rng(heads * 1000 + span)

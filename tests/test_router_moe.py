@@ -49,7 +49,7 @@ def test_router_ties_and_extremes(k3g, dev):
     assert np.isfinite(g_w).all()
 
 
-def _route(k3g, dev, ids, rank, E, ep, strided, tile):
+def _route(k3g, dev, ids, rank, E, ep, strided, tile, fused=False):
     import torch
     T, topk = ids.shape
     blocks = (T + 255) // 256
@@ -62,8 +62,11 @@ def _route(k3g, dev, ids, rank, E, ep, strided, tile):
     e2p = torch.full((T, topk), -9, dtype=torch.int32, device=dev)
     s = k3g.current_stream()
     k3g.call("k3g_moe_route_count", d_ids, T, rank, E, topk, ep, strided, bc, s)
-    k3g.call("k3g_moe_route_tables", bc, blocks, E, tile, bo, cb, cl, nne, tot, rm, s)
-    k3g.call("k3g_moe_route_scatter", d_ids, bo, T, rank, E, topk, ep, strided, rm, e2p, s)
+    if fused:                                                     # tables folded into the scatter launch
+        k3g.call("k3g_moe_route_tables_scatter", d_ids, bc, T, rank, E, topk, ep, strided, tile, bo, cb, cl, nne, tot, rm, e2p, s)
+    else:
+        k3g.call("k3g_moe_route_tables", bc, blocks, E, tile, bo, cb, cl, nne, tot, rm, s)
+        k3g.call("k3g_moe_route_scatter", d_ids, bo, T, rank, E, topk, ep, strided, rm, e2p, s)
     torch.cuda.synchronize()
     return dict(blockcount=bc, blockoff=bo, cta_batch=cb, cta_limit=cl, num_non_exiting=nne, total_padded=tot, route_map=rm,
                 exp2perm=e2p)
@@ -90,6 +93,86 @@ def test_route_tables_bit_exact(k3g, dev, T, topk, ep, strided, tile):
         live = e2p >= 0
         assert len(np.unique(e2p[live])) == live.sum()
         assert np.array_equal(rm[e2p[live]], np.nonzero(live)[0])
+
+
+@pytest.mark.parametrize("T,topk,ep,strided,tile", [(1, 16, 4, 1, 128), (4097, 16, 4, 1, 128), (16384, 16, 4, 1, 128), (16384, 8, 1, 0, 1),
+                                                   (3000, 8, 2, 0, 128), (777, 8, 8, 1, 1), (16384, 16, 1, 1, 128), (16384, 8, 8, 0, 128)])
+def test_route_tables_folded_into_scatter(k3g, dev, T, topk, ep, strided, tile):
+    """count + (tables + scatter in one launch) leaves every table bit-identical to the oracle's three steps."""
+    g = rng(T * 5 + topk + ep)
+    ids = _ids(g, T, topk)
+    E = 224 // ep
+    for rank in sorted({0, ep - 1}):
+        o = k3o.moe_route(ids, rank, E, ep, strided, tile)
+        d = _route(k3g, dev, ids, rank, E, ep, strided, tile, fused=True)
+        for k in o:
+            assert np.array_equal(d[k].cpu().numpy().reshape(o[k].shape), o[k]), (k, rank)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("T,topk,ep,strided,tile", [(16384, 8, 8, 1, 128), (16384, 8, 4, 0, 128), (5000, 16, 2, 1, 128), (700, 8, 8, 0, 1),
+                                                   (16384, 8, 1, 0, 128)])
+def test_route_tables_of_every_owner_at_once(k3g, dev, T, topk, ep, strided, tile, fused):
+    """rank = -1 builds the tables of all `ep` owners in one pass, stacked owner-major: owner o's slice, shifted by
+    its first row, must be exactly the tables the oracle builds for rank o alone (the reference's per-rank tables)."""
+    g = rng(T * 7 + topk + ep + strided)
+    ids = _ids(g, T, topk)
+    per = 224 // ep
+    d = _route(k3g, dev, ids, -1, 224, ep, strided, tile, fused=fused)
+    e2p_all, rm_all, bo_all = d["exp2perm"].cpu().numpy(), d["route_map"].cpu().numpy(), d["blockoff"].cpu().numpy()
+    owner = ids % ep if strided else ids // per
+    total = 0
+    for o in range(ep):
+        t = k3o.moe_route(ids, o, per, ep, strided, tile)
+        base = int(bo_all[0, o * per])
+        assert base == total                                       # owners are stacked without gaps
+        rows = int(t["total_padded"][0])
+        mine = owner == o
+        assert np.array_equal(e2p_all[mine] - base, t["exp2perm"][mine])
+        assert np.array_equal(rm_all[base:base + rows], t["route_map"][:rows])
+        assert np.array_equal(bo_all[:, o * per:(o + 1) * per] - base, t["blockoff"])
+        total += rows
+    assert int(d["total_padded"].cpu().numpy()[0]) == total
+
+
+def _dispatch_case(k3g, dev, T, topk, ep, strided, tile, cols, seed):
+    """All `ep` ranks emulated on one GPU (the dispatch kernel never waits): rank r dispatches its T / ep tokens into
+    the ep owners' buffers; returns what every owner received and the oracle's expert-sorted rows."""
+    import torch
+    g = rng(seed)
+    ids = _ids(g, T, topk)
+    per, B = 224 // ep, T // ep
+    q = g.integers(0, 256, (T, cols), dtype=np.uint8); sf = g.integers(0, 256, (T, cols // 32), dtype=np.uint8)
+    d = _route(k3g, dev, ids, -1, 224, ep, strided, tile, fused=True)
+    want = [k3o.moe_route(ids, o, per, ep, strided, tile) for o in range(ep)]
+    rows = [int(w["total_padded"][0]) for w in want]
+    out_q = [torch.full((max(r, 1), cols), 0xEE, dtype=torch.uint8, device=dev) for r in rows]
+    out_sf = [torch.full((max(r, 1), cols // 32), 0xEE, dtype=torch.uint8, device=dev) for r in rows]
+    tq = torch.tensor([t.data_ptr() for t in out_q], dtype=torch.int64, device=dev)
+    tsf = torch.tensor([t.data_ptr() for t in out_sf], dtype=torch.int64, device=dev)
+    d_ids, dq, dsf = to_dev(ids, dev), to_dev(q, dev), to_dev(sf, dev)
+    for r in range(ep):
+        k3g.call("k3g_permute_dispatch", dq[r * B:(r + 1) * B], dsf[r * B:(r + 1) * B], d_ids, d["exp2perm"], d["blockoff"], B, r * B, topk, cols,
+                 224, ep, strided, tq, tsf, k3g.current_stream())
+    torch.cuda.synchronize()
+    return q, sf, want, rows, out_q, out_sf
+
+
+@pytest.mark.parametrize("T,topk,ep,strided,tile,cols", [(64, 8, 2, 0, 1, 7168), (1000, 8, 4, 1, 128, 7168), (504, 16, 8, 1, 128, 3584),
+                                                        (96, 8, 8, 0, 16, 96), (300, 8, 1, 0, 128, 7168), (8, 8, 8, 1, 128, 7168)])
+def test_permute_dispatch_to_owning_ranks(k3g, dev, T, topk, ep, strided, tile, cols):
+    """Every owner's buffer holds, on the live rows of its own expert-sorted order, exactly what the oracle's
+    permute_gather builds from that owner's route_map; the tile-padding rows are not written."""
+    q, sf, want, rows, out_q, out_sf = _dispatch_case(k3g, dev, T, topk, ep, strided, tile, cols, T + ep + cols)
+    for o in range(ep):
+        if rows[o] == 0:
+            continue
+        o_q, o_sf = k3o.permute_gather(q, sf, want[o]["route_map"], rows[o])
+        live = np.zeros(rows[o], bool)
+        live[want[o]["exp2perm"][want[o]["exp2perm"] >= 0]] = True
+        got_q, got_sf = out_q[o].cpu().numpy(), out_sf[o].cpu().numpy()
+        assert np.array_equal(got_q[live], o_q[live]) and np.array_equal(got_sf[live], o_sf[live]), o
+        assert (got_q[~live] == 0xEE).all() and (got_sf[~live] == 0xEE).all()
 
 
 def test_route_empty_experts_and_duplicates(k3g, dev):

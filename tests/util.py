@@ -42,3 +42,19 @@ def fp8_code_diff(a, b):
         x = x.astype(np.int32)
         return np.where(x & 0x80, -(x & 0x7F), x & 0x7F)
     return np.abs(key(a) - key(b))
+
+
+def router_picks_differ_only_at_near_ties(S, bias, idx_a, idx_b, ulps=4):
+    """Two top-k results for the same logits may differ only where the competing biased scores (sigmoid + bias, an
+    f32 quantity) lie within `ulps` f32 ulps of each other: at every position where the picks differ, the two
+    experts' scores must be that close.  Returns (rows that differ, worst gap in ulps); raises on a wider gap."""
+    sig = 1.0 / (1.0 + np.exp(-S.astype(np.float64))) + bias.astype(np.float64)
+    rows = np.nonzero((idx_a != idx_b).any(axis=1))[0]
+    worst = 0.0
+    for b in rows:
+        for r in np.nonzero(idx_a[b] != idx_b[b])[0]:
+            x, y = sig[b, idx_a[b, r]], sig[b, idx_b[b, r]]
+            gap = abs(x - y) / float(np.spacing(np.float32(max(abs(x), abs(y)))))
+            worst = max(worst, gap)
+            assert gap < ulps, "row %d pick %d: experts %d / %d have scores %.9g / %.9g, %.1f ulps apart" % (b, r, idx_a[b, r], idx_b[b, r], x, y, gap)
+    return len(rows), worst

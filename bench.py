@@ -6,15 +6,19 @@ One "step" is benchmark configuration 1 at world N over T = 16384 tokens x d = 7
 each rank holds a bf16 partial-sum matrix [T, d]; the step reduce-scatters it into T/N-row shards
 (in-kernel NVLink pull, ring-order bf16 chain), applies residual add + RMSNorm + MXFP8 to the shard
 and all-gathers codes and scales back to every rank (in-kernel push), bracketed by the two
-arrive/poll barriers.  Metric: microseconds per step ("per-layer glue us at 16k tokens"; lower is
-better; total work is fixed as N grows, i.e. strong scaling).  Inputs are synthetic and seeded,
-larger than the 126 MB L2 (470 MB read per step at N = 1), so no L2 flush is needed.
+arrive/poll barriers.  `value` is microseconds per such step (lower is better; total work is fixed
+as N grows, i.e. strong scaling); the whole per-layer program (every non-GEMM call of a KDA and an
+MLA layer, 69:24 weighted) is timed too and reported as `layer_glue_us` with its per-call table
+under `layer_glue`.  Inputs are synthetic and seeded, larger than the 126 MB L2 (470 MB read per
+step at N = 1), so no L2 flush is needed.
 
 Rank 0 prints ONE JSON line.  `value` is timed with inputs resident in HBM; `e2e` is the same step
 through host (pinned) buffers with the H2D / D2H copies inside the timed region.  `roofline`
-describes the fused kernel; `cpu_baseline` is the CPU oracle (test infrastructure, oracle/) timed on
-this box's host cores on a bounded sample.  `--impl reference` times that CPU oracle as the
-reference arm (the reference project has no CPU path and no host API of its own).
+describes the fused kernel; `verified_rows` / `mismatches` compare a seeded sample of the gathered
+codes, scales and residual rows of every rank with the CPU oracle after the timed region (the run
+fails on a mismatch); `cpu_baseline` is the CPU oracle (test infrastructure, oracle/) timed on this
+box's host cores on the full workload.  `--impl reference` times that CPU oracle as the reference
+arm (the reference project has no CPU path and no host API of its own).
 """
 import argparse
 import json
@@ -29,6 +33,15 @@ sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
 TOKENS, HIDDEN, EPS = 16384, 7168, 1e-6
 METRIC, UNIT = "per-layer glue us at 16k tokens", "us"
 CPU_SAMPLE_ROWS = 2048
+SEED = 0x5EED
+
+
+def workload_config(world):
+    """The `config` object, identical in both arms."""
+    return {"workload": "config1 step: TP reduce-scatter -> residual add + RMSNorm + MXFP8 -> all-gather, T=16384 d=7168, world=%d "
+                        "(the per-layer program of the metric's name is timed beside it: layer_glue_us)" % world,
+            "tokens": TOKENS, "d": HIDDEN, "world": world, "eps": EPS,
+            "l2": "inputs (470 MB read per step at world 1) exceed the 126 MB L2; no flush"}
 
 
 def measured_peaks():
@@ -100,51 +113,65 @@ def physical_gpu_index(local_rank):
     return local_rank
 
 
-def cpu_oracle_us(steps, warmup, world=1):
+def cpu_oracle_us(steps, warmup, world=1, budget_s=200.0):
     """The CPU oracle's version of the whole step at world `world`, emulated on the host: for every rank the ring-order
-    reduce-scatter chain over the `world` partial buffers, then residual + RMSNorm + MXFP8 of that rank's shard -- all
-    16384 rows, no sampling.  (The all-gather is a no-op on one host: the outputs already sit in one address space.)"""
+    reduce-scatter chain over the `world` partial buffers, then residual + RMSNorm + MXFP8 of that rank's shard.  (The
+    all-gather is a no-op on one host: the outputs already sit in one address space.)  Every step covers all 16384 rows
+    unless `warmup + steps` such steps would exceed `budget_s`; then each step covers the first 1/k of every shard's rows
+    and the time is scaled by k (the work is row-independent).  Returns (us per full step, threads, description)."""
     import numpy as np
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import k3o
     g = np.random.Generator(np.random.Philox(7))
     tile = lambda a: np.ascontiguousarray(np.tile(a, (TOKENS // CPU_SAMPLE_ROWS, 1)))       # 2048 seeded rows repeated: set-up time, not data, is saved
-    partial = tile(k3o.f32_to_bf16(g.standard_normal((CPU_SAMPLE_ROWS, HIDDEN), dtype=np.float32) * np.float32(0.5 / world))).reshape(-1)
+    partial = tile(k3o.f32_to_bf16(g.standard_normal((CPU_SAMPLE_ROWS, HIDDEN), dtype=np.float32) * np.float32(0.5 / world)))
     residual = tile(k3o.f32_to_bf16(g.standard_normal((CPU_SAMPLE_ROWS, HIDDEN), dtype=np.float32)))
     gamma = k3o.f32_to_bf16((1 + 0.02 * g.standard_normal(HIDDEN, dtype=np.float32)).astype(np.float32))
-    partials = [partial] * world                       # every rank's partial buffer (the same values: timing only)
     rows = TOKENS // world
-    times = []
-    for i in range(warmup + steps):
+
+    def one_step(frac):
+        n = max(1, rows // frac)
+        # every rank's partial buffer restricted to the first n rows of each shard (the same values in every buffer: timing only)
+        part = np.ascontiguousarray(partial.reshape(world, rows, HIDDEN)[:, :n]).reshape(-1) if frac > 1 else partial.reshape(-1)
+        parts = [part] * world
         t0 = time.perf_counter()
         for r in range(world):
-            delta = k3o.rs_pull(partials, r, 2 * (world - 1)).reshape(rows, HIDDEN)
-            k3o.resnorm_mxfp8(residual[r * rows:(r + 1) * rows], delta, gamma, EPS, want_normed=False)
+            delta = k3o.rs_pull(parts, r, 2 * (world - 1)).reshape(n, HIDDEN)
+            k3o.resnorm_mxfp8(residual[r * rows:r * rows + n], delta, gamma, EPS, want_normed=False)
+        return time.perf_counter() - t0
+
+    first = one_step(1)                                   # also pages everything in
+    frac = 1
+    while first / frac * (steps + warmup) > budget_s and frac < 64:
+        frac *= 2
+    times = []
+    for i in range(warmup + steps):
+        dt = one_step(frac)
         if i >= warmup:
-            times.append(time.perf_counter() - t0)
-    return sum(times) / len(times) * 1e6, k3o.num_threads()
-
-
-CPU_SAMPLE = "the full workload every step: all %d rows, world %d emulated on the host (ring-order reduce-scatter chain over the partial buffers, then residual + RMSNorm + MXFP8 of every shard), C++/OpenMP oracle, mean of %d steps"
+            times.append(dt * frac)
+    what = ("the full workload every step: all %d rows" % TOKENS) if frac == 1 else (
+        "a bounded sample every step: the first 1/%d of every shard's rows (%d of %d rows), time scaled by %d" % (frac, TOKENS // frac, TOKENS, frac))
+    sample = "%s, world %d emulated on the host (ring-order reduce-scatter chain over the partial buffers, then residual + RMSNorm + MXFP8 of " \
+             "every shard), C++/OpenMP oracle, mean of %d steps after %d warm-up steps" % (what, world, steps, warmup)
+    return sum(times) / len(times) * 1e6, k3o.num_threads(), sample
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    steps, warm = max(1, min(args.steps, 20)), min(args.warmup, 2)
+    steps, warm = max(1, args.steps), max(0, args.warmup)
     world = args.gpus if args.gpus in (1, 2, 4, 8) else 1
-    us, cores = cpu_oracle_us(steps, warm, world)
-    sample = CPU_SAMPLE % (TOKENS, world, steps)
+    us, cores, sample = cpu_oracle_us(steps, warm, world)
     line = {"impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "config1: TP reduce-scatter -> residual add + RMSNorm + MXFP8 -> all-gather, T=16384 d=7168, world=%d" % world,
-                       "tokens": TOKENS, "d": HIDDEN, "world": world, "note": "CPU oracle on the host cores (the reference has no CPU implementation)"},
+            "config": workload_config(world), "note": "CPU oracle on the host cores (the reference has no CPU implementation)",
             "cpu_baseline": {"value": us, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-# DRAM traffic of one launch of the fused kernel at world 1 (469.8 MB read + 304.8 MB written), from the committed ncu capture
+# DRAM traffic of one launch of the fused kernel at world 1 (469.8 MB read + 304.8 MB written): a STATIC figure from the
+# committed ncu capture of this kernel at this shape, not something a bench run measures
 NCU_TRAFFIC_W1 = 774600000
 
 
@@ -219,9 +246,6 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     fc2 = torch.randn((rows, H), generator=g, device=dev, dtype=torch.bfloat16)
     add("config2 finalize_residual 16384x8x7168", lambda: k3g.call("k3g_finalize_residual", fc2, e2p, wts, res, o16, T, H, 8, s), T * 8 * H * 2 + 4 * E)
     del fc2
-    big = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
-    add("context: write-only fill of 1 GiB (torch zero_)", lambda: big.zero_(), big.numel())
-    del big
     # config 3
     kv = rnd(T, 576); qq = rnd(T, 16, 192); gkv = gm[:512].contiguous(); tab = rnd(T, 64)
     qo = torch.empty_like(qq); ko = torch.empty_like(qq); lat = torch.empty((T, 512), dtype=torch.bfloat16, device=dev)
@@ -255,6 +279,51 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     return out
 
 
+def probe_stores(dev, peak_gbs, nbytes=1 << 30, iters=10):
+    """One-direction HBM ceilings of this part: store-only and load-only streams over 1 GiB (larger than L2), swept over
+    access width, store cache operator, grid and block size.  The kernels live in the test-only probe library
+    (tests/native); nothing of the shipped library is involved.  Prints one JSON row per variant."""
+    import ctypes
+    import torch
+    so = os.path.join(ROOT, "tests", "native", "libk3g_probe.so")
+    if not os.path.exists(so):
+        sys.path.insert(0, os.path.dirname(so))
+        import build_probe
+        build_probe.build()
+    lib = ctypes.CDLL(so)
+    st_fn, ld_fn = lib.k3g_test_store_probe, lib.k3g_test_load_probe
+    st_fn.restype = ld_fn.restype = ctypes.c_int
+    st_fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong] + [ctypes.c_int] * 4 + [ctypes.c_void_p]
+    ld_fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong] + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_void_p]
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=dev); out = torch.zeros(1, dtype=torch.int32, device=dev)
+    other = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    rows = []
+
+    def add(name, fn, moved):
+        us = time_us(fn, iters)
+        rows.append({"probe": name, "us": round(us, 1), "gbs": round(moved / us / 1e3, 1), "of_measured_copy": round(moved / us / 1e3 / peak_gbs, 3)})
+        print(json.dumps(rows[-1]), flush=True)
+    hints = {0: "st.global", 1: "st.global.cs", 2: "st.global.wt"}
+    for width in (16, 32):
+        for hint in (0, 1, 2):
+            for per_sm, block in ((2, 1024), (8, 256), (16, 256), (32, 256), (64, 128)):
+                grid = 148 * per_sm
+                def run(width=width, hint=hint, grid=grid, block=block):
+                    rc = st_fn(buf.data_ptr(), nbytes, width, hint, grid, block, stream)
+                    assert rc == 0, rc
+                add("store-only %s %d B/thread grid 148x%d block %d" % (hints[hint], width, per_sm, block), run, nbytes)
+    for width in (16, 32):
+        for per_sm, block in ((2, 1024), (8, 256), (32, 256)):
+            def run(width=width, grid=148 * per_sm, block=block):
+                rc = ld_fn(buf.data_ptr(), nbytes, width, grid, block, out.data_ptr(), stream)
+                assert rc == 0, rc
+            add("load-only ld.global.nc %d B/thread x4 in flight grid 148x%d block %d" % (width, per_sm, block), run, nbytes)
+    add("torch zero_ of 1 GiB (cudaMemsetAsync)", lambda: buf.zero_(), nbytes)
+    add("torch copy_ 1 GiB -> 1 GiB (read + write bytes)", lambda: other.copy_(buf), 2 * nbytes)
+    return rows
+
+
 def bench_layer(rank, world, timed, iters=20, peak_gbs=6529.7):
     """Per-layer glue: every non-GEMM call of one KDA layer and one MLA layer of the reference's prefill
     program (k3g/layer.py), replayed as a CUDA graph, with a per-call breakdown from events."""
@@ -278,25 +347,197 @@ def bench_layer(rank, world, timed, iters=20, peak_gbs=6529.7):
                 acc[label] += a.elapsed_time(b) * 1e3 / 5
         lg.check_status()
         calls = []
+        ideal_nominal = ideal_measured = 0.0
         for l in order:
             nbytes, bound = lg.traffic_of(l)
             row = {"call": l, "us": round(acc[l], 1), "bound": bound}
             if nbytes and bound != "latency":
                 peak = peak_gbs if bound == "hbm" else 770.0
                 row.update({"bytes": nbytes, "gbs": round(nbytes / acc[l] / 1e3, 1), "frac": round(nbytes / acc[l] / 1e3 / peak, 3)})
+                ideal_measured += nbytes / peak / 1e3
+                ideal_nominal += nbytes / (8000.0 if bound == "hbm" else 900.0) / 1e3
             calls.append(row)
-        out[kind] = {"graph_us": round(graph_us, 1), "launches": len(order) + 3, "calls": calls}
+        out[kind] = {"graph_us": round(graph_us, 1), "launches": lg.launches(), "roofline_us_nominal": round(ideal_nominal, 1),
+                     "roofline_us_measured": round(ideal_measured, 1), "calls": calls}
         lg.close()
         del lg
         torch.cuda.empty_cache()
-    out["weighted_69kda_24mla_us"] = round((69 * out["kda"]["graph_us"] + 24 * out["mla"]["graph_us"]) / 93, 1)
-    out["weighted_69kda_24mla_fused_us"] = round((69 * out["kda_fused"]["graph_us"] + 24 * out["mla_fused"]["graph_us"]) / 93, 1)
+    w = lambda key, a, b: (69 * out[a][key] + 24 * out[b][key]) / 93
+    out["weighted_69kda_24mla_us"] = round(w("graph_us", "kda", "mla"), 1)
+    out["weighted_69kda_24mla_fused_us"] = round(w("graph_us", "kda_fused", "mla_fused"), 1)
+    out["fused_frac_of_roofline"] = {"of_nominal_8tbs_900gbs": round(w("roofline_us_nominal", "kda_fused", "mla_fused") / w("graph_us", "kda_fused", "mla_fused"), 3),
+                                     "of_measured_hbm_copy_and_770gbs_peer_copy": round(w("roofline_us_measured", "kda_fused", "mla_fused") / w("graph_us", "kda_fused", "mla_fused"), 3)}
     out["note"] = ("all non-GEMM calls of one layer of the reference's prefill program at T=16384, world=%d (rows T/%d per rank, %d heads per rank, "
-                   "56 local experts); GEMM/attention outputs are seeded random buffers; per-call times are eager launches with events, graph_us "
-                   "is the whole list as one CUDA graph; per call: bytes = algorithmic bytes per rank, frac = bytes / us against the measured HBM copy "
-                   "bandwidth (bound hbm) or the 770 GB/s peer copy (bound nvlink: bytes received or sent per direction); *_fused = the same program with the three per-tensor FP8 quantisations fed by "
-                   "maxima their producers leave (apply launch only) and the two reduce-scatters pulled inside the kernels that consume them (residual kernel, latent norm); "
-                   "outputs bit-identical to the reference call list" % (world, world, 96 // world))
+                   "EP = world: %d local experts, so each rank routes and combines T*16/%d expert rows); GEMM/attention outputs are seeded random buffers; "
+                   "per-call times are eager launches with events, graph_us is the whole list as one CUDA graph; per call: bytes = algorithmic bytes per rank, "
+                   "frac = bytes / us against the measured HBM copy bandwidth (bound hbm) or the 770 GB/s peer copy (bound nvlink: bytes received or sent per "
+                   "direction); roofline_us = sum over the calls of bytes / peak (latency-bound table kernels count as zero), fused_frac_of_roofline = that sum / "
+                   "graph_us, 69:24 weighted; *_fused = the same program with the three per-tensor FP8 quantisations fed by maxima their producers leave (apply "
+                   "launch only), the two reduce-scatters pulled inside the kernels that consume them (residual kernel, latent norm), the epoch bump inside the "
+                   "first barrier and the routing tables inside the scatter launch; outputs bit-identical to the reference call list" % (
+                       world, world, 96 // world, 224 // world, world))
+    return out
+
+
+def seeded_inputs(dev, r, world):
+    """Rank r's partial [T, d] and residual shard [T / world, d] (bf16), from the generator seeded for that rank: the
+    same call on any rank's GPU returns the same bits, so every rank can rebuild any other rank's inputs."""
+    import torch
+    g = torch.Generator(device=dev); g.manual_seed(SEED ^ r)
+    partial = (torch.randn((TOKENS, HIDDEN), generator=g, device=dev) * (0.5 / world)).to(torch.bfloat16)
+    residual = torch.randn((TOKENS // world, HIDDEN), generator=g, device=dev).to(torch.bfloat16)
+    return partial, residual
+
+
+def verify_step(glue, rank, world, dev, per_shard=48):
+    """After the timed region: clear the gathered outputs, run one more step, and compare a seeded sample of rows --
+    `per_shard` rows of EVERY rank's shard as gathered on this rank (codes and scales) plus this rank's residual rows --
+    with the CPU oracle (ring-order reduce-scatter chain over the ranks' partial rows, then residual + RMSNorm + MXFP8).
+    Returns (rows compared, rows that differ) for this rank."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import k3o
+    rows = TOKENS // world
+    pick = np.sort(np.random.Generator(np.random.Philox(SEED + 17)).choice(rows, size=min(per_shard, rows), replace=False))
+    n = len(pick)
+    sel = torch.from_numpy(np.concatenate([r * rows + pick for r in range(world)])).to(dev)       # global rows, shard-major
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    minis, residuals = [], []
+    for r in range(world):                                   # rebuild every rank's inputs, keep only the sampled rows
+        p, res = seeded_inputs(dev, r, world)
+        minis.append(bits(p[sel]).reshape(-1))
+        residuals.append(bits(res[torch.from_numpy(pick).to(dev)]))
+        del p, res
+    gamma = bits(glue.gamma)
+    glue.q_all.zero_(); glue.sf_all.zero_(); glue.residual_out.zero_()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    glue.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    glue.check_status()
+    got_q, got_sf = glue.q_all[sel].cpu().numpy(), glue.sf_all[sel].cpu().numpy()
+    got_res = bits(glue.residual_out[torch.from_numpy(pick).to(dev)])
+    bad = 0
+    for r in range(world):
+        delta = k3o.rs_pull(minis, r, 2 * (world - 1)).reshape(n, HIDDEN)
+        o, q, sf, _ = k3o.resnorm_mxfp8(residuals[r], delta, gamma, EPS, want_normed=False)
+        row_bad = (got_q[r * n:(r + 1) * n] != q).any(axis=1) | (got_sf[r * n:(r + 1) * n] != sf).any(axis=1)
+        if r == rank:
+            row_bad |= (got_res != o).any(axis=1)
+        bad += int(row_bad.sum())
+    return world * n, bad
+
+
+def bench_dispatch(k3g, rank, world, dev, timed, barrier):
+    """Benchmark configuration 2 at EP = world: the MXFP8 rows (d = 7168) of this rank's T / world tokens reach the
+    expert-sorted buffers of the ranks that own their 8 experts (224 / world experts per rank, strided placement),
+    (a) the reference's way -- all-gather every token row to every rank, then gather locally through the rank's own
+    route_map -- and (b) by peer stores from the dispatching rank straight into the owners' buffers.  Both leave the
+    same live rows (compared on the device); NVLink bytes per direction are counted from the routing itself."""
+    import torch
+    import torch.distributed as dist
+    from k3g.peer import PeerGroup, collective_units
+    T, H, K, TILE = TOKENS, HIDDEN, 8, 128
+    B, per = T // world, 224 // world
+    s = k3g.current_stream()
+    g = torch.Generator(device=dev); g.manual_seed(SEED + 100 + rank)
+    S = torch.randn((B, 224), generator=g, device=dev); gb = torch.Generator(device=dev); gb.manual_seed(SEED + 99)
+    bias = 0.1 * torch.randn(224, generator=gb, device=dev); rs = torch.ones(1, dtype=torch.bfloat16, device=dev)
+    idx = torch.empty((B, K), dtype=torch.int32, device=dev); wts = torch.empty((B, K), dtype=torch.float32, device=dev)
+    k3g.call("k3g_router_topk", S, bias, rs, idx, wts, B, 224, K, s)
+    q_own = torch.randint(0, 256, (B, H), generator=g, device=dev, dtype=torch.uint8)
+    sf_own = torch.randint(0, 256, (B, H // 32), generator=g, device=dev, dtype=torch.uint8)
+    idx_all = torch.empty((T, K), dtype=torch.int32, device=dev)
+    if world > 1:
+        dist.all_gather_into_tensor(idx_all, idx)
+    else:
+        idx_all.copy_(idx)
+    blocks = T // 256
+    i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32, device=dev)
+
+    def tables(rk, E):
+        nct = T * K // TILE + E
+        t = dict(bc=i32(blocks, E), bo=i32(blocks, E), cb=i32(nct), cl=i32(nct), nne=i32(1), tot=i32(1), rm=i32(nct * TILE), e2p=i32(T, K))
+        k3g.call("k3g_moe_route_count", idx_all, T, rk, E, K, world, 1, t["bc"], s)
+        k3g.call("k3g_moe_route_tables_scatter", idx_all, t["bc"], T, rk, E, K, world, 1, TILE, t["bo"], t["cb"], t["cl"], t["nne"], t["tot"], t["rm"], t["e2p"], s)
+        return t
+    mine, everyone = tables(rank, per), tables(-1, 224)
+    torch.cuda.synchronize()
+    rows = int(mine["tot"].item())
+    mx = torch.tensor([rows], device=dev)
+    if world > 1:
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    cap = int(mx.item())
+    pg = PeerGroup(rank, world)
+    units = collective_units(T, world, H)
+    b_qall, b_sfall = pg.symmetric("d_q_all", T * H), pg.symmetric("d_sf_all", T * H // 32)
+    b_oq, b_osf = pg.symmetric("d_out_q", cap * H), pg.symmetric("d_out_sf", cap * H // 32)
+    b_fl = pg.symmetric("d_flags", 64)
+    q_all, sf_all = b_qall.tensor(torch.uint8, (T, H)), b_sfall.tensor(torch.uint8, (T, H // 32))
+    out_q, out_sf = b_oq.tensor(torch.uint8, (cap, H)), b_osf.tensor(torch.uint8, (cap, H // 32))
+    flags = b_fl.tensor(torch.int64, (8,))
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    k3g.call("k3g_flags_init", flags, 8, s)
+    sel_q = torch.empty((rows, H), dtype=torch.uint8, device=dev); sel_sf = torch.empty((rows, H // 32), dtype=torch.uint8, device=dev)
+    barrier()
+
+    def gather_then_select():
+        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_allgather4_push", q_own, q_all, b_qall.table, q_own.numel(), sf_own, sf_all, b_sfall.table, sf_own.numel(), None, None, None, 0,
+                 None, None, None, 0, flags, b_fl.table, 1, rank, world, units, 2_000_000, status, s)
+        k3g.call("k3g_permute_gather", q_all, sf_all, mine["rm"], rows, H, sel_q, sel_sf, s)
+
+    def dispatch():
+        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_permute_dispatch", q_own, sf_own, idx_all, everyone["e2p"], everyone["bo"], B, rank * B, K, H, 224, world, 1, b_oq.table,
+                 b_osf.table, s)
+        k3g.call("k3g_rs_arrive", flags, b_fl.table, units, 2, world, 2_000_000, status, s)
+
+    def ag_only():
+        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_allgather4_push", q_own, q_all, b_qall.table, q_own.numel(), sf_own, sf_all, b_sfall.table, sf_own.numel(), None, None, None, 0,
+                 None, None, None, 0, flags, b_fl.table, 3, rank, world, units, 2_000_000, status, s)
+    a_us = timed(gather_then_select, 20, 3)
+    ag_us = timed(ag_only, 20, 3)
+    out_q.fill_(0xEE); out_sf.fill_(0xEE)
+    barrier()
+    b_us = timed(dispatch, 20, 3)
+    if int(status.cpu()[0]) != 0:
+        raise RuntimeError("a dispatch wait expired: %s" % status.cpu().tolist())
+    # same live rows both ways (padding rows are not written by the dispatch)
+    live = torch.zeros(rows, dtype=torch.bool, device=dev)
+    e2p = mine["e2p"].view(-1)
+    live[e2p[e2p >= 0].long()] = True
+    same = bool(torch.equal(out_q[:rows][live], sel_q[live]) and torch.equal(out_sf[:rows][live], sel_sf[live]))
+    untouched = bool((out_q[:rows][~live] == 0xEE).all())
+    ok = torch.tensor([int(same and untouched)], device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    own = (idx % world) == rank                              # strided placement: owner = id % world
+    remote_rows = int((~own).sum().item())                   # rows this rank stores into other ranks' buffers
+    local_rows = int(live.sum().item())
+    received = local_rows - int(own.sum().item())            # rows other ranks store into this rank's buffer
+    rb = H + H // 32
+    out = {"ep": world, "experts_per_rank": per, "tokens_per_rank": B, "rows_per_owner_padded": rows,
+           "gather_then_select_us": round(a_us, 1), "of_which_allgather_us": round(ag_us, 1), "peer_store_dispatch_us": round(b_us, 1),
+           "same_live_rows_both_ways": bool(ok.item()),
+           "nvlink_bytes_per_direction": {"gather_then_select": (world - 1) * B * rb, "peer_store_dispatch_out": remote_rows * rb,
+                                          "peer_store_dispatch_in": received * rb},
+           "peer_store_dispatch_gbs_out": round(remote_rows * rb / b_us / 1e3, 1) if world > 1 else None,
+           "allgather_gbs_out": round((world - 1) * B * rb / ag_us / 1e3, 1) if world > 1 else None,
+           "hbm_bytes_local": {"gather_then_select": (T + rows) * rb + B * rb, "peer_store_dispatch": B * rb + local_rows * rb},
+           "note": "per rank; the dispatch stores each token row once per routed expert (8 per token, (EP-1)/EP of them remote), the all-gather "
+                   "sends each token row once to each of the EP-1 peers, so the dispatch puts 8/EP times the all-gather's bytes on the links: "
+                   "fewer HBM passes, more NVLink bytes below EP = 8"}
+    torch.cuda.synchronize()
+    pg.release()
+    if not ok.item():
+        raise RuntimeError("dispatch paths disagree")
     return out
 
 
@@ -314,9 +555,9 @@ def run_gpu(args, rank, world, local_rank):
             torch.cuda.synchronize()
     peak_gbs, peak_kind = measured_peaks()
     glue = TpGlue(rank, world, TOKENS, HIDDEN, EPS)
-    g = torch.Generator(device=dev); g.manual_seed(0x5EED ^ rank)
-    glue.partial.copy_((torch.randn((TOKENS, HIDDEN), generator=g, device=dev) * (0.5 / world)).to(torch.bfloat16))
-    glue.residual.copy_(torch.randn((glue.rows, HIDDEN), generator=g, device=dev).to(torch.bfloat16))
+    p0, r0 = seeded_inputs(dev, rank, world)
+    glue.partial.copy_(p0); glue.residual.copy_(r0)
+    del p0, r0
     g2 = torch.Generator(device=dev); g2.manual_seed(99)
     glue.gamma.copy_((1 + 0.02 * torch.randn(HIDDEN, generator=g2, device=dev)).to(torch.bfloat16))
 
@@ -404,11 +645,17 @@ def run_gpu(args, rank, world, local_rank):
                 "nccl_all_gather_us": round(nccl_ag_us, 1), "rs_in_bytes": rs_in, "ag_out_bytes": ag_out,
                 "note": "per rank; NVLink nominal 900 GB/s per direction, measured peer copy 770 GB/s; NCCL is the comparison line only"}
 
+    verified_rows, mismatches = verify_step(glue, rank, world, dev)
+    vm = torch.tensor([verified_rows, mismatches], device=dev)
+    if world > 1:
+        dist.all_reduce(vm)                                   # summed over the ranks
+    verified_rows, mismatches = int(vm[0].item()), int(vm[1].item())
+
     W, E = world, TOKENS * HIDDEN
     alg_hbm = (7 * E + E // 32) // W if W == 1 else (2 * E // W) * 3 + (W - 1) * 2 * E // W + E + E // 32   # per rank, incl. serving peers' pulls
     roof = {"bound": "hbm", "kernel": "rs_resnorm_mxfp8_ag_kernel", "achieved": round(alg_hbm / kern_us / 1e3, 1), "peak": peak_gbs, "unit": "GB/s",
             "frac": round(alg_hbm / kern_us / 1e3 / peak_gbs, 4), "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_W1 if W == 1 else None,
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, profiles/rs_resnorm_mxfp8_ag_kernel_config1_world1.md" if W == 1 else None,
+            "traffic_source": "static: dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture of this kernel at this shape; not measured by this run" if W == 1 else None,
             "note": None if W == 1 else "at world > 1 the kernel is NVLink-bound, not HBM-bound: the nvlink object carries its achieved / peak figures",
             "kernel_us": round(kern_us, 2),
             "algorithmic_bytes_per_launch": alg_hbm}
@@ -424,18 +671,21 @@ def run_gpu(args, rank, world, local_rank):
               "target_us_at_770": round(tot / 770e3, 1)}
     line = {"metric": METRIC, "value": round(step_us, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": round(step_us / 1e3, 5), "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "config1: TP reduce-scatter -> residual add + RMSNorm + MXFP8 -> all-gather, T=16384 d=7168, world=%d" % W,
-                       "tokens": TOKENS, "d": HIDDEN, "world": W, "l2": "inputs (470 MB read per step at world 1) exceed the 126 MB L2; no flush"},
+            "config": workload_config(W), "verified_rows": verified_rows, "mismatches": mismatches,
             "clocks": clocks, "roofline": roof, "nvlink": nv, "collectives": coll, "launch_mode": "cuda graph replay of 4 kernels per step (epoch bump, arrive, fused kernel, arrive)",
             "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps, "mode": e2e_mode, "serial_us": round(e2e_serial_us, 1)},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps, "eager_step_us": round(eager_us, 2), "tokens_per_s": round(TOKENS / step_us * 1e6)}
     if not args.no_ops:
         glue.close(); glue = None
         torch.cuda.empty_cache()
+        line["dispatch"] = bench_dispatch(k3g, rank, world, dev, timed, barrier)
+        torch.cuda.empty_cache()
         line["layer_glue"] = bench_layer(rank, world, timed, peak_gbs=peak_gbs)
+        line["layer_glue_us"] = line["layer_glue"]["weighted_69kda_24mla_fused_us"]
+        line["layer_roofline_frac"] = line["layer_glue"]["fused_frac_of_roofline"]
     if rank == 0 and world == 1:
-        us, cores = cpu_oracle_us(20, 2, 1)
-        line["cpu_baseline"] = {"value": round(us, 1), "unit": UNIT, "cores": cores, "kind": "port", "sample": CPU_SAMPLE % (TOKENS, 1, 20)}
+        us, cores, sample = cpu_oracle_us(20, 2, 1)
+        line["cpu_baseline"] = {"value": round(us, 1), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
         if not args.no_ops:
             line["ops"] = bench_ops(k3g, dev, peak_gbs)
     if glue is not None:
@@ -444,6 +694,8 @@ def run_gpu(args, rank, world, local_rank):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if mismatches:
+        sys.exit("verification failed: %d of %d sampled rows differ from the CPU oracle" % (mismatches, verified_rows))
 
 
 def main():
@@ -456,11 +708,17 @@ def main():
     ap.add_argument("--ops-only", default=None, metavar="SUBSTR", help="run only the per-op microbenchmarks whose name contains SUBSTR "
                     "('' = all) and print their table; for profiling a single kernel")
     ap.add_argument("--op-iters", type=int, default=20)
+    ap.add_argument("--probe-stores", action="store_true", help="measure the store-only / load-only HBM ceilings of this GPU (test-only probe kernels) and exit")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.probe_stores:
+        import torch
+        torch.cuda.set_device(local_rank)
+        probe_stores(torch.device("cuda"), measured_peaks()[0])
         return
     if args.ops_only is not None:
         import torch

@@ -19,6 +19,7 @@
 #include "k3g_host.h"
 
 #include <atomic>
+#include <cstdlib>
 
 using namespace k3g;
 
@@ -380,6 +381,112 @@ __global__ void __launch_bounds__(256) permute_gather_kernel(const uint8_t* __re
   }
 }
 
+// ---- the same gather as a bulk row mover -------------------------------------------------------------------------
+// One elected thread per block moves whole rows with the copy engine of the SM (untiled cp.async.bulk: global ->
+// shared with an mbarrier counting the bytes, then shared -> global as a bulk group), kStages rows in flight per
+// block, so no register or LSU instruction touches the payload.  Local memory only; plain (single-CTA) bulk copies.
+// Needs 16-byte aligned rows: cols % 512 == 0 (then cols / 32 scale bytes are a multiple of 16 as well).
+// Every wait is bounded: a barrier that does not complete within kBulkSpin polls sets *err and the block drains
+// its outstanding stores and returns.
+constexpr int kBulkStages = 8;
+constexpr int kBulkSpin = 1 << 22;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__global__ void __launch_bounds__(32) permute_gather_bulk_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                                                 const int* __restrict__ route_map, long long rows, int cols,
+                                                                 uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf, int* err) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  __shared__ __align__(8) unsigned long long bar[kBulkStages];
+  if (threadIdx.x != 0) return;
+  const int sfb = cols >> 5, rb = cols + sfb;                  // bytes per row: codes then scales, both multiples of 16
+  for (int s = 0; s < kBulkStages; ++s)
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bar[s])));
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  const long long first = blockIdx.x, step = gridDim.x;
+  const long long mine = first < rows ? (rows - first + step - 1) / step : 0;     // rows first, first + step, ...
+  auto load = [&](long long i) {                               // i-th row of this block into stage i % kBulkStages
+    const int s = (int)(i % kBulkStages);
+    const long long t = route_map[first + i * step];
+    const unsigned dst = smem_u32(bulk_smem + (size_t)s * rb), b = smem_u32(&bar[s]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(b), "r"(rb) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(q + t * cols), "r"(cols), "r"(b) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst + cols), "l"(sf + t * sfb), "r"(sfb), "r"(b) : "memory");
+  };
+  const long long prime = mine < kBulkStages ? mine : kBulkStages;
+  for (long long i = 0; i < prime; ++i) load(i);
+  bool failed = false;
+  for (long long i = 0; i < mine && !failed; ++i) {
+    const int s = (int)(i % kBulkStages);
+    const unsigned parity = (unsigned)((i / kBulkStages) & 1);
+    unsigned done = 0;
+    for (int spin = 0; spin < kBulkSpin && !done; ++spin)
+      asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                   : "=r"(done) : "r"(smem_u32(&bar[s])), "r"(parity) : "memory");
+    if (!done) { failed = true; break; }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const long long r = first + i * step;
+    const unsigned src = smem_u32(bulk_smem + (size_t)s * rb);
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(out_q + r * cols), "r"(src), "r"(cols) : "memory");
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(out_sf + r * sfb), "r"(src + cols), "r"(sfb) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (i >= 1 && i - 1 + kBulkStages < mine) {
+      // refill the stage of the PREVIOUS row: its stores must have read the stage, which "at most the newest group
+      // still reading" guarantees -- so this thread never waits on the store it has just issued
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      load(i - 1 + kBulkStages);
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");    // own stores have landed before the block exits
+  if (failed) {
+    // give the loads still in flight towards this block's shared memory a bounded chance to land before it goes away
+    for (int s = 0; s < kBulkStages; ++s) {
+      unsigned done = 0;
+      for (int spin = 0; spin < (kBulkSpin >> 4) && !done; ++spin)
+        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(smem_u32(&bar[s])), "r"(0u) : "memory");
+    }
+    if (err) atomicExch(err, 1);
+  }
+}
+
+// warp-per-row gather with 32-byte accesses per lane (sm_100 256-bit ld / st): half the instructions of the 16-byte form
+__global__ void __launch_bounds__(256) permute_gather_v8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                                                const int* __restrict__ route_map, long long rows, int cols,
+                                                                uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int qv = cols >> 5, sfb = cols >> 5;                 // 32-byte vectors of codes per row; scale bytes per row
+  long long r = warp;
+  long long t = r < rows ? route_map[r] : 0;
+  while (r < rows) {
+    const long long rn = r + nwarps;
+    const long long tn = rn < rows ? route_map[rn] : 0;
+    const uint8_t* src = q + t * cols;
+    uint8_t* dst = out_q + r * cols;
+    for (int v0 = lane; v0 < qv; v0 += 4 * 32) {
+      unsigned x[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + 32 * u < qv)
+          asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                       : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3]), "=r"(x[u][4]), "=r"(x[u][5]), "=r"(x[u][6]), "=r"(x[u][7])
+                       : "l"(src + (size_t)(v0 + 32 * u) * 32));
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + 32 * u < qv)
+          asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                       :: "l"(dst + (size_t)(v0 + 32 * u) * 32), "r"(x[u][0]), "r"(x[u][1]), "r"(x[u][2]), "r"(x[u][3]), "r"(x[u][4]), "r"(x[u][5]),
+                          "r"(x[u][6]), "r"(x[u][7]) : "memory");
+    }
+    if (lane < (sfb >> 4)) __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + lane, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + lane));
+    r = rn; t = tn;
+  }
+}
+
 template <int MAXE>
 __global__ void __launch_bounds__(256) route_count_kernel(const int* ids, int T, int rank, int E, int topk, int ep_ranks,
                                                           int strided, int* blockcount) {
@@ -726,6 +833,24 @@ K3G_API int k3g_permute_gather(const void* q, const void* sf, const void* route_
   K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
   if ((cols >> 5) % 16 == 0) { K3G_REQUIRE_ALIGNED(sf); K3G_REQUIRE_ALIGNED(out_sf); }
   if (rows == 0) return K3G_OK;
+  static const int variant = getenv("K3G_PERMUTE_VARIANT") ? atoi(getenv("K3G_PERMUTE_VARIANT")) : 0;
+  if (variant == 1 && cols % 512 == 0 && ((uintptr_t)q & 31) == 0 && ((uintptr_t)out_q & 31) == 0) {
+    long long g1 = (rows + 7) / 8;
+    if (g1 > 148 * 64) g1 = 148 * 64;
+    permute_gather_v8_kernel<<<(unsigned)g1, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
+                                                                          cols, (uint8_t*)out_q, (uint8_t*)out_sf);
+    return k3g_launch_status();
+  }
+  if (variant >= 2 && cols % 512 == 0) {
+    const int smem = kBulkStages * (cols + cols / 32);
+    static std::atomic<bool> opted[64];
+    if (int rc = opt_in_wide_smem(permute_gather_bulk_kernel, opted, smem)) return rc;
+    const int per_sm = variant == 2 ? 3 : variant - 2;
+    long long g2 = rows < 148LL * per_sm ? rows : 148LL * per_sm;
+    permute_gather_bulk_kernel<<<(unsigned)g2, 32, smem, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
+                                                                              cols, (uint8_t*)out_q, (uint8_t*)out_sf, nullptr);
+    return k3g_launch_status();
+  }
   long long grid = (rows + 7) / 8;                 // eight warps per block, one row per warp pass
   if (grid > 148 * 64) grid = 148 * 64;            // then rows are walked with a warp stride
   permute_gather_kernel<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,

@@ -6,17 +6,18 @@ span block replaced by mla_prep).  Buffers that a GEMM or attention kernel would
 random data.  This is the program the metric "per-layer glue us at 16k tokens" is measured on: the
 whole list replayed as one CUDA graph per rank, plus a per-call breakdown from events.
 
-Shapes follow the reference deployment: H = 7168, MoE latent 3584, 224 experts placed round-robin on an
-expert-parallel group of 4 (56 local, 16 slots per token), 96 attention heads split over the W ranks,
-rows sharded T / W.  For W in {1, 2} the expert placement still uses a group of 4 (rank % 4), so the
-routing tables keep the reference's 56-local-expert shape.
+Shapes follow the reference deployment: H = 7168, MoE latent 3584, 224 experts placed round-robin
+(strided, xiaguan/kern-k3 source/k3_moe_prefill_v4.cu:100-109) on an expert-parallel group as wide as the
+tensor-parallel one -- EP = W, so 224 / 112 / 56 / 28 local experts at W = 1 / 2 / 4 / 8 and each rank routes,
+combines and reduce-scatters T * 16 / W expert rows -- 16 slots per token, 96 attention heads split over the
+W ranks, rows sharded T / W.  W = 4 is the reference's own deployment (56 local experts).
 """
 import torch
 
 from . import call, current_stream
 from .peer import PeerGroup, collective_units, shard_rows
 
-H, LATENT, EXPERTS, TOPK, EP, TILE = 7168, 3584, 224, 16, 4, 128
+H, LATENT, EXPERTS, TOPK, TILE = 7168, 3584, 224, 16, 128
 SHARED = 6144
 
 
@@ -95,7 +96,8 @@ class LayerGlue:
         self.idx = torch.empty((B, TOPK), dtype=torch.int32, device=dev); self.wts = torch.empty((B, TOPK), dtype=torch.float32, device=dev)
         self.latent = rnd(B, LATENT)
         self.latent_q = torch.empty((B, LATENT), dtype=torch.uint8, device=dev); self.latent_sf = torch.empty((B, LATENT // 32), dtype=torch.uint8, device=dev)
-        self.E = EXPERTS // EP
+        self.ep = world                      # expert-parallel group = tensor-parallel group
+        self.E = EXPERTS // self.ep
         nblk = (T + 255) // 256
         nct = T * TOPK // TILE + self.E
         i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)
@@ -114,7 +116,7 @@ class LayerGlue:
         s = current_stream
         W, r, T, B, inner, heads, nb = self.world, self.rank, self.T, self.B, self.inner, self.heads, self.nb
         ft, fl, un, to, st = self.b_flags.table, self.flags, self.units, self.timeout_us, self.status
-        ep_rank = r % EP
+        ep_rank, EP = r, self.ep
         c = [("coll_epoch", lambda: call("k3g_epoch_bump", fl, un, s())),
              ("res_in (land_add2 + attnres + rms + push)", lambda: call(
                  "k3g_attnres_rms_push", self.blocks, self.sw, self.gamma, self.normed_all, self.b_normed_all.table, nb, 0, B, r, W, self.sw_mlp,
@@ -169,7 +171,15 @@ class LayerGlue:
             #  - the attention reduce-scatter is pulled inside the residual kernel that consumes it and the routed-latent
             #    reduce-scatter inside the latent norm, so their HBM / special-function work hides under the NVLink
             #    transfer and the reduce-scattered tensors are never written.
+            #  - the epoch bump rides in the first barrier launch and the routing tables are built inside the scatter
+            #    launch (two launches fewer, same tables).
             swap = {
+                "coll_epoch": None,
+                "normed_sync (arrive)": ("normed_sync (epoch + arrive)", lambda: call("k3g_epoch_arrive", fl, ft, un, 1, W, to, st, s())),
+                "route_tables": None,
+                "route_scatter": ("route_tables + route_scatter (one launch)", lambda: call(
+                    "k3g_moe_route_tables_scatter", self.idx_all, self.blockcount, T, ep_rank, self.E, TOPK, EP, 1, TILE, self.blockoff,
+                    self.cta_batch, self.cta_limit, self.nne, self.total, self.route_map, self.exp2perm, s())),
                 "res_in (land_add2 + attnres + rms + push)": ("res_in (land_add2 + attnres + rms + push, row maxima)", lambda: call(
                     "k3g_attnres_rms_push_amax", self.blocks, self.sw, self.gamma, self.normed_all, self.b_normed_all.table, nb, 0, B, r, W,
                     self.sw_mlp, self.stats, self.p1, self.p2, self.prefix2, self.hidden, 1, H, 1e-5, self.rowmax_all, self.b_rowmax.table, s())),
@@ -225,14 +235,19 @@ class LayerGlue:
             "moe_quant (": (B * LATENT * 3 + B * LATENT // 32, "hbm"),
             "gather_small": link(B * (LATENT + LATENT // 32 + 2 * TOPK * 4)) if W > 1 else (2 * B * (LATENT + LATENT // 32 + 2 * TOPK * 4), "hbm"),
             "moe_quant + gather_small": link(B * (LATENT + LATENT // 32 + 2 * TOPK * 4)) if W > 1 else (B * LATENT * 3, "hbm"),
-            "route_count": (0, "latency"), "route_tables": (0, "latency"), "route_scatter": (0, "latency"),
-            "finalize": ((T * TOPK // EP + T) * LATENT * 2, "hbm"),
+            "route_count": (0, "latency"), "route_tables": (0, "latency"), "route_scatter": (0, "latency"), "normed_sync (epoch": (0, "latency"),
+            "finalize": ((T * TOPK // self.ep + T) * LATENT * 2, "hbm"),
             "scatter_moe (pull RS)": link(B * LATENT * 2) if W > 1 else (2 * B * LATENT * 2, "hbm"),
             "shared_situ": (B * (SHARED * 6 + LATENT * 4), "hbm"),
             "scatter_moe + shared_situ": link(B * LATENT * 2) if W > 1 else (B * (SHARED * 6 + LATENT * 4), "hbm"),
             "shared_act_quant": (3 * B * SHARED, "hbm"),
         }
         return t
+
+    def launches(self):
+        """Kernel launches of one pass of the call list (a two-pass quantisation and the pair of state copies are two each)."""
+        two = ("(fp8 tensor", "span_state_in + span_state_out")
+        return sum(2 if any(k in label for k in two) else 1 for label, _ in self.calls())
 
     def traffic_of(self, label):
         best = None

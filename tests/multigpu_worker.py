@@ -1,6 +1,17 @@
-"""Worker of tests/test_multigpu.py: one rank of a world-W run of the collective kernels, checked
-against the CPU oracle.  Every rank regenerates every rank's seeded inputs, so no data is exchanged
-besides the IPC handles."""
+"""Worker of tests/test_multigpu.py: one rank of a world-W run of the collective kernels over real NVLink peers.
+
+Part 1 (3 replays, everything against the CPU oracle): flag protocol, pull reduce-scatter, the fused
+reduce-scatter -> residual/RMSNorm/MXFP8 -> all-gather kernel, the reduce-scatter folded into the residual kernel and
+into the latent norm, the four-payload push all-gather with its ticket tail, and the dispatch to owning ranks.
+
+Part 2 (soak, K3G_SOAK_REPLAYS replays, default 500): the same protocol round with the inputs CHANGED every replay --
+the rows of every shard are rotated by a replay-dependent amount and the all-gather payloads are xor-ed with a
+replay-dependent byte -- and every output compared bit for bit on the device against the (rotated) oracle result.
+Nothing synchronises the ranks between replays except the kernels' own arrive / poll barriers, so a stale read, a
+store that lands after the barrier or a ticket published early shows up as a mismatch.  All waits are bounded: an
+expired wait sets the status word, which fails the run.
+
+Every rank regenerates every rank's seeded inputs, so no data is exchanged besides the IPC handles."""
 import os
 import sys
 
@@ -15,6 +26,49 @@ import k3g  # noqa: E402
 import k3o  # noqa: E402
 from k3g.peer import PeerGroup, collective_units  # noqa: E402
 from util import bf16_bits, normal_bf16, rng, to_dev, to_dev_bf16  # noqa: E402
+
+TIMEOUT_US = 5_000_000
+
+
+def dispatch_check(pg, rank, world, dev, s):
+    """Dispatch to owning ranks across real peers: T tokens, 8 slots, 224 / world experts per rank (strided); every
+    owner's live rows against the oracle's expert-sorted gather on that owner's own route_map."""
+    T, K, cols, tile = 64 * world, 8, 7168, 128
+    B, per = T // world, 224 // world
+    g = rng(77)
+    ids = np.stack([g.permutation(224)[:K] for _ in range(T)]).astype(np.int32)
+    q = g.integers(0, 256, (T, cols), dtype=np.uint8); sf = g.integers(0, 256, (T, cols // 32), dtype=np.uint8)
+    want = k3o.moe_route(ids, rank, per, world, 1, tile)
+    rows = int(want["total_padded"][0])
+    cap = max(int(k3o.moe_route(ids, o, per, world, 1, tile)["total_padded"][0]) for o in range(world))
+    b_q, b_sf = pg.symmetric("disp_q", cap * cols), pg.symmetric("disp_sf", cap * cols // 32)
+    b_fl = pg.symmetric("disp_flags", 64)
+    out_q, out_sf = b_q.tensor(torch.uint8, (cap, cols)), b_sf.tensor(torch.uint8, (cap, cols // 32))
+    flags = b_fl.tensor(torch.int64, (8,))
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out_q.fill_(0xEE); out_sf.fill_(0xEE)
+    k3g.call("k3g_flags_init", flags, 8, s)
+    torch.cuda.synchronize(); dist.barrier()
+    blocks, E = (T + 255) // 256, 224
+    nct = T * K // tile + E
+    i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32, device=dev)
+    bc, bo, cb, cl, nne, tot, rm, e2p = i32(blocks, E), i32(blocks, E), i32(nct), i32(nct), i32(1), i32(1), i32(nct * tile), i32(T, K)
+    d_ids = to_dev(ids, dev)
+    k3g.call("k3g_moe_route_count", d_ids, T, -1, E, K, world, 1, bc, s)
+    k3g.call("k3g_moe_route_tables_scatter", d_ids, bc, T, -1, E, K, world, 1, tile, bo, cb, cl, nne, tot, rm, e2p, s)
+    k3g.call("k3g_epoch_bump", flags, 4, s)
+    k3g.call("k3g_permute_dispatch", to_dev(q[rank * B:(rank + 1) * B], dev), to_dev(sf[rank * B:(rank + 1) * B], dev), d_ids, e2p, bo, B, rank * B, K, cols,
+             224, world, 1, b_q.table, b_sf.table, s)
+    k3g.call("k3g_rs_arrive", flags, b_fl.table, 4, 1, world, TIMEOUT_US, status, s)
+    torch.cuda.synchronize()
+    assert not status.cpu().numpy().any(), status
+    o_q, o_sf = k3o.permute_gather(q, sf, want["route_map"], rows)
+    live = np.zeros(rows, bool)
+    live[want["exp2perm"][want["exp2perm"] >= 0]] = True
+    got_q, got_sf = out_q[:rows].cpu().numpy(), out_sf[:rows].cpu().numpy()
+    assert np.array_equal(got_q[live], o_q[live]) and np.array_equal(got_sf[live], o_sf[live])
+    assert (got_q[~live] == 0xEE).all() and (got_sf[~live] == 0xEE).all()
+    dist.barrier()
 
 
 def main():
@@ -51,21 +105,34 @@ def main():
         if r == rank:
             want_res = o
     wq, wsf = np.concatenate(wq), np.concatenate(wsf)
+    d_res, d_gamma = to_dev_bf16(residual[rank], dev), to_dev_bf16(gamma, dev)
+    sizes = (rows * 3584, rows * 112, rows * 64, rows * 64)
+    payload = lambda r, i: rng(50 + r * 4 + i).integers(0, 256, sizes[i], dtype=np.uint8)
+    srcs = [to_dev(payload(rank, i), dev) for i in range(4)]
+    bufs = [pg.symmetric("ag%d" % i, world * n) for i, n in enumerate(sizes)]
+    gathered = [b.tensor(torch.uint8, (world * n,)) for b, n in zip(bufs, sizes)]
+    want_gathered = [np.concatenate([payload(r, i) for r in range(world)]) for i in range(4)]
+
+    def push4(src_list):
+        a = []
+        for t, b in zip(src_list, bufs):
+            a += [t, b.ptr, b.table, t.numel()]
+        k3g.call("k3g_allgather4_push", *a, flags, b_flags.table, 4, rank, world, units, TIMEOUT_US, status, s)
 
     for replay in range(3):
         q_all.zero_(); sf_all.zero_()
         torch.cuda.synchronize(); dist.barrier()
         k3g.call("k3g_epoch_bump", flags, units, s)
         # unfused: arrive, pull reduce-scatter
-        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 1, world, 5_000_000, status, s)
+        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 1, world, TIMEOUT_US, status, s)
         dst = torch.zeros(rows * H, dtype=torch.bfloat16, device=dev)
         k3g.call("k3g_rs_pull", part, dst, b_part.table, rows * H, 2 * (world - 1), rank, world, units, s)
         # fused: arrive (partials ready), fused kernel, arrive (pushes landed)
-        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 2, world, 5_000_000, status, s)
+        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 2, world, TIMEOUT_US, status, s)
         res_out = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
-        k3g.call("k3g_rs_resnorm_mxfp8_ag", part, b_part.table, to_dev_bf16(residual[rank], dev), to_dev_bf16(gamma, dev), res_out, q_all,
+        k3g.call("k3g_rs_resnorm_mxfp8_ag", part, b_part.table, d_res, d_gamma, res_out, q_all,
                  b_q.table, sf_all, b_sf.table, rows, H, 1e-6, rank, world, 0, 0, 0, s)
-        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 3, world, 5_000_000, status, s)
+        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 3, world, TIMEOUT_US, status, s)
         torch.cuda.synchronize()
         assert not status.cpu().numpy().any(), status
         assert np.array_equal(bf16_bits(dst), want_delta)
@@ -78,8 +145,8 @@ def main():
             blocks_h = normal_bf16(rng(4000 + rank), (rows, 8, H)); sw_h = (rng(5).standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32)
             p2, nrm = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev), torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
             rowmax = torch.zeros(rows, dtype=torch.float32, device=dev)
-            k3g.call("k3g_rs_land_add_attnres_rms", part, b_part.table, rank, world, to_dev_bf16(residual[rank], dev), to_dev_bf16(blocks_h, dev),
-                     to_dev(sw_h, dev), to_dev_bf16(gamma, dev), p2, nrm, nb, 0, rows, H, 1e-5, None, 0, rowmax, s)
+            k3g.call("k3g_rs_land_add_attnres_rms", part, b_part.table, rank, world, d_res, to_dev_bf16(blocks_h, dev),
+                     to_dev(sw_h, dev), d_gamma, p2, nrm, nb, 0, rows, H, 1e-5, None, 0, rowmax, s)
             torch.cuda.synchronize()
             o_p2, o_n = k3o.land_add_attnres_rms(want_delta.reshape(rows, H), residual[rank], blocks_h, sw_h, gamma, nb, 0, 1e-5)
             assert np.array_equal(bf16_bits(p2), o_p2) and np.array_equal(bf16_bits(nrm), o_n)
@@ -94,27 +161,69 @@ def main():
             o_act, o_ln = k3o.situ_rms(sp_h, want_delta.reshape(L2, h2), gam2, 256, h2)
             assert np.array_equal(bf16_bits(ln), o_ln)
         # push all-gather of four byte streams with its own barrier tail
-        srcs = [torch.from_numpy(rng(50 + rank * 4 + i).integers(0, 256, n, dtype=np.uint8)).to(dev) for i, n in enumerate((rows * 3584, rows * 112, rows * 64, rows * 64))]
-        if replay == 0:
-            bufs = [pg.symmetric("ag%d" % i, world * t.numel()) for i, t in enumerate(srcs)]
-        a = []
-        for t, b in zip(srcs, bufs):
-            a += [t, b.ptr, b.table, t.numel()]
-        k3g.call("k3g_allgather4_push", *a, flags, b_flags.table, 4, rank, world, units, 5_000_000, status, s)
+        push4(srcs)
         torch.cuda.synchronize()
         assert not status.cpu().numpy().any(), status
-        for i, b in enumerate(bufs):
-            n = srcs[i].numel()
-            got = b.tensor(torch.uint8, (world * n,)).cpu().numpy()
-            want = np.concatenate([rng(50 + r * 4 + i).integers(0, 256, n, dtype=np.uint8) for r in range(world)])
-            assert np.array_equal(got, want), i
+        for i in range(4):
+            assert np.array_equal(gathered[i].cpu().numpy(), want_gathered[i]), i
         dist.barrier()
     f = flags.cpu().numpy()
     assert f[0] == 3 * units and all(f[k] == 3 * units for k in (1, 2, 3, 4))
+
+    if world in (1, 2, 4, 8):
+        dispatch_check(pg, rank, world, dev, s)
+
+    # ---- part 2: soak with inputs that change every replay ------------------------------------------------------------
+    replays = int(os.environ.get("K3G_SOAK_REPLAYS", "500"))
+    base_part = [to_dev_bf16(partials[r], dev).view(world, rows, H) for r in range(world)]      # every rank's partial, by shard
+    base_res = [to_dev_bf16(residual[r], dev) for r in range(world)]
+    base_delta = to_dev_bf16(want_delta.reshape(rows, H), dev)
+    base_res_out = to_dev_bf16(want_res, dev)
+    base_q, base_sf = to_dev(wq, dev).view(world, rows, H), to_dev(wsf, dev).view(world, rows, H // 32)
+    base_gathered = [to_dev(w, dev) for w in want_gathered]
+    bad = torch.zeros(6, dtype=torch.int64, device=dev)
+    res_in = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
+    dst = torch.empty(rows * H, dtype=torch.bfloat16, device=dev); res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
+    soak_src = [torch.empty_like(t) for t in srcs]
+    torch.cuda.synchronize(); dist.barrier()
+    for replay in range(replays):
+        shift = (replay * 7 + 1) % rows
+        key = (replay * 37 + 11) & 0xff
+        # this replay's inputs: rows of every shard rotated by `shift`; payloads xor `key`.  No host barrier: the peers are
+        # held back by the arrive launches alone.
+        part.view(world, rows, H).copy_(torch.roll(base_part[rank], shift, dims=1))
+        res_in.copy_(torch.roll(base_res[rank], shift, dims=0))
+        for t, b in zip(soak_src, srcs):
+            torch.bitwise_xor(b, key, out=t)
+        q_all.fill_(0x5a); sf_all.fill_(0x5a); dst.zero_(); res_out.zero_()
+        for t in gathered:
+            t.fill_(0xa5)
+        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 1, world, TIMEOUT_US, status, s)
+        k3g.call("k3g_rs_pull", part, dst, b_part.table, rows * H, 2 * (world - 1), rank, world, units, s)
+        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 2, world, TIMEOUT_US, status, s)
+        k3g.call("k3g_rs_resnorm_mxfp8_ag", part, b_part.table, res_in, d_gamma, res_out, q_all, b_q.table, sf_all, b_sf.table, rows, H, 1e-6,
+                 rank, world, 0, 0, 0, s)
+        k3g.call("k3g_rs_arrive", flags, b_flags.table, units, 3, world, TIMEOUT_US, status, s)
+        push4(soak_src)
+        bad[0] += (dst.view(rows, H) != torch.roll(base_delta, shift, dims=0)).any()
+        bad[1] += (res_out != torch.roll(base_res_out, shift, dims=0)).any()
+        bad[2] += (q_all.view(world, rows, H) != torch.roll(base_q, shift, dims=1)).any()
+        bad[3] += (sf_all.view(world, rows, H // 32) != torch.roll(base_sf, shift, dims=1)).any()
+        for i in range(4):
+            bad[4] += (gathered[i] != torch.bitwise_xor(base_gathered[i], key)).any()
+        if replay % 100 == 99 or replay == replays - 1:
+            torch.cuda.synchronize()
+            bad[5] = int(status[0])
+            assert not bad.cpu().numpy().any(), ("soak replay %d: mismatching replays [pull, residual, codes, scales, gather4, expired waits] = %s, status %s"
+                                                 % (replay, bad.cpu().tolist(), status.cpu().tolist()))
+    torch.cuda.synchronize(); dist.barrier()
+    f = flags.cpu().numpy()
+    assert f[0] == (3 + replays) * units and all(f[k] == (3 + replays) * units for k in (1, 2, 3, 4))
     pg.release()
     dist.barrier()
     if rank == 0:
-        print("MULTIGPU_OK world=%d" % world)
+        print("MULTIGPU_OK world=%d soak_replays=%d" % (world, replays))
     dist.destroy_process_group()
 
 

@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 CSRC = os.path.join(ROOT, "kern-k3_b200", "csrc")
 SO = os.path.join(HERE, "libk3g_probe.so")
-SOURCES = [os.path.join(HERE, "situ_probe.cu")]
+SOURCES = [os.path.join(HERE, "situ_probe.cu"), os.path.join(HERE, "store_probe.cu")]
 
 
 def build(force=False):

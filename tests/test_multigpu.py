@@ -1,6 +1,8 @@
-"""The real NVLink path: one process per GPU, CUDA IPC peer tables, the flag protocol across
-devices, pull reduce-scatter, fused kernel and push all-gather at world 2 (and 4 when present).
-Skipped on a single-GPU box."""
+"""The real NVLink path: one process per GPU, CUDA IPC peer tables, the flag protocol across devices, pull
+reduce-scatter, fused kernel, push all-gather with its ticket tail and the dispatch to owning ranks at world 2, 4
+and 8 (as many as the box has GPUs), each checked against the CPU oracle and then soaked for 500 replays whose
+inputs change every replay (tests/multigpu_worker.py).  NVLS is off in NCCL for these runs and every wait in the
+kernels is bounded.  Skipped on a single-GPU box."""
 import os
 import subprocess
 import sys

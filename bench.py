@@ -477,31 +477,33 @@ def bench_dispatch(k3g, rank, world, dev, timed, barrier):
     units = collective_units(T, world, H)
     b_qall, b_sfall = pg.symmetric("d_q_all", T * H), pg.symmetric("d_sf_all", T * H // 32)
     b_oq, b_osf = pg.symmetric("d_out_q", cap * H), pg.symmetric("d_out_sf", cap * H // 32)
-    b_fl = pg.symmetric("d_flags", 64)
+    # one flag table per timed call list: a slot has to see exactly one arrival per epoch of its table
+    b_fls = [pg.symmetric("d_flags%d" % i, 64) for i in range(3)]
     q_all, sf_all = b_qall.tensor(torch.uint8, (T, H)), b_sfall.tensor(torch.uint8, (T, H // 32))
     out_q, out_sf = b_oq.tensor(torch.uint8, (cap, H)), b_osf.tensor(torch.uint8, (cap, H // 32))
-    flags = b_fl.tensor(torch.int64, (8,))
+    fls = [b.tensor(torch.int64, (8,)) for b in b_fls]
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-    k3g.call("k3g_flags_init", flags, 8, s)
+    for f in fls:
+        k3g.call("k3g_flags_init", f, 8, s)
     sel_q = torch.empty((rows, H), dtype=torch.uint8, device=dev); sel_sf = torch.empty((rows, H // 32), dtype=torch.uint8, device=dev)
     barrier()
 
     def gather_then_select():
-        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_epoch_bump", fls[0], units, s)
         k3g.call("k3g_allgather4_push", q_own, q_all, b_qall.table, q_own.numel(), sf_own, sf_all, b_sfall.table, sf_own.numel(), None, None, None, 0,
-                 None, None, None, 0, flags, b_fl.table, 1, rank, world, units, 2_000_000, status, s)
+                 None, None, None, 0, fls[0], b_fls[0].table, 1, rank, world, units, 2_000_000, status, s)
         k3g.call("k3g_permute_gather", q_all, sf_all, mine["rm"], rows, H, sel_q, sel_sf, s)
 
     def dispatch():
-        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_epoch_bump", fls[1], units, s)
         k3g.call("k3g_permute_dispatch", q_own, sf_own, idx_all, everyone["e2p"], everyone["bo"], B, rank * B, K, H, 224, world, 1, b_oq.table,
                  b_osf.table, s)
-        k3g.call("k3g_rs_arrive", flags, b_fl.table, units, 2, world, 2_000_000, status, s)
+        k3g.call("k3g_rs_arrive", fls[1], b_fls[1].table, units, 1, world, 2_000_000, status, s)
 
     def ag_only():
-        k3g.call("k3g_epoch_bump", flags, units, s)
+        k3g.call("k3g_epoch_bump", fls[2], units, s)
         k3g.call("k3g_allgather4_push", q_own, q_all, b_qall.table, q_own.numel(), sf_own, sf_all, b_sfall.table, sf_own.numel(), None, None, None, 0,
-                 None, None, None, 0, flags, b_fl.table, 3, rank, world, units, 2_000_000, status, s)
+                 None, None, None, 0, fls[2], b_fls[2].table, 1, rank, world, units, 2_000_000, status, s)
     a_us = timed(gather_then_select, 20, 3)
     ag_us = timed(ag_only, 20, 3)
     out_q.fill_(0xEE); out_sf.fill_(0xEE)

@@ -97,7 +97,8 @@ int k3g_quant_fp8_apply(const void* x, void* y, void* scale_out, const void* par
  * ring-order chain of row rank * B + b (k3g_rs_pull with order 2 (nranks - 1)) and continues as
  * k3g_land_add_attnres_rms_stats_amax; outputs are bit-identical to the two calls in sequence, the reduce-scattered
  * tensor is never written.  Bracket with k3g_rs_arrive as for k3g_rs_pull.  H = 7168; nranks 1, 2, 4 or 8; stats
- * and rowmax may be null. */
+ * and rowmax may be null.  With nranks > 1 every rank's partial buffer must be 32-byte aligned (peer rows are read
+ * 32 bytes per access). */
 int k3g_rs_land_add_attnres_rms(const void* partial, const void* partial_peer, int rank, int nranks, const void* prefix,
                                 const void* blocks, const void* sw, const void* gamma, void* prefix2, void* normed, int nb,
                                 int snapshot, int B, int H, float eps, const void* stats, int nb_stats, void* rowmax, void* stream);
@@ -248,7 +249,9 @@ int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long long n0, 
  * kern_k3_rs_pull + kern_k3_land_add_attnres_rms (nb = 0) + kern_k3_moe_quant + the all-gather push of
  * kern_k3_attnres_rms_push (source/k3_residual_push_add2.cu:356-360) in one kernel.  Bracket it with
  * k3g_rs_arrive before (partials ready) and after (pushes landed).  Processes rows
- * [row_begin, row_begin + rows) of a shard of shard_rows rows (shard_rows <= 0: shard = rows). */
+ * [row_begin, row_begin + rows) of a shard of shard_rows rows (shard_rows <= 0: shard = rows).  With nranks > 1
+ * every rank's partial buffer must be 32-byte aligned (peer rows are read 32 bytes per access; scale bytes leave
+ * as 16-byte stores, staged per row in shared memory). */
 int k3g_rs_resnorm_mxfp8_ag(const void* partial, const void* partial_peer, const void* residual, const void* gamma,
                             void* residual_out, void* q_all, const void* q_all_peer, void* sf_all, const void* sf_all_peer,
                             int rows, int H, float eps, int rank, int nranks, int grid_hint, int row_begin, int shard_rows,

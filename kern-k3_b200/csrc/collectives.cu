@@ -127,6 +127,21 @@ __device__ __forceinline__ void block_arrive_tail(unsigned long long* flags, con
 }
 
 // ---- reduce-scatter, pull form (rs_bases / rs_chain: k3g_device.cuh) ---------------------------
+// 32 bytes per access when the chunk allows it: the chain is element-wise, so the wider access needs no exchange.
+template <int NR>
+__device__ __forceinline__ V16 rs_chain32(const uint4* const (&base)[NR], long long i) {
+  V16 x[NR];
+#pragma unroll
+  for (int k = 0; k < NR; ++k) x[k] = ld_plain32(base[k] + 2 * i);   // all hops' loads issued back to back
+  V16 a = x[0];
+#pragma unroll
+  for (int k = 1; k < NR; ++k) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a.w[j] = add_bf2(a.w[j], x[k].w[j]);
+  }
+  return a;
+}
+
 template <int NR, int OWNPOS, int DESCEND>
 __device__ __forceinline__ void rs_pull_body(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                              const unsigned long long* __restrict__ src_peer, long long count, int rank) {
@@ -135,6 +150,20 @@ __device__ __forceinline__ void rs_pull_body(const __nv_bfloat16* __restrict__ s
   rs_bases<NR, OWNPOS, DESCEND>(src, src_peer, (long long)rank * count, rank, base);
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  bool wide = (count & 15) == 0 && (reinterpret_cast<unsigned long long>(dst) & 31ull) == 0;
+#pragma unroll
+  for (int k = 0; k < NR; ++k) wide = wide && (reinterpret_cast<unsigned long long>(base[k]) & 31ull) == 0;
+  if (wide) {                                          // uniform over the grid
+    const long long n32 = count >> 4;
+    long long i = tid;
+    for (; i + stride < n32; i += 2 * stride) {        // two 32-byte vectors per hop in flight per thread
+      const V16 a = rs_chain32<NR>(base, i), b = rs_chain32<NR>(base, i + stride);
+      st_stream32(reinterpret_cast<unsigned char*>(dst) + 32 * i, a);
+      st_stream32(reinterpret_cast<unsigned char*>(dst) + 32 * (i + stride), b);
+    }
+    if (i < n32) st_stream32(reinterpret_cast<unsigned char*>(dst) + 32 * i, rs_chain32<NR>(base, i));
+    return;
+  }
   long long i = tid;
   for (; i + stride < nvec; i += 2 * stride) {      // two vectors per thread in flight
     const V8 a = rs_chain<NR>(base, i), b = rs_chain<NR>(base, i + stride);
@@ -179,6 +208,20 @@ __global__ void __launch_bounds__(1024) rs_pull_kernel(const __nv_bfloat16* src,
 __device__ __forceinline__ void push_span(const unsigned char* __restrict__ s, unsigned char* __restrict__ d,
                                           const unsigned long long* __restrict__ p, long long nb, int rank, int nr, long long tid,
                                           long long stride) {
+  // 32 bytes per access when the span allows it (every rank's copy is then assumed 32-byte aligned like this one)
+  if ((nb & 31) == 0 && ((reinterpret_cast<unsigned long long>(s) | reinterpret_cast<unsigned long long>(d)) & 31ull) == 0) {
+    const long long n32 = nb >> 5;
+    for (long long i = tid; i < n32; i += stride) {
+      const V16 val = ld_stream32(s + (i << 5));
+      const long long eb = (long long)rank * nb + (i << 5);
+      *reinterpret_cast<uint4*>(d + eb) = make_uint4(val.w[0], val.w[1], val.w[2], val.w[3]);          // own copy: keep in L2 for the consumer
+      *reinterpret_cast<uint4*>(d + eb + 16) = make_uint4(val.w[4], val.w[5], val.w[6], val.w[7]);
+#pragma unroll
+      for (int q = 0; q < K3G_MAX_RANKS; ++q)
+        if (q < nr && q != rank) st_stream32(reinterpret_cast<unsigned char*>(p[q]) + eb, val);
+    }
+    return;
+  }
   const long long nv = nb >> 4;
   for (long long i = tid; i < nv; i += stride) {
     const V8 val = ld_stream(s + (i << 4));
@@ -212,8 +255,8 @@ __device__ __forceinline__ void allgather4_body(const unsigned char* s0, unsigne
 // fusion (same team layout and reduction order as resnorm.cu); codes and scales are stored to
 // every rank's gathered buffers.  The caller brackets this kernel with two arrive launches.
 constexpr int kTeam = 128;
-#ifndef K3G_FUSED_PAIR16
-#define K3G_FUSED_PAIR16 1
+#ifndef K3G_FUSED_WIDE_PULL
+#define K3G_FUSED_WIDE_PULL 1      /* 32-byte peer loads in the fused kernel; 0 keeps the 16-byte form for comparison builds */
 #endif
 
 template <int VPT, int NR>
@@ -229,9 +272,6 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
   // block barrier per row).
   constexpr bool kStageScales = NR > 1 && (H / 32) % 16 == 0;
   constexpr int kSfVecs = H / 512;                      // 16-byte vectors of scale bytes per row
-  // ... and the codes leave as 16-byte stores: a thread's vector is 8 codes, so neighbouring lanes swap halves of a
-  // pair of vectors (K3G_FUSED_PAIR16 = 0 keeps the 8-byte stores, for comparison runs).
-  constexpr bool kPairCodes = kStageScales && K3G_FUSED_PAIR16;
   __shared__ float s_red[2][kTeam / 32];
   __shared__ __align__(16) unsigned s_sf[2][kStageScales ? H / 128 : 1];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -252,27 +292,31 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
   for (int b = row_begin + blockIdx.x; b < row_begin + rows; b += gridDim.x, ++it) {
     const size_t rowoff = (size_t)b * H;
     V8 x[VPT];
+    if (K3G_FUSED_WIDE_PULL && NR > 1) {
+      rs_chain_team_row<VPT, NR, (NR == 2 ? 4 : NR == 4 ? 2 : 1)>(base, (long long)(rowoff >> 3), t, x);
+    } else {
 #pragma unroll
-    for (int v0 = 0; v0 < VPT; v0 += CH) {
-      V8 p[CH][NR];
+      for (int v0 = 0; v0 < VPT; v0 += CH) {
+        V8 p[CH][NR];
 #pragma unroll
-      for (int k = 0; k < NR; ++k) {
+        for (int k = 0; k < NR; ++k) {
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            if (v0 + c < VPT) {
+              const long long vi = (long long)((rowoff + (t + (v0 + c) * kTeam) * 8) >> 3);
+              p[c][k] = NR == 1 ? ld_stream(base[k] + vi) : ld_plain(base[k] + vi);
+            }
+          }
+        }
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
           if (v0 + c < VPT) {
-            const long long vi = (long long)((rowoff + (t + (v0 + c) * kTeam) * 8) >> 3);
-            p[c][k] = NR == 1 ? ld_stream(base[k] + vi) : ld_plain(base[k] + vi);
-          }
-        }
-      }
+            x[v0 + c] = p[c][0];
 #pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        if (v0 + c < VPT) {
-          x[v0 + c] = p[c][0];
+            for (int k = 1; k < NR; ++k) {
 #pragma unroll
-          for (int k = 1; k < NR; ++k) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) x[v0 + c].w[j] = add_bf2(x[v0 + c].w[j], p[c][k].w[j]);
+              for (int j = 0; j < 4; ++j) x[v0 + c].w[j] = add_bf2(x[v0 + c].w[j], p[c][k].w[j]);
+            }
           }
         }
       }
@@ -308,7 +352,6 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
 #pragma unroll
     for (int w = 0; w < kTeam / 32; ++w) tot = __fadd_rn(tot, red[w]);
     const float rr = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
-    unsigned hq0 = 0u, hq1 = 0u;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int u = (t + v * kTeam) * 8;
@@ -327,23 +370,10 @@ __global__ void __launch_bounds__(kTeam, 4) rs_resnorm_mxfp8_ag_kernel(
       sfb |= __shfl_down_sync(0xffffffffu, sfb, 4) << 8;
       sfb |= __shfl_down_sync(0xffffffffu, sfb, 8) << 16;
       if (kStageScales && (lane & 15) == 0) s_sf[it & 1][u >> 7] = sfb;
-      if (kPairCodes && (v & 1) == 0 && v + 1 < VPT) {
-        hq0 = q0; hq1 = q1;                              // wait for vector v + 1
-      } else if (kPairCodes && (v & 1) == 1) {
-        // vectors v - 1 and v: the even lane stores its own vector v - 1 and the odd neighbour's (16 contiguous
-        // bytes), the odd lane the even neighbour's vector v and its own; each lane hands over the other half
-        const bool odd = (lane & 1) != 0;
-        const unsigned g0 = __shfl_xor_sync(0xffffffffu, odd ? hq0 : q0, 1), g1 = __shfl_xor_sync(0xffffffffu, odd ? hq1 : q1, 1);
-        const V8 w = odd ? V8{{g0, g1, q0, q1}} : V8{{hq0, hq1, g0, g1}};
-        const int uu = odd ? u - 8 : u - kTeam * 8;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) st_stream(qdst[r] + rowoff + uu, w);
-      } else {
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          st_stream8(qdst[r] + rowoff + u, q0, q1);
-          if (!kStageScales && (lane & 15) == 0) *reinterpret_cast<unsigned*>(sfdst[r] + (size_t)b * (H / 32) + (u >> 5)) = sfb;
-        }
+      for (int r = 0; r < NR; ++r) {
+        st_stream8(qdst[r] + rowoff + u, q0, q1);
+        if (!kStageScales && (lane & 15) == 0) *reinterpret_cast<unsigned*>(sfdst[r] + (size_t)b * (H / 32) + (u >> 5)) = sfb;
       }
     }
     if (kStageScales) {
@@ -629,6 +659,7 @@ K3G_API int k3g_rs_resnorm_mxfp8_ag(const void* partial, const void* partial_pee
   K3G_REQUIRE(rows >= 0 && (H == 1024 || H == 2048 || H == 7168), K3G_ESHAPE);
   if (shard_rows <= 0) shard_rows = rows;                       // whole shard in one call
   K3G_REQUIRE(row_begin >= 0 && row_begin + rows <= shard_rows, K3G_ERANGE);
+  if (nranks > 1) K3G_REQUIRE((reinterpret_cast<uintptr_t>(partial) & 31u) == 0, K3G_EALIGN);   // peers are read 32 bytes at a time
   if (rows == 0) return K3G_OK;
   const int grid = grid_hint > 0 && grid_hint < rows ? grid_hint : rows;
   cudaStream_t st = k3g_stream(stream);

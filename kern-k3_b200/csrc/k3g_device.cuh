@@ -45,6 +45,43 @@ __device__ __forceinline__ void st_plain(void* p, const V8& v) {
   *(uint4*)p = make_uint4(v.w[0], v.w[1], v.w[2], v.w[3]);
 }
 
+// 32 bytes at a time (sm_100: 256-bit global loads and stores), for kernels that only move bytes.
+struct V16 { unsigned w[8]; };
+template <int BYTES> struct VecOf;
+template <> struct VecOf<16> { typedef V8 type; };
+template <> struct VecOf<32> { typedef V16 type; };
+__device__ __forceinline__ V16 ld_stream32(const void* p) {
+  V16 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ V16 ld_plain32(const void* p) {      // plain (possibly remote / coherent) load
+  V16 v;
+  asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ V16 ld_keep32(const void* p) {       // read-only path, allocated in the caches
+  V16 v;
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream32(void* p, const V16& v) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7]) : "memory");
+}
+template <int BYTES> __device__ __forceinline__ typename VecOf<BYTES>::type ld_stream_vec(const void* p);
+template <> __device__ __forceinline__ V8 ld_stream_vec<16>(const void* p) { return ld_stream(p); }
+template <> __device__ __forceinline__ V16 ld_stream_vec<32>(const void* p) { return ld_stream32(p); }
+template <int BYTES> __device__ __forceinline__ typename VecOf<BYTES>::type ld_keep_vec(const void* p);
+template <> __device__ __forceinline__ V8 ld_keep_vec<16>(const void* p) { return ld_keep(p); }
+template <> __device__ __forceinline__ V16 ld_keep_vec<32>(const void* p) { return ld_keep32(p); }
+template <int BYTES> __device__ __forceinline__ void st_stream_vec(void* p, const typename VecOf<BYTES>::type& v);
+template <> __device__ __forceinline__ void st_stream_vec<16>(void* p, const V8& v) { st_stream(p, v); }
+template <> __device__ __forceinline__ void st_stream_vec<32>(void* p, const V16& v) { st_stream32(p, v); }
+
 // ---- bf16 pairs ---------------------------------------------------------------------------
 __device__ __forceinline__ float bf_lo(unsigned u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(unsigned u) { return __uint_as_float(u & 0xffff0000u); }
@@ -193,5 +230,64 @@ __device__ __forceinline__ V8 rs_chain(const uint4* const (&base)[NR], long long
   return a;
 }
 
+// The same chain for one row in the 128-thread team layout (thread t owns the 16-byte vectors t + 128 v, v < VPT),
+// pulled with 32-BYTE loads: over NVLink the wider access moves measurably more (32-byte peer stores reached 666 GB/s
+// where 16-byte ones reached 590).  Vectors are taken in pairs (2p, 2p + 1): the even lane of a lane pair loads the
+// pair's two neighbouring vectors of chunk 2p, the odd lane those of chunk 2p + 1; the chain is added on all eight
+// words (it is element-wise, so it does not care whose element it is), and the two lanes then swap the halves that
+// belong to each other -- four shuffles per pair.  An odd last vector is loaded as 16 bytes.  PIF pairs are in flight
+// at a time (NR x 32 bytes each).  row_vec = index of the row's first 16-byte vector from each base; it must be even
+// and every base 32-byte aligned.
+template <int VPT, int NR, int PIF>
+__device__ __forceinline__ void rs_chain_team_row(const uint4* const (&base)[NR], long long row_vec, int t, V8 (&x)[VPT]) {
+  constexpr int kTeamThreads = 128;
+  const bool odd = (t & 1) != 0;
+#pragma unroll
+  for (int p0 = 0; p0 < VPT / 2; p0 += PIF) {
+    V16 a[PIF][NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) {
+#pragma unroll
+      for (int c = 0; c < PIF; ++c) {
+        if (p0 + c < VPT / 2) {
+          const int va = 2 * (p0 + c), vb = va + 1;
+          a[c][k] = ld_plain32(base[k] + row_vec + (t & ~1) + kTeamThreads * (odd ? vb : va));
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < PIF; ++c) {
+      if (p0 + c < VPT / 2) {
+        const int va = 2 * (p0 + c), vb = va + 1;
+        V16 s = a[c][0];
+#pragma unroll
+        for (int k = 1; k < NR; ++k) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s.w[j] = add_bf2(s.w[j], a[c][k].w[j]);
+        }
+        V8 got;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) got.w[j] = __shfl_xor_sync(0xffffffffu, odd ? s.w[j] : s.w[4 + j], 1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          x[va].w[j] = odd ? got.w[j] : s.w[j];
+          x[vb].w[j] = odd ? s.w[4 + j] : got.w[j];
+        }
+      }
+    }
+  }
+  if (VPT & 1) {
+    const long long vi = row_vec + t + kTeamThreads * (VPT - 1);
+    V8 q[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) q[k] = ld_plain(base[k] + vi);
+    x[VPT - 1] = q[0];
+#pragma unroll
+    for (int k = 1; k < NR; ++k) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[VPT - 1].w[j] = add_bf2(x[VPT - 1].w[j], q[k].w[j]);
+    }
+  }
+}
 
 }  // namespace k3g

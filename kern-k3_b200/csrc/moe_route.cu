@@ -19,7 +19,6 @@
 #include "k3g_host.h"
 
 #include <atomic>
-#include <cstdlib>
 
 using namespace k3g;
 
@@ -346,120 +345,21 @@ __device__ __forceinline__ void finalize_body(const __nv_bfloat16* __restrict__ 
 }
 
 // dst row r = src row route_map[r]: `cols` code bytes and cols / 32 scale bytes per row.
-// One WARP per destination row: a lane issues up to eight 16-byte loads before its first store,
-// rows are walked with a warp stride, and the token id of the next row is fetched one row ahead.
+// One WARP per destination row, rows walked with a warp stride, the token id of the next row fetched one row ahead.
+// A lane moves VB = 32 bytes per access where rows allow it (sm_100's 256-bit ld / st: measured on this part, a
+// store-only stream reaches 7.1 TB/s with 32-byte stores against 6.8 TB/s with 16-byte ones, and this kernel writes
+// eight bytes for every byte it reads from HBM) and issues up to eight loads -- a whole 7168-byte row -- before its
+// first store.  The scale bytes ride as 16-byte vectors.
+template <int VB>
 __global__ void __launch_bounds__(256) permute_gather_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
                                                              const int* __restrict__ route_map, long long rows, int cols,
                                                              uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
+  using Vec = typename VecOf<VB>::type;
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  const int qv = cols >> 4, sfb = cols >> 5;
+  const int qv = cols / VB, sfb = cols >> 5;
   const bool sf_vec = (sfb & 15) == 0;
-  long long r = warp;
-  long long t = r < rows ? route_map[r] : 0;
-  while (r < rows) {
-    const long long rn = r + nwarps;
-    const long long tn = rn < rows ? route_map[rn] : 0;
-    const uint4* src = reinterpret_cast<const uint4*>(q + t * cols);
-    uint4* dst = reinterpret_cast<uint4*>(out_q + r * cols);
-    for (int v0 = lane; v0 < qv; v0 += 8 * 32) {
-      uint4 x[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (v0 + 32 * u < qv) x[u] = __ldg(src + v0 + 32 * u);      // a token row is read once per expert it routes to: keep it cached
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (v0 + 32 * u < qv) __stcs(dst + v0 + 32 * u, x[u]);
-    }
-    if (sf_vec) {
-      if (lane < (sfb >> 4)) __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + lane, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + lane));
-    } else {
-      for (int b = lane; b < sfb; b += 32) out_sf[r * sfb + b] = sf[t * sfb + b];
-    }
-    r = rn; t = tn;
-  }
-}
-
-// ---- the same gather as a bulk row mover -------------------------------------------------------------------------
-// One elected thread per block moves whole rows with the copy engine of the SM (untiled cp.async.bulk: global ->
-// shared with an mbarrier counting the bytes, then shared -> global as a bulk group), kStages rows in flight per
-// block, so no register or LSU instruction touches the payload.  Local memory only; plain (single-CTA) bulk copies.
-// Needs 16-byte aligned rows: cols % 512 == 0 (then cols / 32 scale bytes are a multiple of 16 as well).
-// Every wait is bounded: a barrier that does not complete within kBulkSpin polls sets *err and the block drains
-// its outstanding stores and returns.
-constexpr int kBulkStages = 8;
-constexpr int kBulkSpin = 1 << 22;
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__global__ void __launch_bounds__(32) permute_gather_bulk_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
-                                                                 const int* __restrict__ route_map, long long rows, int cols,
-                                                                 uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf, int* err) {
-  extern __shared__ __align__(128) unsigned char bulk_smem[];
-  __shared__ __align__(8) unsigned long long bar[kBulkStages];
-  if (threadIdx.x != 0) return;
-  const int sfb = cols >> 5, rb = cols + sfb;                  // bytes per row: codes then scales, both multiples of 16
-  for (int s = 0; s < kBulkStages; ++s)
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(smem_u32(&bar[s])));
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  const long long first = blockIdx.x, step = gridDim.x;
-  const long long mine = first < rows ? (rows - first + step - 1) / step : 0;     // rows first, first + step, ...
-  auto load = [&](long long i) {                               // i-th row of this block into stage i % kBulkStages
-    const int s = (int)(i % kBulkStages);
-    const long long t = route_map[first + i * step];
-    const unsigned dst = smem_u32(bulk_smem + (size_t)s * rb), b = smem_u32(&bar[s]);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(b), "r"(rb) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(dst), "l"(q + t * cols), "r"(cols), "r"(b) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(dst + cols), "l"(sf + t * sfb), "r"(sfb), "r"(b) : "memory");
-  };
-  const long long prime = mine < kBulkStages ? mine : kBulkStages;
-  for (long long i = 0; i < prime; ++i) load(i);
-  bool failed = false;
-  for (long long i = 0; i < mine && !failed; ++i) {
-    const int s = (int)(i % kBulkStages);
-    const unsigned parity = (unsigned)((i / kBulkStages) & 1);
-    unsigned done = 0;
-    for (int spin = 0; spin < kBulkSpin && !done; ++spin)
-      asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                   : "=r"(done) : "r"(smem_u32(&bar[s])), "r"(parity) : "memory");
-    if (!done) { failed = true; break; }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    const long long r = first + i * step;
-    const unsigned src = smem_u32(bulk_smem + (size_t)s * rb);
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(out_q + r * cols), "r"(src), "r"(cols) : "memory");
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(out_sf + r * sfb), "r"(src + cols), "r"(sfb) : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    if (i >= 1 && i - 1 + kBulkStages < mine) {
-      // refill the stage of the PREVIOUS row: its stores must have read the stage, which "at most the newest group
-      // still reading" guarantees -- so this thread never waits on the store it has just issued
-      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      load(i - 1 + kBulkStages);
-    }
-  }
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");    // own stores have landed before the block exits
-  if (failed) {
-    // give the loads still in flight towards this block's shared memory a bounded chance to land before it goes away
-    for (int s = 0; s < kBulkStages; ++s) {
-      unsigned done = 0;
-      for (int spin = 0; spin < (kBulkSpin >> 4) && !done; ++spin)
-        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                     : "=r"(done) : "r"(smem_u32(&bar[s])), "r"(0u) : "memory");
-    }
-    if (err) atomicExch(err, 1);
-  }
-}
-
-// warp-per-row gather with 32-byte accesses per lane (sm_100 256-bit ld / st): half the instructions of the 16-byte form
-__global__ void __launch_bounds__(256) permute_gather_v8_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
-                                                                const int* __restrict__ route_map, long long rows, int cols,
-                                                                uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf) {
-  const int lane = threadIdx.x & 31;
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  const int qv = cols >> 5, sfb = cols >> 5;                 // 32-byte vectors of codes per row; scale bytes per row
   long long r = warp;
   long long t = r < rows ? route_map[r] : 0;
   while (r < rows) {
@@ -467,22 +367,20 @@ __global__ void __launch_bounds__(256) permute_gather_v8_kernel(const uint8_t* _
     const long long tn = rn < rows ? route_map[rn] : 0;
     const uint8_t* src = q + t * cols;
     uint8_t* dst = out_q + r * cols;
-    for (int v0 = lane; v0 < qv; v0 += 4 * 32) {
-      unsigned x[4][8];
+    for (int v0 = lane; v0 < qv; v0 += 8 * 32) {
+      Vec x[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + 32 * u < qv)
-          asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                       : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3]), "=r"(x[u][4]), "=r"(x[u][5]), "=r"(x[u][6]), "=r"(x[u][7])
-                       : "l"(src + (size_t)(v0 + 32 * u) * 32));
+      for (int u = 0; u < 8; ++u)
+        if (v0 + 32 * u < qv) x[u] = ld_keep_vec<VB>(src + (size_t)(v0 + 32 * u) * VB);      // a token row is read once per expert it routes to: keep it cached
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + 32 * u < qv)
-          asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                       :: "l"(dst + (size_t)(v0 + 32 * u) * 32), "r"(x[u][0]), "r"(x[u][1]), "r"(x[u][2]), "r"(x[u][3]), "r"(x[u][4]), "r"(x[u][5]),
-                          "r"(x[u][6]), "r"(x[u][7]) : "memory");
+      for (int u = 0; u < 8; ++u)
+        if (v0 + 32 * u < qv) st_stream_vec<VB>(dst + (size_t)(v0 + 32 * u) * VB, x[u]);
     }
-    if (lane < (sfb >> 4)) __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + lane, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + lane));
+    if (sf_vec) {
+      if (lane < (sfb >> 4)) __stcs(reinterpret_cast<uint4*>(out_sf + r * sfb) + lane, __ldg(reinterpret_cast<const uint4*>(sf + t * sfb) + lane));
+    } else {
+      for (int b = lane; b < sfb; b += 32) out_sf[r * sfb + b] = sf[t * sfb + b];
+    }
     r = rn; t = tn;
   }
 }
@@ -531,26 +429,22 @@ __global__ void __launch_bounds__(512) route_tables_scatter_wide_kernel(const in
 // Dispatch to the owning ranks (benchmark configuration 2): the MXFP8 row of every token of this rank's shard is
 // stored, once per expert it routes to, straight into the expert-sorted buffer of the rank that owns the expert
 // -- a peer address over NVLink, or this rank's own buffer.  One warp per token: the row (cols code bytes and
-// cols / 32 scale bytes) is read from HBM once, in chunks of eight 16-byte vectors per lane, and each chunk is
-// stored to the token's topk destination rows, 512 contiguous bytes per warp instruction; the scale bytes leave
-// as 16-byte stores.  Destination of slot k: owner = rank that holds expert ids[t, k]; row = exp2perm[t, k] of
+// cols / 32 scale bytes) is read from HBM once, eight vectors of VB = 32 (or 16) bytes per lane at a time, and each
+// chunk is stored to the token's topk destination rows, 1 KB (512 B) contiguous per warp instruction; the scale
+// bytes leave as 16-byte stores.  Destination of slot k: owner = rank that holds expert ids[t, k]; row = exp2perm[t, k] of
 // the all-owner tables minus the owner's first row (blockoff[owner * per], block 0 of the offsets table).
 // Plain stores only: no TMA, no multicast, nothing waits.  The caller follows with a barrier (k3g_rs_arrive).
-__global__ void __launch_bounds__(256) permute_dispatch_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
-                                                               const int* __restrict__ ids, const int* __restrict__ exp2perm,
-                                                               const int* __restrict__ blockoff, int B, long long token_begin, int topk,
-                                                               int cols, int per, int ep_ranks, int strided,
-                                                               const unsigned long long* __restrict__ q_peer,
-                                                               const unsigned long long* __restrict__ sf_peer) {
+template <int VB>
+__device__ __forceinline__ void permute_dispatch_body(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                                      const int* __restrict__ ids, const int* __restrict__ exp2perm, int B,
+                                                      long long token_begin, int topk, int cols, int per, int ep_ranks, int strided,
+                                                      unsigned long long my_q, unsigned long long my_sf, int my_base) {
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  const int qv = cols >> 4, sfb = cols >> 5;
+  using Vec = typename VecOf<VB>::type;
+  const int qv = cols / VB, sfb = cols >> 5;
   const bool sf_vec = (sfb & 15) == 0;
-  // lane o keeps owner o's buffer addresses and first row
-  unsigned long long my_q = 0ull, my_sf = 0ull;
-  int my_base = 0;
-  if (lane < ep_ranks) { my_q = q_peer[lane]; my_sf = sf_peer[lane]; my_base = blockoff[lane * per]; }
   for (long long b = warp; b < B; b += nwarps) {
     const long long t = token_begin + b;
     int owner = -1, row = -1;
@@ -563,21 +457,21 @@ __global__ void __launch_bounds__(256) permute_dispatch_kernel(const uint8_t* __
     const unsigned long long dq = __shfl_sync(0xffffffffu, my_q, owner < 0 ? 0 : owner);
     const unsigned long long dsf = __shfl_sync(0xffffffffu, my_sf, owner < 0 ? 0 : owner);
     const long long local_row = row >= 0 ? (long long)(row - base) : -1;
-    const uint4* src = reinterpret_cast<const uint4*>(q + b * cols);
+    const uint8_t* src = q + b * cols;
     for (int c0 = 0; c0 < qv; c0 += 8 * 32) {             // warp-uniform trip count: the shuffles below need every lane
       const int v0 = c0 + lane;
-      uint4 x[8];
+      Vec x[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)
-        if (v0 + 32 * u < qv) x[u] = __ldcs(src + v0 + 32 * u);
+        if (v0 + 32 * u < qv) x[u] = ld_stream_vec<VB>(src + (size_t)(v0 + 32 * u) * VB);
       for (int k = 0; k < topk; ++k) {
         const long long r = __shfl_sync(0xffffffffu, local_row, k);
         const unsigned long long d = __shfl_sync(0xffffffffu, dq, k);
         if (r < 0) continue;
-        uint4* dst = reinterpret_cast<uint4*>(d + (unsigned long long)r * cols);
+        uint8_t* dst = reinterpret_cast<uint8_t*>(d + (unsigned long long)r * cols);
 #pragma unroll
         for (int u = 0; u < 8; ++u)
-          if (v0 + 32 * u < qv) __stcs(dst + v0 + 32 * u, x[u]);
+          if (v0 + 32 * u < qv) st_stream_vec<VB>(dst + (size_t)(v0 + 32 * u) * VB, x[u]);
       }
     }
     if (sf_vec) {
@@ -597,6 +491,24 @@ __global__ void __launch_bounds__(256) permute_dispatch_kernel(const uint8_t* __
       }
     }
   }
+}
+
+__global__ void __launch_bounds__(256) permute_dispatch_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                                               const int* __restrict__ ids, const int* __restrict__ exp2perm,
+                                                               const int* __restrict__ blockoff, int B, long long token_begin, int topk,
+                                                               int cols, int per, int ep_ranks, int strided,
+                                                               const unsigned long long* __restrict__ q_peer,
+                                                               const unsigned long long* __restrict__ sf_peer) {
+  // lane o keeps owner o's buffer addresses and first row
+  const int lane = threadIdx.x & 31;
+  unsigned long long my_q = 0ull, my_sf = 0ull;
+  int my_base = 0;
+  if (lane < ep_ranks) { my_q = q_peer[lane]; my_sf = sf_peer[lane]; my_base = blockoff[lane * per]; }
+  // 32-byte accesses when every source and destination row starts on a 32-byte boundary (uniform over the grid)
+  const bool wide = (cols & 31) == 0 && (reinterpret_cast<unsigned long long>(q) & 31ull) == 0 &&
+                    __all_sync(0xffffffffu, (my_q & 31ull) == 0);
+  if (wide) permute_dispatch_body<32>(q, sf, ids, exp2perm, B, token_begin, topk, cols, per, ep_ranks, strided, my_q, my_sf, my_base);
+  else permute_dispatch_body<16>(q, sf, ids, exp2perm, B, token_begin, topk, cols, per, ep_ranks, strided, my_q, my_sf, my_base);
 }
 
 template <bool RESIDUAL>
@@ -833,28 +745,15 @@ K3G_API int k3g_permute_gather(const void* q, const void* sf, const void* route_
   K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0, K3G_ESHAPE);
   if ((cols >> 5) % 16 == 0) { K3G_REQUIRE_ALIGNED(sf); K3G_REQUIRE_ALIGNED(out_sf); }
   if (rows == 0) return K3G_OK;
-  static const int variant = getenv("K3G_PERMUTE_VARIANT") ? atoi(getenv("K3G_PERMUTE_VARIANT")) : 0;
-  if (variant == 1 && cols % 512 == 0 && ((uintptr_t)q & 31) == 0 && ((uintptr_t)out_q & 31) == 0) {
-    long long g1 = (rows + 7) / 8;
-    if (g1 > 148 * 64) g1 = 148 * 64;
-    permute_gather_v8_kernel<<<(unsigned)g1, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
-                                                                          cols, (uint8_t*)out_q, (uint8_t*)out_sf);
-    return k3g_launch_status();
-  }
-  if (variant >= 2 && cols % 512 == 0) {
-    const int smem = kBulkStages * (cols + cols / 32);
-    static std::atomic<bool> opted[64];
-    if (int rc = opt_in_wide_smem(permute_gather_bulk_kernel, opted, smem)) return rc;
-    const int per_sm = variant == 2 ? 3 : variant - 2;
-    long long g2 = rows < 148LL * per_sm ? rows : 148LL * per_sm;
-    permute_gather_bulk_kernel<<<(unsigned)g2, 32, smem, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
-                                                                              cols, (uint8_t*)out_q, (uint8_t*)out_sf, nullptr);
-    return k3g_launch_status();
-  }
   long long grid = (rows + 7) / 8;                 // eight warps per block, one row per warp pass
   if (grid > 148 * 64) grid = 148 * 64;            // then rows are walked with a warp stride
-  permute_gather_kernel<<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
-                                                                       cols, (uint8_t*)out_q, (uint8_t*)out_sf);
+  const bool wide = cols % 32 == 0 && ((uintptr_t)q & 31) == 0 && ((uintptr_t)out_q & 31) == 0;    // every row starts on a 32-byte boundary
+  if (wide)
+    permute_gather_kernel<32><<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
+                                                                             cols, (uint8_t*)out_q, (uint8_t*)out_sf);
+  else
+    permute_gather_kernel<16><<<(unsigned)grid, 256, 0, k3g_stream(stream)>>>((const uint8_t*)q, (const uint8_t*)sf, (const int*)route_map, rows,
+                                                                             cols, (uint8_t*)out_q, (uint8_t*)out_sf);
   return k3g_launch_status();
 }
 K3G_API int k3g_permute_dispatch(const void* q, const void* sf, const void* ids, const void* exp2perm, const void* blockoff, int B,

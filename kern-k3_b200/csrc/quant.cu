@@ -59,23 +59,110 @@ __device__ __forceinline__ unsigned block_max_u32(unsigned m) {
 
 // partials[b] = max |x| over block b's slice, as f32.  |bf16| ordering = unsigned ordering of
 // the low 15 bits, so the maximum is taken on bit patterns (exact, order-free).
-extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_amax_v2(const __nv_bfloat16* __restrict__ x, int n,
-                                                                           float* __restrict__ partials) {
-  const uint4* p = reinterpret_cast<const uint4*>(x);
-  const int nv = n >> 3;
-  unsigned m2 = 0;   // two 15-bit maxima, packed like the data
-  for (int i = blockIdx.x * K3G_QT + threadIdx.x; i < nv; i += gridDim.x * K3G_QT) {
-    const uint4 v = p[i];
-    m2 = __vmaxu2(m2, v.x & 0x7fff7fffu);
-    m2 = __vmaxu2(m2, v.y & 0x7fff7fffu);
-    m2 = __vmaxu2(m2, v.z & 0x7fff7fffu);
-    m2 = __vmaxu2(m2, v.w & 0x7fff7fffu);
+// VB bytes per access (32 when x allows it), four accesses in flight per thread: the pass is a pure read stream and
+// one 16-byte load per thread at a time leaves HBM half idle.  Loads allocate in L2 on purpose (see the apply pass).
+template <int VB>
+__device__ __forceinline__ unsigned amax_words(const unsigned char* p) {
+  unsigned m2 = 0;
+  if (VB == 32) {
+    unsigned w[8];
+    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m2 = __vmaxu2(m2, w[j] & 0x7fff7fffu);
+  } else {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    m2 = __vmaxu2(__vmaxu2(v.x & 0x7fff7fffu, v.y & 0x7fff7fffu), __vmaxu2(v.z & 0x7fff7fffu, v.w & 0x7fff7fffu));
   }
+  return m2;
+}
+
+template <int VB>
+__device__ __forceinline__ void amax_body(const __nv_bfloat16* __restrict__ x, int n, float* __restrict__ partials) {
+  constexpr int EPV = VB / 2;                                      // elements per access
+  const unsigned char* p = reinterpret_cast<const unsigned char*>(x);
+  const long long nv = n / EPV;
+  const long long stride = (long long)gridDim.x * K3G_QT;
+  unsigned m2 = 0;   // two 15-bit maxima, packed like the data
+  long long i = (long long)blockIdx.x * K3G_QT + threadIdx.x;
+  for (; i + 3 * stride < nv; i += 4 * stride) {
+    const unsigned a = amax_words<VB>(p + i * VB), b = amax_words<VB>(p + (i + stride) * VB);
+    const unsigned c = amax_words<VB>(p + (i + 2 * stride) * VB), d = amax_words<VB>(p + (i + 3 * stride) * VB);
+    m2 = __vmaxu2(m2, __vmaxu2(__vmaxu2(a, b), __vmaxu2(c, d)));
+  }
+  for (; i < nv; i += stride) m2 = __vmaxu2(m2, amax_words<VB>(p + i * VB));
   unsigned m = max(m2 & 0xffffu, m2 >> 16);
-  if (blockIdx.x == 0 && threadIdx.x < (n & 7))
-    m = max(m, (unsigned)__bfloat16_as_ushort(x[nv * 8 + threadIdx.x]) & 0x7fffu);
+  if (blockIdx.x == 0 && threadIdx.x < (n % EPV))
+    m = max(m, (unsigned)__bfloat16_as_ushort(x[nv * EPV + threadIdx.x]) & 0x7fffu);
   m = block_max_u32(m);
   if (threadIdx.x == 0) partials[blockIdx.x] = __uint_as_float(m << 16);
+}
+
+extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_amax_v2(const __nv_bfloat16* __restrict__ x, int n,
+                                                                           float* __restrict__ partials) {
+  if ((reinterpret_cast<unsigned long long>(x) & 31ull) == 0) amax_body<32>(x, n, partials);
+  else amax_body<16>(x, n, partials);
+}
+
+// y = e4m3(x * (1 / scale)), scale = max(partials) / 448.  The tensor is walked BACKWARDS: the amax pass went forwards
+// with L2-allocating loads, so what it touched last is what this pass reads first, out of the 126 MB L2.  VB = 32:
+// a thread converts sixteen elements per access (one 32-byte load, one 16-byte store), two accesses in flight.
+template <int VB>
+__device__ __forceinline__ void apply_vec(const unsigned char* xp, uint8_t* yp, float inv) {
+  if (VB == 32) {
+    const V16 v = ld_stream32(xp);
+    V8 lo, hi, o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { lo.w[j] = v.w[j]; hi.w[j] = v.w[4 + j]; }
+    quant8(lo, inv, o.w[0], o.w[1]);
+    quant8(hi, inv, o.w[2], o.w[3]);
+    st_stream(yp, o);
+  } else {
+    const V8 v = ld_stream(xp);
+    unsigned q0, q1;
+    quant8(v, inv, q0, q1);
+    st_stream8(yp, q0, q1);
+  }
+}
+
+template <int VB>
+__device__ __forceinline__ void apply_body(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, int n, float inv) {
+  constexpr int EPV = VB / 2;
+  const unsigned char* xp = reinterpret_cast<const unsigned char*>(x);
+  const long long nv = n / EPV;
+  const long long total = (long long)gridDim.x * K3G_QT;
+  // backwards: start with the part of x the amax pass touched last
+  for (long long i = nv - 1 - ((long long)blockIdx.x * K3G_QT + threadIdx.x); i >= 0; i -= 2 * total) {
+    const long long i1 = i - total;
+    if (i1 >= 0) {
+      // both loads issued before the first conversion
+      if (VB == 32) {
+        const V16 a = ld_stream32(xp + i * VB), b = ld_stream32(xp + i1 * VB);
+        V8 lo, hi, o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { lo.w[j] = a.w[j]; hi.w[j] = a.w[4 + j]; }
+        quant8(lo, inv, o.w[0], o.w[1]); quant8(hi, inv, o.w[2], o.w[3]);
+        st_stream(y + i * EPV, o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { lo.w[j] = b.w[j]; hi.w[j] = b.w[4 + j]; }
+        quant8(lo, inv, o.w[0], o.w[1]); quant8(hi, inv, o.w[2], o.w[3]);
+        st_stream(y + i1 * EPV, o);
+      } else {
+        const V8 a = ld_stream(xp + i * VB), b = ld_stream(xp + i1 * VB);
+        unsigned q0, q1;
+        quant8(a, inv, q0, q1);
+        st_stream8(y + i * EPV, q0, q1);
+        quant8(b, inv, q0, q1);
+        st_stream8(y + i1 * EPV, q0, q1);
+      }
+    } else {
+      apply_vec<VB>(xp + i * VB, y + i * EPV, inv);
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n % EPV)) {
+    const long long i = nv * EPV + threadIdx.x;
+    y[i] = (uint8_t)(e4m3x2(__fmul_rn(__bfloat162float(x[i]), inv), 0.f) & 0xffu);
+  }
 }
 
 extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_apply_v2(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, int n,
@@ -87,27 +174,8 @@ extern "C" __global__ void __launch_bounds__(K3G_QT) kern_quant_fp8_apply_v2(con
   const float scale = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
   if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = scale;
   const float inv = __fdiv_rn(1.f, scale);
-
-  const int nv = n >> 3;
-  const int total = gridDim.x * K3G_QT;
-  // backwards: start with the part of x the amax pass touched last
-  for (int i = nv - 1 - (blockIdx.x * K3G_QT + threadIdx.x); i >= 0; i -= 2 * total) {   // two vectors in flight per thread
-    const int i1 = i - total;
-    const V8 v = ld_stream(x + (size_t)i * 8);
-    V8 w = v;
-    if (i1 >= 0) w = ld_stream(x + (size_t)i1 * 8);
-    unsigned q0, q1;
-    quant8(v, inv, q0, q1);
-    st_stream8(y + (size_t)i * 8, q0, q1);
-    if (i1 >= 0) {
-      quant8(w, inv, q0, q1);
-      st_stream8(y + (size_t)i1 * 8, q0, q1);
-    }
-  }
-  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
-    const int i = nv * 8 + threadIdx.x;
-    y[i] = (uint8_t)(e4m3x2(__fmul_rn(__bfloat162float(x[i]), inv), 0.f) & 0xffu);
-  }
+  if ((reinterpret_cast<unsigned long long>(x) & 31ull) == 0 && (reinterpret_cast<unsigned long long>(y) & 15ull) == 0) apply_body<32>(x, y, n, inv);
+  else apply_body<16>(x, y, n, inv);
 }
 
 #ifndef K3G_CUBIN_ONLY

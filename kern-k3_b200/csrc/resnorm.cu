@@ -294,30 +294,35 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
   for (int b = blockIdx.x; b < B; b += gridDim.x, ++it) {
     const size_t base = (size_t)b * H;
     V8 x[VPT];
-    if constexpr (NR > 0) {
-      // pull the NR partial rows a few vectors at a time (CH (NR + 1) loads in flight per thread), land the chain, add
-      constexpr int CH = NR == 1 ? VPT : NR == 2 ? 4 : NR == 4 ? 2 : 1;
+    if constexpr (NR > 1) {
+      // pull the NR partial rows with 32-byte loads and land the ring-order chain (k3g::rs_chain_team_row), then add
+      rs_chain_team_row<VPT, NR, (NR == 2 ? 2 : 1)>(ring, (long long)(base >> 3), t, x);
+      if (!snapshot) {
+        V8 pr[VPT];
 #pragma unroll
-      for (int v0 = 0; v0 < VPT; v0 += CH) {
-        V8 pr[CH], p[CH];
+        for (int v = 0; v < VPT; ++v) pr[v] = ld_stream(prefix + base + (t + v * kTeam) * 8);
 #pragma unroll
-        for (int c = 0; c < CH; ++c)
-          if (v0 + c < VPT && !snapshot) pr[c] = ld_stream(prefix + base + (t + (v0 + c) * kTeam) * 8);
+        for (int v = 0; v < VPT; ++v) {
 #pragma unroll
-        for (int c = 0; c < CH; ++c)
-          if (v0 + c < VPT) p[c] = rs_chain<NRC>(ring, (long long)((base >> 3) + t + (v0 + c) * kTeam));
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          if (v0 + c >= VPT) continue;
-          const int v = v0 + c;
-          if (snapshot) {
-            x[v] = p[c];
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr[c].w[j], p[c].w[j]);
-          }
-          st_stream(prefix2 + base + (t + v * kTeam) * 8, x[v]);
+          for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr[v].w[j], x[v].w[j]);
         }
+      }
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) st_stream(prefix2 + base + (t + v * kTeam) * 8, x[v]);
+    } else if constexpr (NR == 1) {
+      // a single rank: the chain is the rank's own partial row
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) {
+        const size_t off = base + (t + v * kTeam) * 8;
+        const V8 p = rs_chain<1>(ring, (long long)(off >> 3));
+        if (snapshot) {
+          x[v] = p;
+        } else {
+          const V8 pr = ld_stream(prefix + off);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr.w[j], p.w[j]);
+        }
+        st_stream(prefix2 + off, x[v]);
       }
     }
 #pragma unroll
@@ -420,6 +425,7 @@ __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict_
     const float r = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
     const size_t dst_off = ((size_t)rank * B + b) * H;
     unsigned m2 = 0u;
+    V8 held = V8{{0u, 0u, 0u, 0u}};
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int u = (t + v * kTeam) * 8;
@@ -431,9 +437,28 @@ __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict_
         m2 = __vmaxu2(m2, o.w[j] & 0x7fff7fffu);
       }
       st_plain(normed_all + dst_off + u, o);            // own slice: the next GEMM reads it, keep it in L2
+      // Peer copies leave as 32-byte stores (over NVLink the wider store moves measurably more): vectors go in pairs
+      // (v - 1, v); the even lane of a lane pair stores its own and its neighbour's vector v - 1, the odd lane the
+      // two vectors v, after the lanes have handed each other the missing halves.
+      if ((v & 1) == 0 && v + 1 < VPT) {
+        held = o;
+      } else if ((v & 1) == 1) {
+        const bool odd = (lane & 1) != 0;
+        V8 got;
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        if (peer[q] != nullptr) st_stream(peer[q] + dst_off + u, o);
+        for (int j = 0; j < 4; ++j) got.w[j] = __shfl_xor_sync(0xffffffffu, odd ? held.w[j] : o.w[j], 1);
+        V16 w;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { w.w[j] = odd ? got.w[j] : held.w[j]; w.w[4 + j] = odd ? o.w[j] : got.w[j]; }
+        const int uu = odd ? u - 8 : u - kTeam * 8;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (peer[q] != nullptr) st_stream32(peer[q] + dst_off + uu, w);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (peer[q] != nullptr) st_stream(peer[q] + dst_off + u, o);
+      }
     }
     if (rowmax_all != nullptr) {                        // max |normed| of the row, gathered like the row itself
       const unsigned m = team_absmax_bits(m2, s_amax[it & 1], lane, warp);
@@ -741,6 +766,7 @@ K3G_API int k3g_rs_land_add_attnres_rms(const void* partial, const void* partial
   K3G_REQUIRE_ALIGNED(gamma); K3G_REQUIRE_ALIGNED(prefix2); K3G_REQUIRE_ALIGNED(normed);
   K3G_REQUIRE(B >= 0 && H == 7168 && (nranks == 1 || nranks == 2 || nranks == 4 || nranks == 8), K3G_ESHAPE);
   K3G_REQUIRE(rank >= 0 && rank < nranks, K3G_ERANGE);
+  if (nranks > 1) K3G_REQUIRE((reinterpret_cast<uintptr_t>(partial) & 31u) == 0, K3G_EALIGN);   // peers are read 32 bytes at a time
   if (B == 0) return K3G_OK;
 #define K3G_RS_K1B(NR)                                                                                                                         \
   rs_land_add_attnres_rms_kernel<7, NR><<<B, kTeam, 0, k3g_stream(stream)>>>(                                                                   \

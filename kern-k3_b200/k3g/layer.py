@@ -215,46 +215,53 @@ class LayerGlue:
         return c
 
     def traffic(self):
-        """label prefix -> (algorithmic bytes per rank, bound): the unique bytes a call must move through HBM ("hbm") or
-        receive / send over NVLink ("nvlink", world > 1 only); small table kernels are "latency"."""
+        """label prefix -> (HBM bytes, NVLink bytes per direction) per rank: the unique bytes a call must move through this
+        GPU's HBM and must receive / send over NVLink (0 at world 1); small table kernels have neither."""
         W, T, B, inner, nb = self.world, self.T, self.B, self.inner, self.nb
         EB, ET = B * H * 2, T * H * 2                       # one bf16 pass over the shard / over all rows
-        link = lambda nbytes: ((W - 1) * nbytes, "nvlink")
+        link = lambda nbytes: (W - 1) * nbytes
+        small = B * (LATENT + LATENT // 32 + 2 * TOPK * 4)
         t = {
-            "coll_epoch": (0, "latency"), "normed_sync": (0, "latency"), "reduce_attn (arrive)": (0, "latency"), "scatter_moe (arrive)": (0, "latency"),
-            "res_in": link(EB) if W > 1 else ((3 + 2 * nb + 2) * EB, "hbm"),
-            "qkvg_quant": (3 * ET // 2, "hbm"),
-            "span_gather": (T * 3 * inner * 4 + T * 256 * 4, "hbm"), "span_state_in": (2 * 2 * self.heads * 128 * 128 * 4, "latency"),
-            "span_out_gate": (T * inner * 6, "hbm"),
-            "mla_prep": (T * ((2112 + inner) * 2 + (1536 + 576 + inner) * 2), "hbm"), "latent_gather": (T * 576 * 4, "hbm"),
-            "mla_gate": (T * inner * 6, "hbm"),
-            "reduce_attn (pull RS)": link(EB) if W > 1 else (2 * EB, "hbm"),
-            "res_mlp": ((4 + nb) * EB, "hbm"),
-            "reduce_attn + res_mlp": link(EB) if W > 1 else ((4 + nb) * EB, "hbm"),
-            "normed_quant": (3 * EB // 2, "hbm"), "topk": (B * EXPERTS * 4 + B * TOPK * 8, "latency"),
-            "moe_quant (": (B * LATENT * 3 + B * LATENT // 32, "hbm"),
-            "gather_small": link(B * (LATENT + LATENT // 32 + 2 * TOPK * 4)) if W > 1 else (2 * B * (LATENT + LATENT // 32 + 2 * TOPK * 4), "hbm"),
-            "moe_quant + gather_small": link(B * (LATENT + LATENT // 32 + 2 * TOPK * 4)) if W > 1 else (B * LATENT * 3, "hbm"),
-            "route_count": (0, "latency"), "route_tables": (0, "latency"), "route_scatter": (0, "latency"), "normed_sync (epoch": (0, "latency"),
-            "finalize": ((T * TOPK // self.ep + T) * LATENT * 2, "hbm"),
-            "scatter_moe (pull RS)": link(B * LATENT * 2) if W > 1 else (2 * B * LATENT * 2, "hbm"),
-            "shared_situ": (B * (SHARED * 6 + LATENT * 4), "hbm"),
-            "scatter_moe + shared_situ": link(B * LATENT * 2) if W > 1 else (B * (SHARED * 6 + LATENT * 4), "hbm"),
-            "shared_act_quant": (3 * B * SHARED, "hbm"),
+            "coll_epoch": (0, 0), "normed_sync": (0, 0), "reduce_attn (arrive)": (0, 0), "scatter_moe (arrive)": (0, 0),
+            "res_in": ((3 + 2 * nb + 2) * EB, link(EB)),
+            "qkvg_quant": (3 * ET // 2, 0),
+            "span_gather": (T * 3 * inner * 4 + T * 256 * 4, 0), "span_state_in": (0, 0),
+            "span_out_gate": (T * inner * 6, 0),
+            "mla_prep": (T * ((2112 + inner) * 2 + (1536 + 576 + inner) * 2), 0), "latent_gather": (T * 576 * 4, 0),
+            "mla_gate": (T * inner * 6, 0),
+            "reduce_attn (pull RS)": (2 * EB, link(EB)),
+            "res_mlp": ((4 + nb) * EB, 0),
+            "reduce_attn + res_mlp": ((4 + nb) * EB, link(EB)),
+            "normed_quant": (3 * EB // 2, 0), "topk": (0, 0),
+            "moe_quant (": (B * LATENT * 3 + B * LATENT // 32, 0),
+            "gather_small": (2 * small, link(small)),
+            "moe_quant + gather_small": (B * LATENT * 3, link(small)),
+            "route_count": (0, 0), "route_tables": (0, 0), "route_scatter": (0, 0),
+            "finalize": ((T * TOPK // self.ep + T) * LATENT * 2, 0),
+            "scatter_moe (pull RS)": (2 * B * LATENT * 2, link(B * LATENT * 2)),
+            "shared_situ": (B * (SHARED * 6 + LATENT * 4), 0),
+            "scatter_moe + shared_situ": (B * (SHARED * 6 + LATENT * 4), link(B * LATENT * 2)),
+            "shared_act_quant": (3 * B * SHARED, 0),
         }
         return t
+
+    def traffic_of(self, label, hbm_gbs=6529.7, link_gbs=770.0):
+        """(bytes, bound) of the call: the resource whose roofline time is larger -- "hbm", "nvlink" or "latency"."""
+        best = None
+        for k, v in self.traffic().items():
+            if label.startswith(k) and (best is None or len(k) > len(best[0])):
+                best = (k, v)
+        if best is None:
+            return 0, "latency"
+        hbm, lnk = best[1]
+        if hbm == 0 and lnk == 0:
+            return 0, "latency"
+        return (lnk, "nvlink") if lnk / link_gbs > hbm / hbm_gbs else (hbm, "hbm")
 
     def launches(self):
         """Kernel launches of one pass of the call list (a two-pass quantisation and the pair of state copies are two each)."""
         two = ("(fp8 tensor", "span_state_in + span_state_out")
         return sum(2 if any(k in label for k in two) else 1 for label, _ in self.calls())
-
-    def traffic_of(self, label):
-        best = None
-        for k, v in self.traffic().items():
-            if label.startswith(k) and (best is None or len(k) > len(best[0])):
-                best = (k, v)
-        return best[1] if best else (0, "latency")
 
     def run(self):
         for _, fn in self.calls():

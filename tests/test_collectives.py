@@ -82,12 +82,12 @@ def test_epoch_bump_folded_into_the_first_barrier(k3g, dev):
     torch.cuda.synchronize()
     f = flags.cpu().numpy()
     assert f[0] == f[1] == f[2] == 3 * 896 and not status.cpu().numpy().any()
-    # a peer that has not arrived in this epoch makes it expire like k3g_rs_arrive
-    peer = _flags(dev)
-    tab2 = _table([flags, peer], dev)
-    k3g.call("k3g_epoch_arrive", flags, tab2, 896, 3, 2, 1000, status, s)
+    # a peer that has not arrived in this epoch makes it expire like k3g_rs_arrive (fresh tables: a slot is used every epoch)
+    mine, peer = _flags(dev), _flags(dev)
+    tab2 = _table([mine, peer], dev)
+    k3g.call("k3g_epoch_arrive", mine, tab2, 896, 3, 2, 1000, status, s)
     torch.cuda.synchronize()
-    assert list(status.cpu().numpy()[:3]) == [1, 3, 1] and int(flags[0]) == 4 * 896
+    assert list(status.cpu().numpy()[:3]) == [1, 3, 1] and int(mine[0]) == 896 and int(mine[3]) == 896
 
 
 def test_bounded_wait_reports_and_returns(k3g, dev):

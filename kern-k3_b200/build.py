@@ -57,6 +57,9 @@ CUBINS = {
     "k3_mla_v2": ("glue_small.cu", []),
     "k3_span_gather_v3+HEADS=24": ("kda.cu", ["-DHEADS=24"]),
     "k3_kda_out_gate_v3+HEADS=24": ("kda.cu", ["-DHEADS=24"]),
+    # entries of the fused call list (patch_manifest.py --fuse); no counterpart module in the reference
+    "k3g_fused_residual": ("resnorm.cu", ["-DLAND_BF16=1", "-DK3G_FUSED_ENTRIES=1", "-DK3G_NR=4"]),
+    "k3g_fused_situ": ("glue_small.cu", ["-DK3G_FUSED_ENTRIES=1", "-DK3G_NR=4"]),
 }
 
 

@@ -276,6 +276,34 @@ __global__ void __launch_bounds__(128) rs_situ_rms_kernel(const __nv_bfloat16* _
   }
 }
 
+#if defined(K3G_CUBIN_ONLY) && defined(K3G_FUSED_ENTRIES)
+// Module k3g_fused_situ, op rs_situ_rms (second launch; the first is the arrive barrier) of a manifest rewritten by
+// `patch_manifest.py --fuse`: kern_k3_situ_rms_bf16 with the latent rows pulled from every rank's partial buffer and
+// the item maxima for the following quantisation.  The tensor-parallel width is a build constant (K3G_NR).
+#ifndef K3G_NR
+#define K3G_NR 4
+#endif
+extern "C" __global__ void __launch_bounds__(128) kern_k3g_rs_situ_rms(const __nv_bfloat16* __restrict__ sp, __nv_bfloat16* __restrict__ act,
+                                                                      const __nv_bfloat16* __restrict__ partial,
+                                                                      const unsigned long long* __restrict__ partial_peer, int rank, int nranks,
+                                                                      const __nv_bfloat16* __restrict__ gam, __nv_bfloat16* __restrict__ ln, int n,
+                                                                      int B, int h, int L, float* __restrict__ item_max) {
+  if (nranks != K3G_NR) return;
+  __shared__ float sm[kRmsRows * 32];
+  const unsigned nv = (unsigned)n >> 3, total = (unsigned)B * nv;
+  const unsigned SC = (total + kSituVec * 128u - 1) / (kSituVec * 128u);
+  const unsigned q = blockIdx.x >> 1, pull_blocks = (gridDim.x + 1) >> 1;
+  if ((blockIdx.x & 1) == 0) {
+    const uint4* ring[K3G_NR];
+    rs_bases<K3G_NR, K3G_NR - 1, 0>(partial, partial_peer, (long long)rank * L * h, rank, ring);
+    for (unsigned r = q; r < (unsigned)L; r += pull_blocks) rms_row_pull<K3G_NR>(ring, gam, ln, h, (int)r, sm);
+  } else {
+    const unsigned situ_blocks = gridDim.x - pull_blocks;
+    for (unsigned c = q; c < SC; c += situ_blocks) situ_item(sp, act, nv, total, c, item_max, reinterpret_cast<unsigned*>(sm));
+  }
+}
+#endif
+
 // ---- f32 landings (module k3_land) -----------------------------------------------------------------
 // row / column of flat index i over rows of `width` items: 32-bit division whenever the index fits
 __device__ __forceinline__ void split_index(long long i, int width, long long& row, int& col) {

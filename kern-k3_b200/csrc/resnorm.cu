@@ -557,6 +557,35 @@ extern "C" __global__ void __launch_bounds__(128, 4) kern_k3_attnres_rms_push(
 }
 #endif
 
+#if defined(K3G_CUBIN_ONLY) && defined(K3G_FUSED_ENTRIES)
+// Module k3g_fused_residual: the fusions beyond the reference's call list as cubin entries with fixed parameter lists,
+// for a manifest rewritten by `patch_manifest.py --fuse`.  The tensor-parallel width is a build constant (K3G_NR), as in
+// the reference's own collectives (source/k3_reducescatter_pull_nr4.cu:135).
+#ifndef K3G_NR
+#define K3G_NR 4
+#endif
+// op attnres_rms_push_add2_amax: kern_k3_attnres_rms_push's 17 parameters, then the gathered row maxima and their peer table
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3g_attnres_rms_push_amax(
+    __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw, const __nv_bfloat16* __restrict__ gamma,
+    __nv_bfloat16* __restrict__ normed_all, const unsigned long long* __restrict__ dst_peer, int nb, int snapshot, int B, int rank,
+    int nranks, const float* __restrict__ sw_mlp, float* __restrict__ stats, const __nv_bfloat16* __restrict__ p1,
+    const __nv_bfloat16* __restrict__ p2, const __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ hidden, int two,
+    float* __restrict__ rowmax_all, const unsigned long long* __restrict__ rowmax_peer) {
+  attnres_rms_push_body<K3G_RES_VPT>(blocks, sw, gamma, normed_all, dst_peer, nb, snapshot, B, rank, nranks, sw_mlp, stats, p1, p2, prefix2,
+                                     hidden, two, K3G_RES_EPS, rowmax_all, rowmax_peer);
+}
+// op rs_land_add_attnres_rms (second launch; the first is the arrive barrier): the pull reduce-scatter inside the landing
+extern "C" __global__ void __launch_bounds__(128, 4) kern_k3g_rs_land_add_attnres_rms(
+    const __nv_bfloat16* __restrict__ partial, const unsigned long long* __restrict__ partial_peer, int rank, int nranks,
+    const __nv_bfloat16* __restrict__ prefix, const __nv_bfloat16* __restrict__ blocks, const float* __restrict__ sw,
+    const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ prefix2, __nv_bfloat16* __restrict__ normed, int nb, int snapshot,
+    int B, const float* __restrict__ stats, int nb_stats, float* __restrict__ rowmax) {
+  if (nranks != K3G_NR) return;                        // one module per world size, as the reference's pull kernel
+  land_add_attnres_rms_body<K3G_RES_VPT, true, K3G_NR>(partial, prefix, blocks, sw, gamma, prefix2, normed, nb, snapshot, B, K3G_RES_EPS, stats,
+                                                       nb_stats, rowmax, partial_peer, rank);
+}
+#endif
+
 #if defined(K3G_CUBIN_ONLY)
 // one landing dtype per module, as in the reference (-DLAND_BF16 selects bf16)
 #ifdef LAND_BF16

@@ -86,3 +86,45 @@ def test_patch_reference_default_manifest(pm):
     for _, entry, mod in s["moved"]:
         blob = open(os.path.join(pm.CUBIN_DIR, mod[len("b200/"):] + ".cubin"), "rb").read()
         assert entry.encode() + b"\0" in blob
+
+
+@pytest.mark.skipif(not os.path.exists(REF_MANIFEST), reason="reference checkout not present")
+def test_fuse_reference_default_manifest(pm):
+    """--fuse on the reference's default manifest: 185 calls and 437 launches fewer (per fused layer: the two
+    reduce-scatter calls folded into their consumers, three amax launches dropped), every rewritten call matches its op
+    record, the new entries exist in the cubins, nothing but the glue calls moves, and a second run changes nothing."""
+    m = json.load(open(REF_MANIFEST))
+    ref_calls = copy.deepcopy(m["programs"]["prefill"]["calls"])
+    assert not pm.patch(m)["missing"]
+    launches_before = sum(len(m["ops"][c["op"]]["impl"]["launches"]) for c in m["programs"]["prefill"]["calls"])
+    f = pm.fuse(m)
+    calls = m["programs"]["prefill"]["calls"]
+    assert f["launches_before"] == launches_before == 3455 and len(ref_calls) == 2923
+    assert f["layers_res_mlp"] == 93 and f["layers_shared_situ"] == 92 and f["layers_normed_quant"] == 92 and f["layers_qkvg_quant"] == 68
+    assert len(calls) == len(ref_calls) - 93 - 92
+    assert f["launches_after"] == launches_before - 2 * 93 - 2 * 92 - 68 + 93 + 92 - 92 - 92 == 3018
+    labels = [c["label"] for c in calls]
+    assert not any(l.endswith((".reduce_attn", ".scatter_moe")) for l in labels)
+    kept = [c for c in ref_calls if not c["label"].endswith((".reduce_attn", ".scatter_moe"))]
+    assert labels == [c["label"] for c in kept]                                              # order and everything else untouched
+    changed = {"attnres_rms_push_add2_amax", "quant_fp8_apply", "rs_land_add_attnres_rms", "rs_situ_rms"}
+    for new, old in zip(calls, kept):
+        if new["op"] not in changed:
+            assert new == old, new["label"]
+        assert len(new["args"]) == len(m["ops"][new["op"]]["params"])
+    for op in changed:
+        for l in m["ops"][op]["impl"]["launches"]:
+            assert l["module"].startswith("b200/") and l["module"] in m["modules"]
+            blob = open(os.path.join(pm.CUBIN_DIR, l["module"][len("b200/"):] + ".cubin"), "rb").read()
+            assert l["entry"].encode() + b"\0" in blob, l["entry"]
+            assert len(l["args"]) == len(l["params"])
+    for name in ("rowmax_all", "rowmax_all_peer", "rowmax", "item_max"):
+        assert name in m["buffers"]
+    assert m["buffers"]["rowmax_all"]["export"] is True and m["buffers"]["rowmax_all_peer"]["of"] == "rowmax_all"
+    # the landing keeps its statistics hand-off: layers whose landing read attn_stats still do, with the same count
+    for new, old in zip(calls, kept):
+        if new["op"] == "rs_land_add_attnres_rms" and len(old["args"]) == 12:
+            assert new["args"][15:17] == old["args"][10:12]
+    again = copy.deepcopy(m)
+    f2 = pm.fuse(again)
+    assert again == m and f2["launches_after"] == f["launches_after"]

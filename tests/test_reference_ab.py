@@ -137,3 +137,71 @@ def test_router_against_the_reference_kernel_at_16384_rows(k3g, dev):
     assert differing <= B // 1000                                   # ~1e-5 per pick expected; 0.1 % of rows is already a bug
     same = (idx == ref_idx).all(axis=1)
     assert np.allclose(w[same], ref_w[same], rtol=2e-6, atol=0)
+
+
+def test_fused_cubin_entries_equal_the_c_abi(k3g, dev):
+    """The entries `patch_manifest.py --fuse` points the fused call list at (modules k3g_fused_residual / k3g_fused_situ,
+    built for a tensor-parallel group of 4) launched with the manifest's geometry on four emulated ranks: their outputs
+    equal the C-ABI entry points' byte for byte (those are checked against the oracle elsewhere)."""
+    import torch
+    import refcubin
+    from util import normal_bf16, rng, to_dev, to_dev_bf16
+    W, B, H, nb = 4, 21, 7168, 4
+    g = rng(4242)
+    bf = torch.bfloat16
+    z = lambda *shape, dt=bf: torch.zeros(shape, dtype=dt, device=dev)
+    tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    s = k3g.current_stream()
+    # ---- push with row maxima (rank 1 of 4) --------------------------------------------------------------------------
+    blocks_h = normal_bf16(g, (B, 8, H)); sw = to_dev((g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32), dev)
+    sw_mlp = to_dev((g.standard_normal(H, dtype=np.float32) * 0.05).astype(np.float32), dev); gamma = to_dev_bf16(normal_bf16(g, (H,), 1.0, 0.02), dev)
+    p1, p2, prefix2 = (to_dev_bf16(normal_bf16(g, (B, H), std=0.5), dev) for _ in range(3))
+    res = []
+    for use_cubin in (False, True):
+        blocks = to_dev_bf16(blocks_h, dev)
+        alls = [z(W * B, H) for _ in range(W)]; maxes = [z(W * B, dt=torch.float32) for _ in range(W)]
+        hidden, stats = z(B, H), z(B, 8, 2, dt=torch.float32)
+        if use_cubin:
+            fn = refcubin.load_external(os.path.join(OURS, "k3g_fused_residual.cubin"), "kern_k3g_attnres_rms_push_amax")
+            refcubin.launch(fn, B, 128, [blocks, sw, gamma, alls[1], tab(alls), nb, 1, B, 1, W, sw_mlp, stats, p1, p2, prefix2, hidden, 1, maxes[1], tab(maxes)])
+        else:
+            k3g.call("k3g_attnres_rms_push_amax", blocks, sw, gamma, alls[1], tab(alls), nb, 1, B, 1, W, sw_mlp, stats, p1, p2, prefix2, hidden, 1, H,
+                     1e-5, maxes[1], tab(maxes), s)
+        torch.cuda.synchronize()
+        res.append([blocks, hidden, stats] + alls + maxes)
+    for a, b in zip(*res):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    assert res[0][3].abs().sum() > 0 and res[0][7][B:2 * B].min() > 0          # a peer's copy and the pushed maxima are populated
+    # ---- reduce-scatter inside the landing (rank 2 of 4) ---------------------------------------------------------------
+    parts = [to_dev_bf16(normal_bf16(g, (W * B, H), std=0.2), dev) for _ in range(W)]
+    stats = res[0][2]; blocks = res[0][0]; prefix = res[0][1]
+    out = []
+    for use_cubin in (False, True):
+        pre2, nrm, rowmax = z(B, H), z(B, H), z(B, dt=torch.float32)
+        if use_cubin:
+            fn = refcubin.load_external(os.path.join(OURS, "k3g_fused_residual.cubin"), "kern_k3g_rs_land_add_attnres_rms")
+            refcubin.launch(fn, B, 128, [parts[2], tab(parts), 2, W, prefix, blocks, sw_mlp, gamma, pre2, nrm, nb, 0, B, stats, nb, rowmax])
+        else:
+            k3g.call("k3g_rs_land_add_attnres_rms", parts[2], tab(parts), 2, W, prefix, blocks, sw_mlp, gamma, pre2, nrm, nb, 0, B, H, 1e-5, stats, nb, rowmax, s)
+        torch.cuda.synchronize()
+        out.append([pre2, nrm, rowmax])
+    for a, b in zip(*out):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    assert out[0][1].abs().sum() > 0
+    # ---- reduce-scatter inside the latent norm + SiTU landing (rank 3 of 4), manifest grid -----------------------------
+    n, h = 6144, 3584
+    lat_parts = [to_dev_bf16(normal_bf16(g, (W * B, h), std=0.3), dev) for _ in range(W)]
+    sp = to_dev_bf16(normal_bf16(g, (B, 2 * n), std=2.0), dev); gam = to_dev_bf16(normal_bf16(g, (h,), 1.0, 0.02), dev)
+    out = []
+    for use_cubin in (False, True):
+        act, ln, item_max = z(B, n), z(B, h), z((B * n + 4095) // 4096, dt=torch.float32)
+        if use_cubin:
+            fn = refcubin.load_external(os.path.join(OURS, "k3g_fused_situ.cubin"), "kern_k3g_rs_situ_rms")
+            refcubin.launch(fn, ((B * 3 + 1) // 2) * 2, 128, [sp, act, lat_parts[3], tab(lat_parts), 3, W, gam, ln, n, B, h, B, item_max])
+        else:
+            k3g.call("k3g_rs_situ_rms", sp, act, lat_parts[3], tab(lat_parts), 3, W, gam, ln, n, B, h, B, item_max, s)
+        torch.cuda.synchronize()
+        out.append([act, ln, item_max])
+    for a, b in zip(*out):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    assert out[0][0].abs().sum() > 0 and out[0][1].abs().sum() > 0

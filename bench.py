@@ -201,6 +201,7 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
 
     def add(name, fn, nbytes):
         if only and only not in name:
+            fn()                                   # later ops consume this one's outputs (router -> tables -> gather): run it once, untimed
             return
         us = time_us(fn, iters)
         out.append({"op": name, "us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_measured": round(nbytes / us / 1e3 / peak_gbs, 3),
@@ -232,16 +233,24 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     tot = torch.zeros(1, dtype=torch.int32, device=dev); rm = torch.zeros(nct * tile, dtype=torch.int32, device=dev)
     e2p = torch.zeros((T, 8), dtype=torch.int32, device=dev)
 
-    def route():
+    def route3():
         k3g.call("k3g_moe_route_count", idx, T, 0, NE, 8, 1, 0, bc, s)
         k3g.call("k3g_moe_route_tables", bc, blocks, NE, tile, bo, cb, cl, nne, tot, rm, s)
         k3g.call("k3g_moe_route_scatter", idx, bo, T, 0, NE, 8, 1, 0, rm, e2p, s)
-    route()
-    add("config2 route count+tables+scatter (3 launches), EP=1: 224 local experts", route, T * 8 * 4 * 4)
+
+    def route2():
+        k3g.call("k3g_moe_route_count", idx, T, 0, NE, 8, 1, 0, bc, s)
+        k3g.call("k3g_moe_route_tables_scatter", idx, bc, T, 0, NE, 8, 1, 0, tile, bo, cb, cl, nne, tot, rm, e2p, s)
+    add("config2 route count + tables + scatter (3 launches), EP=1: 224 local experts", route3, T * 8 * 4 * 4)
+    add("config2 route count + (tables in scatter) (2 launches), EP=1: 224 local experts", route2, T * 8 * 4 * 4)
     torch.cuda.synchronize()
     rows = int(tot.item())             # tile-padded permuted rows (padding rows route token 0)
     pq = torch.empty((rows, H), dtype=torch.uint8, device=dev); psf = torch.empty((rows, H // 32), dtype=torch.uint8, device=dev)
-    add("config2 permute_gather %dx7168 mxfp8" % rows, lambda: k3g.call("k3g_permute_gather", q8, sf8, rm, rows, H, pq, psf, s), (T + rows) * (H + H // 32))
+    add("config2 permute_gather %dx7168 mxfp8 (row -> token through route_map: every token row is fetched 8 times)" % rows,
+        lambda: k3g.call("k3g_permute_gather", q8, sf8, rm, rows, H, pq, psf, s), (T + rows) * (H + H // 32))
+    tq = torch.tensor([pq.data_ptr()], dtype=torch.int64, device=dev); tsf = torch.tensor([psf.data_ptr()], dtype=torch.int64, device=dev)
+    add("config2 permute_dispatch EP=1 %d live rows x 7168 mxfp8 (token -> rows through exp2perm: every token row is read once)" % (T * 8),
+        lambda: k3g.call("k3g_permute_dispatch", q8, sf8, idx, e2p, bo, T, 0, 8, H, NE, 1, 0, tq, tsf, s), (T + T * 8) * (H + H // 32))
     del pq, psf
     fc2 = torch.randn((rows, H), generator=g, device=dev, dtype=torch.bfloat16)
     add("config2 finalize_residual 16384x8x7168", lambda: k3g.call("k3g_finalize_residual", fc2, e2p, wts, res, o16, T, H, 8, s), T * 8 * H * 2 + 4 * E)

@@ -434,6 +434,12 @@ __global__ void __launch_bounds__(512) route_tables_scatter_wide_kernel(const in
 // bytes leave as 16-byte stores.  Destination of slot k: owner = rank that holds expert ids[t, k]; row = exp2perm[t, k] of
 // the all-owner tables minus the owner's first row (blockoff[owner * per], block 0 of the offsets table).
 // Plain stores only: no TMA, no multicast, nothing waits.  The caller follows with a barrier (k3g_rs_arrive).
+#ifndef K3G_DISPATCH_MINB
+#define K3G_DISPATCH_MINB 2
+#endif
+#ifndef K3G_DISPATCH_VPL
+#define K3G_DISPATCH_VPL 8      /* vectors in flight per lane */
+#endif
 template <int VB>
 __device__ __forceinline__ void permute_dispatch_body(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
                                                       const int* __restrict__ ids, const int* __restrict__ exp2perm, int B,
@@ -458,11 +464,11 @@ __device__ __forceinline__ void permute_dispatch_body(const uint8_t* __restrict_
     const unsigned long long dsf = __shfl_sync(0xffffffffu, my_sf, owner < 0 ? 0 : owner);
     const long long local_row = row >= 0 ? (long long)(row - base) : -1;
     const uint8_t* src = q + b * cols;
-    for (int c0 = 0; c0 < qv; c0 += 8 * 32) {             // warp-uniform trip count: the shuffles below need every lane
+    for (int c0 = 0; c0 < qv; c0 += K3G_DISPATCH_VPL * 32) {             // warp-uniform trip count: the shuffles below need every lane
       const int v0 = c0 + lane;
-      Vec x[8];
+      Vec x[K3G_DISPATCH_VPL];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < K3G_DISPATCH_VPL; ++u)
         if (v0 + 32 * u < qv) x[u] = ld_stream_vec<VB>(src + (size_t)(v0 + 32 * u) * VB);
       for (int k = 0; k < topk; ++k) {
         const long long r = __shfl_sync(0xffffffffu, local_row, k);
@@ -470,7 +476,7 @@ __device__ __forceinline__ void permute_dispatch_body(const uint8_t* __restrict_
         if (r < 0) continue;
         uint8_t* dst = reinterpret_cast<uint8_t*>(d + (unsigned long long)r * cols);
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < K3G_DISPATCH_VPL; ++u)
           if (v0 + 32 * u < qv) st_stream_vec<VB>(dst + (size_t)(v0 + 32 * u) * VB, x[u]);
       }
     }
@@ -493,7 +499,7 @@ __device__ __forceinline__ void permute_dispatch_body(const uint8_t* __restrict_
   }
 }
 
-__global__ void __launch_bounds__(256) permute_dispatch_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+__global__ void __launch_bounds__(256, K3G_DISPATCH_MINB) permute_dispatch_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
                                                                const int* __restrict__ ids, const int* __restrict__ exp2perm,
                                                                const int* __restrict__ blockoff, int B, long long token_begin, int topk,
                                                                int cols, int per, int ep_ranks, int strided,

@@ -373,9 +373,10 @@ int k3g_sigmoid_mul(void* out, const void* attn, const void* gate, int tokens, i
                     int gate_hstride, void* stream);
 
 /* kern_k3_span_state, source/k3_span_state.cu:19 (ops span_state_load / span_state_store): copy of the
- * sequence's [24][128][128] f32 KDA state between its state line and a flat buffer. */
+ * sequence's [heads][128][128] f32 KDA state between its state line and a flat buffer.  The reference fixes
+ * heads = 24 when it builds the module; here it is an argument (the drop-in cubin keeps the reference's list). */
 int k3g_span_state(void* kda_base, const void* line_index, long long line_bytes, const void* span_at, void* buf, int to_line,
-                   void* stream);
+                   int heads, void* stream);
 
 /* kern_k3_latent_gather, source/k3_mla_v2.cu:22 (op latent_gather): cached latent rows [n, 576] laid
  * contiguous from 64-row pages; rows >= lens[0] are zero. */

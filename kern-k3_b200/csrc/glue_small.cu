@@ -561,13 +561,15 @@ K3G_API int k3g_sigmoid_mul(void* out, const void* attn, const void* gate, int t
   return k3g_launch_status();
 }
 
-// heads is a build constant of the reference module (HEADS); the library entry serves the 24-head build.
+// The reference fixes the head count when the module is built (HEADS, = gridDim.x of its launch); the kernel here takes it
+// from the grid, so the library entry serves any count: `heads` heads of [128][128] f32 = heads * 64 KB per direction.
 K3G_API int k3g_span_state(void* kda_base, const void* line_index, long long line_bytes, const void* span_at, void* buf, int to_line,
-                           void* stream) {
+                           int heads, void* stream) {
   K3G_REQUIRE_PTR(kda_base); K3G_REQUIRE_PTR(line_index); K3G_REQUIRE_PTR(span_at); K3G_REQUIRE_PTR(buf);
   K3G_REQUIRE_ALIGNED(kda_base); K3G_REQUIRE_ALIGNED(buf); K3G_REQUIRE(line_bytes % 16 == 0, K3G_EALIGN);
-  kern_k3_span_state<<<dim3(HEADS, 32, 1), 128, 0, k3g_stream(stream)>>>(kda_base, (const int*)line_index, line_bytes, (const int*)span_at,
-                                                                       (float*)buf, to_line);
+  K3G_REQUIRE(heads > 0 && heads <= 65535 && (long long)heads * 65536 <= line_bytes, K3G_ESHAPE);
+  kern_k3_span_state<<<dim3((unsigned)heads, 32, 1), 128, 0, k3g_stream(stream)>>>(kda_base, (const int*)line_index, line_bytes, (const int*)span_at,
+                                                                                 (float*)buf, to_line);
   return k3g_launch_status();
 }
 

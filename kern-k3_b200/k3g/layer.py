@@ -128,8 +128,8 @@ class LayerGlue:
                       "k3g_span_gather", self.kda_partial, 4 * inner, self.cw, 0, self.win, self.wsm, self.span_q, self.span_k, self.span_v, self.beta,
                       self.flow, heads, 0, T, 0, s())),
                   ("span_state_in + span_state_out (2 copies)", lambda: (
-                      call("k3g_span_state", self.state_lines, self.line_index, self.state_lines.numel(), self.span_at, self.state_buf, 0, s()),
-                      call("k3g_span_state", self.state_lines, self.line_index, self.state_lines.numel(), self.span_at, self.state_buf, 1, s()))),
+                      call("k3g_span_state", self.state_lines, self.line_index, self.state_lines.numel(), self.span_at, self.state_buf, 0, heads, s()),
+                      call("k3g_span_state", self.state_lines, self.line_index, self.state_lines.numel(), self.span_at, self.state_buf, 1, heads, s()))),
                   ("span_out_gate", lambda: call("k3g_kda_out_gate", self.span_v, self.kda_partial, 4 * inner, 3 * inner, self.gamma_o, self.gated, None,
                                                  None, heads, 0, T, 1e-5, s()))]
         else:

@@ -81,23 +81,27 @@ def test_sigmoid_mul(k3g, dev, tokens, heads, hd):
     assert d.max() <= 1 and (d > 0).mean() < 5e-3
 
 
-def test_span_state_roundtrip_and_latent_gather(k3g, dev):
+@pytest.mark.parametrize("heads", [24, 12, 96])
+def test_span_state_roundtrip_and_latent_gather(k3g, dev, heads):
     import torch
     g = rng(3)
-    rec_floats = 24 * 128 * 128
-    line_bytes = rec_floats * 4 + 3 * 3 * 3072 * 2
+    rec_floats = heads * 128 * 128
+    line_bytes = rec_floats * 4 + 3 * 3 * heads * 128 * 2
     lines = torch.from_numpy(g.integers(0, 256, 3 * line_bytes, dtype=np.uint8)).to(dev)
     before = lines.clone()
     line_index = torch.tensor([2, 0, 1], dtype=torch.int32, device=dev); span_at = torch.tensor([1], dtype=torch.int32, device=dev)   # row 1 -> line 0
-    buf = torch.zeros(rec_floats, dtype=torch.float32, device=dev)
+    guard = 4096                                                  # the copy must stop after `heads` heads
+    buf = torch.zeros(rec_floats + guard, dtype=torch.float32, device=dev)
     s = k3g.current_stream()
-    k3g.call("k3g_span_state", lines, line_index, line_bytes, span_at, buf, 0, s)
+    k3g.call("k3g_span_state", lines, line_index, line_bytes, span_at, buf, 0, heads, s)
     torch.cuda.synchronize()
-    assert torch.equal(buf.view(torch.uint8), before[:rec_floats * 4]) and torch.equal(lines, before)
+    assert torch.equal(buf[:rec_floats].view(torch.uint8), before[:rec_floats * 4]) and torch.equal(lines, before)
+    assert not buf[rec_floats:].any()
     buf += 1.0
-    k3g.call("k3g_span_state", lines, line_index, line_bytes, span_at, buf, 1, s)
+    k3g.call("k3g_span_state", lines, line_index, line_bytes, span_at, buf, 1, heads, s)
     torch.cuda.synchronize()
-    assert torch.equal(lines[:rec_floats * 4], buf.view(torch.uint8)) and torch.equal(lines[rec_floats * 4:], before[rec_floats * 4:])
+    assert torch.equal(lines[:rec_floats * 4], buf[:rec_floats].view(torch.uint8)) and torch.equal(lines[rec_floats * 4:], before[rec_floats * 4:])
+    assert k3g.raw("k3g_span_state", lines, line_index, rec_floats * 4 - 16, span_at, buf, 0, heads, s) == -2      # the line cannot hold that many heads
     # latent gather: 3 pages of 64 rows in shuffled order, 150 cached rows, 200 output rows
     page_stride = 64 * 576 * 2
     slab = normal_bf16(g, (4 * page_stride,))

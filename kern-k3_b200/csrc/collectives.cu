@@ -205,20 +205,28 @@ __global__ void __launch_bounds__(1024) rs_pull_kernel(const __nv_bfloat16* src,
 }
 
 // ---- all-gather, push form ---------------------------------------------------------------------
+template <int INFLIGHT>
 __device__ __forceinline__ void push_span(const unsigned char* __restrict__ s, unsigned char* __restrict__ d,
                                           const unsigned long long* __restrict__ p, long long nb, int rank, int nr, long long tid,
                                           long long stride) {
   // 32 bytes per access when the span allows it (every rank's copy is then assumed 32-byte aligned like this one)
   if ((nb & 31) == 0 && ((reinterpret_cast<unsigned long long>(s) | reinterpret_cast<unsigned long long>(d)) & 31ull) == 0) {
     const long long n32 = nb >> 5;
-    for (long long i = tid; i < n32; i += stride) {
-      const V16 val = ld_stream32(s + (i << 5));
-      const long long eb = (long long)rank * nb + (i << 5);
-      *reinterpret_cast<uint4*>(d + eb) = make_uint4(val.w[0], val.w[1], val.w[2], val.w[3]);          // own copy: keep in L2 for the consumer
-      *reinterpret_cast<uint4*>(d + eb + 16) = make_uint4(val.w[4], val.w[5], val.w[6], val.w[7]);
+    for (long long i0 = tid; i0 < n32; i0 += INFLIGHT * stride) {   // INFLIGHT vectors loaded before the first store: INFLIGHT x (nr - 1) peer stores in flight
+      V16 val[INFLIGHT];
 #pragma unroll
-      for (int q = 0; q < K3G_MAX_RANKS; ++q)
-        if (q < nr && q != rank) st_stream32(reinterpret_cast<unsigned char*>(p[q]) + eb, val);
+      for (int u = 0; u < INFLIGHT; ++u)
+        if (i0 + u * stride < n32) val[u] = ld_stream32(s + ((i0 + u * stride) << 5));
+#pragma unroll
+      for (int u = 0; u < INFLIGHT; ++u) {
+        if (i0 + u * stride >= n32) continue;
+        const long long eb = (long long)rank * nb + ((i0 + u * stride) << 5);
+        *reinterpret_cast<uint4*>(d + eb) = make_uint4(val[u].w[0], val[u].w[1], val[u].w[2], val[u].w[3]);          // own copy: keep in L2 for the consumer
+        *reinterpret_cast<uint4*>(d + eb + 16) = make_uint4(val[u].w[4], val[u].w[5], val[u].w[6], val[u].w[7]);
+#pragma unroll
+        for (int q = 0; q < K3G_MAX_RANKS; ++q)
+          if (q < nr && q != rank) st_stream32(reinterpret_cast<unsigned char*>(p[q]) + eb, val[u]);
+      }
     }
     return;
   }
@@ -233,6 +241,7 @@ __device__ __forceinline__ void push_span(const unsigned char* __restrict__ s, u
   }
 }
 
+template <int INFLIGHT>
 __device__ __forceinline__ void allgather4_body(const unsigned char* s0, unsigned char* d0, const unsigned long long* p0, long long n0,
                                                 const unsigned char* s1, unsigned char* d1, const unsigned long long* p1, long long n1,
                                                 const unsigned char* s2, unsigned char* d2, const unsigned long long* p2, long long n2,
@@ -242,10 +251,10 @@ __device__ __forceinline__ void allgather4_body(const unsigned char* s0, unsigne
   const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  if (n0 > 0) push_span(s0, d0, p0, n0, rank, nr, tid, stride);
-  if (n1 > 0) push_span(s1, d1, p1, n1, rank, nr, tid, stride);
-  if (n2 > 0) push_span(s2, d2, p2, n2, rank, nr, tid, stride);
-  if (n3 > 0) push_span(s3, d3, p3, n3, rank, nr, tid, stride);
+  if (n0 > 0) push_span<INFLIGHT>(s0, d0, p0, n0, rank, nr, tid, stride);
+  if (n1 > 0) push_span<INFLIGHT>(s1, d1, p1, n1, rank, nr, tid, stride);
+  if (n2 > 0) push_span<INFLIGHT>(s2, d2, p2, n2, rank, nr, tid, stride);
+  if (n3 > 0) push_span<INFLIGHT>(s3, d3, p3, n3, rank, nr, tid, stride);
   block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status, arrivals);
 }
 
@@ -406,14 +415,15 @@ __global__ void __launch_bounds__(32) epoch_arrive_kernel(unsigned long long* fl
   __syncwarp();
   arrive_and_wait(flags, flags_peer, units, slot, nranks, timeout_ns, status ? status : g_wait_status);
 }
-__global__ void __launch_bounds__(1024) allgather4_kernel(const unsigned char* s0, unsigned char* d0, const unsigned long long* p0, long long n0,
+// C-ABI launch: 256-thread blocks (room for four 32-byte vectors in flight per thread), several resident per SM
+__global__ void __launch_bounds__(256) allgather4_kernel(const unsigned char* s0, unsigned char* d0, const unsigned long long* p0, long long n0,
                                                           const unsigned char* s1, unsigned char* d1, const unsigned long long* p1, long long n1,
                                                           const unsigned char* s2, unsigned char* d2, const unsigned long long* p2, long long n2,
                                                           const unsigned char* s3, unsigned char* d3, const unsigned long long* p3, long long n3,
                                                           unsigned long long* flags, const unsigned long long* flags_peer, int slot, int rank,
                                                           int nranks, long long timeout_ns, unsigned* status, unsigned arrivals) {
-  allgather4_body(s0, d0, p0, n0, s1, d1, p1, n1, s2, d2, p2, n2, s3, d3, p3, n3, flags, flags_peer, slot, rank, nranks, timeout_ns,
-                  status ? status : g_wait_status, arrivals);
+  allgather4_body<4>(s0, d0, p0, n0, s1, d1, p1, n1, s2, d2, p2, n2, s3, d3, p3, n3, flags, flags_peer, slot, rank, nranks, timeout_ns,
+                     status ? status : g_wait_status, arrivals);
 }
 
 // MXFP8 quantisation of this rank's latent rows written straight into every rank's gathered buffers, then two plain
@@ -457,8 +467,8 @@ __global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bf
       }
     }
   }
-  if (n2 > 0) push_span(s2, d2, p2, n2, rank, nr, tid, stride);
-  if (n3 > 0) push_span(s3, d3, p3, n3, rank, nr, tid, stride);
+  if (n2 > 0) push_span<1>(s2, d2, p2, n2, rank, nr, tid, stride);
+  if (n3 > 0) push_span<1>(s3, d3, p3, n3, rank, nr, tid, stride);
   block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status ? status : g_wait_status, arrivals);
 }
 
@@ -505,14 +515,14 @@ extern "C" __global__ void __launch_bounds__(1024) kern_k3_allgather4_push(
     const unsigned char* __restrict__ s2, unsigned char* __restrict__ d2, const unsigned long long* __restrict__ p2, long long n2,
     const unsigned char* __restrict__ s3, unsigned char* __restrict__ d3, const unsigned long long* __restrict__ p3, long long n3,
     unsigned long long* __restrict__ flags, const unsigned long long* __restrict__ flags_peer, int slot, int rank, int nranks) {
-  allgather4_body(s0, d0, p0, n0, s1, d1, p1, n1, s2, d2, p2, n2, s3, d3, p3, n3, flags, flags_peer, slot, rank, nranks, K3G_SPIN_NS,
-                  g_wait_status, gridDim.x);
+  allgather4_body<1>(s0, d0, p0, n0, s1, d1, p1, n1, s2, d2, p2, n2, s3, d3, p3, n3, flags, flags_peer, slot, rank, nranks, K3G_SPIN_NS,
+                     g_wait_status, gridDim.x);
 }
 
 #ifndef K3G_CUBIN_ONLY
-// Grid of a push kernel launched through the C ABI: at most two 1024-thread blocks per SM of a 148-SM part, all
-// resident at once (the blocks stride over the payload), instead of `units` short-lived blocks; the launch still
-// publishes `units` arrivals, so the counter protocol is the reference's.
+// Grid of a push kernel launched through the C ABI: a few resident blocks per SM of a 148-SM part that stride over
+// the payload (two 1024-thread blocks, or four 256-thread ones for the four-payload all-gather), instead of `units`
+// short-lived blocks; the launch still publishes `units` arrivals, so the counter protocol is the reference's.
 static inline unsigned push_grid(int units) { return (unsigned)(units < 296 ? units : 296); }
 
 static int check_world(int rank, int nranks) {
@@ -590,7 +600,7 @@ K3G_API int k3g_allgather4_push(const void* s0, void* d0, const void* p0, long l
     K3G_REQUIRE(nn[i] >= 0 && nn[i] % 16 == 0, K3G_ESHAPE);
     if (nn[i] > 0) { K3G_REQUIRE_PTR(ss[i]); K3G_REQUIRE_PTR(dd[i]); K3G_REQUIRE_PTR(pp[i]); K3G_REQUIRE_ALIGNED(ss[i]); K3G_REQUIRE_ALIGNED(dd[i]); }
   }
-  allgather4_kernel<<<push_grid(units), 1024, 0, k3g_stream(stream)>>>(
+  allgather4_kernel<<<push_grid(units) * 2, 256, 0, k3g_stream(stream)>>>(
       (const unsigned char*)s0, (unsigned char*)d0, (const unsigned long long*)p0, n0, (const unsigned char*)s1, (unsigned char*)d1,
       (const unsigned long long*)p1, n1, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2,
       (const unsigned char*)s3, (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags,

@@ -448,21 +448,19 @@ __global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bf
     for (int j = 1; j < 4; ++j) am = max_bf16_bits(am, absmax8(v[j]));
     const int e = ue8m0_exp_from_bf16(am);
     const float sc = pow2_neg(e);
-    V8 o0, o1;
-    quant8(v[0], sc, o0.w[0], o0.w[1]);
-    quant8(v[1], sc, o0.w[2], o0.w[3]);
-    quant8(v[2], sc, o1.w[0], o1.w[1]);
-    quant8(v[3], sc, o1.w[2], o1.w[3]);
+    V16 o;                                                       // the group's 32 codes: one 32-byte store per rank (a full sector)
+    quant8(v[0], sc, o.w[0], o.w[1]);
+    quant8(v[1], sc, o.w[2], o.w[3]);
+    quant8(v[2], sc, o.w[4], o.w[5]);
+    quant8(v[3], sc, o.w[6], o.w[7]);
     const long long at = (long long)rank * ngroups + g;          // group index in the gathered buffers
-    st_plain(q_all + at * 32, o0);
-    st_plain(q_all + at * 32 + 16, o1);
+    *reinterpret_cast<uint4*>(q_all + at * 32) = make_uint4(o.w[0], o.w[1], o.w[2], o.w[3]);
+    *reinterpret_cast<uint4*>(q_all + at * 32 + 16) = make_uint4(o.w[4], o.w[5], o.w[6], o.w[7]);
     sf_all[at] = (unsigned char)(e + 127);
 #pragma unroll
     for (int q = 0; q < K3G_MAX_RANKS; ++q) {
       if (q < nr && q != rank) {
-        unsigned char* qd = reinterpret_cast<unsigned char*>(q_peer[q]);
-        st_stream(qd + at * 32, o0);
-        st_stream(qd + at * 32 + 16, o1);
+        st_stream32(reinterpret_cast<unsigned char*>(q_peer[q]) + at * 32, o);
         reinterpret_cast<unsigned char*>(sf_peer[q])[at] = (unsigned char)(e + 127);
       }
     }
@@ -618,7 +616,7 @@ K3G_API int k3g_moe_quant_allgather_push(const void* x, int rows, int cols, void
                                          long long timeout_us, void* status, void* stream) {
   K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(q_all); K3G_REQUIRE_PTR(q_peer); K3G_REQUIRE_PTR(sf_all); K3G_REQUIRE_PTR(sf_peer);
   K3G_REQUIRE_PTR(flags); K3G_REQUIRE_PTR(flags_peer);
-  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE_ALIGNED(q_all);
+  K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE((reinterpret_cast<uintptr_t>(q_all) & 31u) == 0, K3G_EALIGN);   // 32-byte code stores, every rank's buffer alike
   K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0 && nranks >= 1 && nranks <= K3G_MAX_RANKS && units > 0, K3G_ESHAPE);
   K3G_REQUIRE(rank >= 0 && rank < nranks && slot >= 1 && timeout_us > 0, K3G_ERANGE);
   const void* ss[2] = {s2, s3}; void* dd[2] = {d2, d3}; const void* pp[2] = {p2, p3};

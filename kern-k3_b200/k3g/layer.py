@@ -167,7 +167,7 @@ class LayerGlue:
             #  - the producers leave the maxima a per-tensor quantisation needs, so the three quantisations run
             #    their apply launch only (one pass over each tensor less);
             #  - the latent MXFP8 quantisation writes straight into every rank's gathered buffers (one launch with the
-            #    small all-gather);
+            #    small all-gather; a thread's 32 codes leave as one 32-byte store per rank, a full sector on the links);
             #  - the attention reduce-scatter is pulled inside the residual kernel that consumes it and the routed-latent
             #    reduce-scatter inside the latent norm, so their HBM / special-function work hides under the NVLink
             #    transfer and the reduce-scattered tensors are never written.
@@ -206,11 +206,6 @@ class LayerGlue:
                     "k3g_quant_fp8_apply", self.shared_act, self.shared_q, self.qscale[2:], self.item_max, self.item_max.numel(), B * SHARED, 2048,
                     s())),
             }
-            if W > 1:
-                # Over NVLink the quantise-into-gather launch loses: a lane's two 16-byte code stores leave half-filled
-                # 32-byte sectors per instruction, which is free in local HBM but doubles the packets on the links
-                # (157 us against 12 + 88 us for the two launches at world 4), so it is used at world 1 only.
-                del swap["moe_quant (MXFP8 latent)"], swap["gather_small (AG4 push + barrier)"]
             c = [swap.get(label, (label, fn)) for label, fn in c if swap.get(label, 0) is not None]
         return c
 

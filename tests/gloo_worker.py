@@ -1,5 +1,6 @@
 """World-2 gloo rank for tests/test_host_cpu.py: the peer-table exchange and the row sharding with a
-fake allocator (no CUDA), and the sharded oracle pipeline reassembled across ranks."""
+fake allocator (no CUDA), the sharded oracle pipeline reassembled across ranks, and the expert-parallel
+dispatch (who owns which expert, which row a routed token lands on) played through on the host."""
 import os
 import sys
 
@@ -77,6 +78,41 @@ def main():
     assert np.allclose(k3o.bf16_to_f32(full_delta), total, rtol=2e-2, atol=1e-2)
     _, q_ref, sf_ref, _ = k3o.resnorm_mxfp8(residual, full_delta, gamma, 1e-6, want_normed=False)
     assert np.array_equal(q_all, q_ref) and np.array_equal(sf_all, sf_ref)
+    # expert-parallel dispatch, EP = world: every rank routes its own tokens, the ids are gathered, every rank builds
+    # its OWN tables from the gathered ids (the oracle's per-rank tables), and each (token, slot) is delivered by the
+    # rank that holds the token to the rank that owns the expert, at the row the owner's tables assign.  What an owner
+    # receives must be exactly the live rows of the oracle's expert-sorted gather on the owner's route_map.
+    Tt, K, cols, tile = 96, 8, 64, 16
+    B, per = Tt // world, 224 // world
+    g = rng(30 + rank)
+    my_ids = np.stack([g.permutation(224)[:K] for _ in range(B)]).astype(np.int32)
+    my_q = g.integers(0, 256, (B, cols), dtype=np.uint8); my_sf = g.integers(0, 256, (B, cols // 32), dtype=np.uint8)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, (my_ids, my_q, my_sf))
+    ids = np.concatenate([e[0] for e in everyone]); q_all_rows = np.concatenate([e[1] for e in everyone]); sf_all_rows = np.concatenate([e[2] for e in everyone])
+    tabs = [k3o.moe_route(ids, o, per, world, 1, tile) for o in range(world)]     # every rank can build every owner's tables
+    outbox = [[] for _ in range(world)]
+    for b in range(B):
+        t = rank * B + b
+        for k in range(K):
+            o = int(ids[t, k]) % world                                # strided placement: owner = id % EP
+            row = int(tabs[o]["exp2perm"][t, k])
+            assert row >= 0 and all(int(tabs[x]["exp2perm"][t, k]) == -1 for x in range(world) if x != o)   # exactly one owner
+            outbox[o].append((row, my_q[b].copy(), my_sf[b].copy()))
+    inbox = [None] * world
+    dist.all_gather_object(inbox, outbox)
+    rows_mine = int(tabs[rank]["total_padded"][0])
+    got_q = np.full((rows_mine, cols), 0xEE, np.uint8); got_sf = np.full((rows_mine, cols // 32), 0xEE, np.uint8)
+    seen = np.zeros(rows_mine, bool)
+    for sender in range(world):
+        for row, qr, sr in inbox[sender][rank]:
+            assert not seen[row]                                      # every destination row is written once
+            seen[row] = True; got_q[row] = qr; got_sf[row] = sr
+    want_q, want_sf = k3o.permute_gather(q_all_rows, sf_all_rows, tabs[rank]["route_map"], rows_mine)
+    live = np.zeros(rows_mine, bool)
+    live[tabs[rank]["exp2perm"][tabs[rank]["exp2perm"] >= 0]] = True
+    assert np.array_equal(seen, live) and np.array_equal(got_q[live], want_q[live]) and np.array_equal(got_sf[live], want_sf[live])
+    assert sum(int(t["exp2perm"].__ge__(0).sum()) for t in tabs) == Tt * K          # the owners' live rows partition the routed slots
     dist.barrier()
     print("GLOO_OK rank %d" % rank)
     dist.destroy_process_group()

@@ -214,7 +214,15 @@ def bench_ops(k3g, dev, peak_gbs, iters=20, only=None):
     n16 = torch.empty_like(res)
     add("land_add_attnres_rms nb=0 16384x7168", lambda: k3g.call("k3g_land_add_attnres_rms", dl, 1, res, None, None, gm, o16, n16, 0, 0, T, H, 1e-5, s), 8 * E)
     add("land_add2 two 16384x7168", lambda: k3g.call("k3g_land_add2", dl, res, 1, o16, n16, 1, T, H, s), 8 * E)
-    del n16
+    # the attention-residual kernels as the layer program runs them (nb = 4 snapshot candidates, statistics hand-off), world 1
+    blocks8 = rnd(T, 8, H); sw_a = 0.05 * torch.randn(H, generator=g, device=dev); sw_m = 0.05 * torch.randn(H, generator=g, device=dev)
+    stats = torch.zeros((T, 8, 2), dtype=torch.float32, device=dev); nall = torch.empty_like(res); hid = torch.empty_like(res)
+    tabn = torch.tensor([nall.data_ptr()], dtype=torch.int64, device=dev)
+    add("res_in attnres_rms_push nb=4 16384x7168 (land_add2 + mix + RMSNorm + own slice; world 1)",
+        lambda: k3g.call("k3g_attnres_rms_push", blocks8, sw_a, gm, nall, tabn, 4, 0, T, 0, 1, sw_m, stats, dl, res, o16, hid, 1, H, 1e-5, s), (3 + 8 + 2) * 2 * E)
+    add("res_mlp land_add_attnres_rms_stats nb=4 16384x7168 (landing + mix + RMSNorm, statistics handed over)",
+        lambda: k3g.call("k3g_land_add_attnres_rms_stats", dl, 1, hid, blocks8, sw_m, gm, o16, n16, 4, 0, T, H, 1e-5, stats, 4, s), (4 + 4) * 2 * E)
+    del n16, blocks8, stats, nall, hid
     add("moe_quant 32768x3584", lambda: k3g.call("k3g_moe_quant", res, q8, sf8, 2 * T, 3584, 0, s), 3 * E + E // 32)
     part = torch.empty(2048, device=dev); sc = torch.empty(1, device=dev)
     add("quant_fp8_tensor 16384x7168", lambda: k3g.call("k3g_quant_fp8_tensor", res, q8, sc, part, E, 2048, s), 3 * E)

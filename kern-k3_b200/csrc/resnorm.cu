@@ -115,7 +115,10 @@ __device__ __forceinline__ void team_rms_store(const V8 (&x)[VPT], const __nv_bf
 //   consumer  (nb_stats > 0): takes (sq_c, dp_c) of candidates c < nb_stats from stats_in instead of
 //             reading those rows in pass 1.  Same summation order on both sides, so the value read
 //             is bit-identical to the value recomputed.
-template <int VPT>
+// PAIR: pass 1 takes the snapshot rows two at a time (both rows' loads in flight before the first fma chain) -- worth
+// its registers where pass 1 really reads the rows (the producer, the kernels without a hand-off), not in the consumer
+// that takes the statistics from the hand-off and skips those reads.
+template <int VPT, bool PAIR = false>
 __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat16* __restrict__ blk_row,
                                                  const float* __restrict__ sw, int nb, float eps, float* s_mix, int t,
                                                  const float* __restrict__ sw_other = nullptr, float* __restrict__ stats_out = nullptr,
@@ -125,14 +128,15 @@ __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat
   const int lane = t & 31, warp = t >> 5;
   const int ncand = nb + 1;
   float* s_oth = s_mix + (kNbMax + 1) * 2 * NW;       // dp' warp partials (producer only)
-  // pass 1: (sum x^2, sum x*sw) per candidate, candidate by candidate (same per-thread order)
-  for (int c = (nb_stats < nb ? nb_stats : nb); c < ncand; ++c) {
+  // pass 1: (sum x^2, sum x*sw) per candidate (same per-thread order).  Candidates go two at a time so that the loads
+  // of both rows are in flight before the first dependent fma chain starts: half as many memory round trips.
+  auto reduce_candidate = [&](const V8 (&cvs)[VPT], int c) {
     float sq = 0.f, dp = 0.f, dq = 0.f;
     const bool other = sw_other != nullptr && c < nb;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
       const int u = (t + v * kTeam) * 8;
-      const V8 cv = (c < nb) ? ld_plain(blk_row + (size_t)c * H + u) : x[v];
+      const V8 cv = cvs[v];
       const float4 a = __ldg((const float4*)(sw + u)), b = __ldg((const float4*)(sw + u + 4));
       const float s8[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
@@ -157,7 +161,24 @@ __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat
       dq = butterfly_sum<32>(dq);
       if (lane == 0) s_oth[c * NW + warp] = dq;
     }
+  };
+  int c = nb_stats < nb ? nb_stats : nb;
+  for (; PAIR && c + 1 < nb; c += 2) {                // two snapshot rows per round
+    V8 ca[VPT], cb[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) ca[v] = ld_plain(blk_row + (size_t)c * H + (t + v * kTeam) * 8);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) cb[v] = ld_plain(blk_row + (size_t)(c + 1) * H + (t + v * kTeam) * 8);
+    reduce_candidate(ca, c);
+    reduce_candidate(cb, c + 1);
   }
+  for (; c < nb; ++c) {                               // one row per round (all of them without PAIR, else the odd one left)
+    V8 ca[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) ca[v] = ld_plain(blk_row + (size_t)c * H + (t + v * kTeam) * 8);
+    reduce_candidate(ca, c);
+  }
+  reduce_candidate(x, nb);                            // the prefix candidate is the row held in registers
   __syncthreads();
   float sc = -3.0e38f;
   if (lane < ncand) {
@@ -189,27 +210,36 @@ __device__ __forceinline__ void team_attnres_mix(V8 (&x)[VPT], const __nv_bfloat
   const float pmine = __fdiv_rn(ex, den);
   const float pp = __shfl_sync(0xffffffffu, pmine, nb);
   __syncthreads();   // s_mix is reused by the next row of a persistent launch
-  // pass 2: mixed = bf16(p_prefix * x + sum_c p_c * cand_c), candidates ascending
+  // pass 2: mixed = bf16(p_prefix * x + sum_c p_c * cand_c), candidates ascending.  The accumulators of the whole
+  // row stay in registers and the candidate loop is the outer one, so all VPT loads of a candidate row are in flight
+  // together (they hit L2: pass 1 has just read the row); per element the order of operations is unchanged.
+  float acc[VPT][8];
 #pragma unroll
   for (int v = 0; v < VPT; ++v) {
-    const int u = (t + v * kTeam) * 8;
-    float acc[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      acc[2 * j] = __fmul_rn(pp, bf_lo(x[v].w[j]));
-      acc[2 * j + 1] = __fmul_rn(pp, bf_hi(x[v].w[j]));
+      acc[v][2 * j] = __fmul_rn(pp, bf_lo(x[v].w[j]));
+      acc[v][2 * j + 1] = __fmul_rn(pp, bf_hi(x[v].w[j]));
     }
-    for (int c = 0; c < nb; ++c) {
-      const float pc = __shfl_sync(0xffffffffu, pmine, c);
-      const V8 cv = ld_plain(blk_row + (size_t)c * H + u);
+  }
+  for (int c = 0; c < nb; ++c) {
+    const float pc = __shfl_sync(0xffffffffu, pmine, c);
+    V8 cv[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) cv[v] = ld_plain(blk_row + (size_t)c * H + (t + v * kTeam) * 8);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        acc[2 * j] = __fmaf_rn(pc, bf_lo(cv.w[j]), acc[2 * j]);
-        acc[2 * j + 1] = __fmaf_rn(pc, bf_hi(cv.w[j]), acc[2 * j + 1]);
+        acc[v][2 * j] = __fmaf_rn(pc, bf_lo(cv[v].w[j]), acc[v][2 * j]);
+        acc[v][2 * j + 1] = __fmaf_rn(pc, bf_hi(cv[v].w[j]), acc[v][2 * j + 1]);
       }
     }
+  }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) x[v].w[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
+  for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[v].w[j] = pack_bf2(acc[v][2 * j], acc[v][2 * j + 1]);
   }
 }
 
@@ -263,7 +293,7 @@ __device__ __forceinline__ void attnres_rms_body(const __nv_bfloat16* __restrict
 #pragma unroll
       for (int v = 0; v < VPT; ++v) st_plain(blk_row + (size_t)nb * H + (t + v * kTeam) * 8, x[v]);
     }
-    if (nb > 0) team_attnres_mix<VPT>(x, blk_row, sw, nb, eps, s_mix, t);
+    if (nb > 0) team_attnres_mix<VPT, true>(x, blk_row, sw, nb, eps, s_mix, t);
     team_rms_store<VPT, true, false>(x, gamma, normed + base, nullptr, nullptr, eps, s_red[it & 1], t);
   }
 }
@@ -420,7 +450,7 @@ __device__ __forceinline__ void attnres_rms_push_body(__nv_bfloat16* __restrict_
       for (int v = 0; v < VPT; ++v) st_plain(blk_row + (size_t)nb * H + (t + v * kTeam) * 8, x[v]);
     }
     if (nb > 0)
-      team_attnres_mix<VPT>(x, blk_row, sw, nb, eps, s_mix, t, stats ? sw_mlp : nullptr, stats ? stats + (size_t)b * kNbMax * 2 : nullptr);
+      team_attnres_mix<VPT, true>(x, blk_row, sw, nb, eps, s_mix, t, stats ? sw_mlp : nullptr, stats ? stats + (size_t)b * kNbMax * 2 : nullptr);
     const float tot = team_sumsq<VPT>(x, s_red[it & 1], lane, warp);
     const float r = __frsqrt_rn(__fmaf_rn(tot, 1.0f / (float)H, eps));
     const size_t dst_off = ((size_t)rank * B + b) * H;

@@ -340,20 +340,21 @@ __device__ __forceinline__ void land_add_attnres_rms_body(const void* __restrict
 #pragma unroll
       for (int v = 0; v < VPT; ++v) st_stream(prefix2 + base + (t + v * kTeam) * 8, x[v]);
     } else if constexpr (NR == 1) {
-      // a single rank: the chain is the rank's own partial row
+      // a single rank: the chain is the rank's own partial row; every load of the row issued before the first add
+      V8 pr[VPT];
 #pragma unroll
-      for (int v = 0; v < VPT; ++v) {
-        const size_t off = base + (t + v * kTeam) * 8;
-        const V8 p = rs_chain<1>(ring, (long long)(off >> 3));
-        if (snapshot) {
-          x[v] = p;
-        } else {
-          const V8 pr = ld_stream(prefix + off);
+      for (int v = 0; v < VPT; ++v) x[v] = rs_chain<1>(ring, (long long)((base >> 3) + t + v * kTeam));
+      if (!snapshot) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr.w[j], p.w[j]);
+        for (int v = 0; v < VPT; ++v) pr[v] = ld_stream(prefix + base + (t + v * kTeam) * 8);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[v].w[j] = add_bf2(pr[v].w[j], x[v].w[j]);
         }
-        st_stream(prefix2 + off, x[v]);
       }
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) st_stream(prefix2 + base + (t + v * kTeam) * 8, x[v]);
     }
 #pragma unroll
     for (int v = 0; v < (NR > 0 ? 0 : VPT); ++v) {

@@ -200,7 +200,9 @@ int k3g_permute_gather(const void* q, const void* sf, const void* route_map, lon
  * exp2perm[t, k] - blockoff[owner * experts / ep_ranks] of the owner's out_q / out_sf (out_*_peer: u64 tables of every
  * rank's buffer, own included), owner = ids % ep_ranks (strided) or ids / (experts / ep_ranks).  Destination rows are
  * exactly the live rows of the owner's own expert-sorted order (k3g_permute_gather on its route_map); the tile-padding
- * rows are not written.  Plain peer stores; follow with k3g_rs_arrive before the owner reads. */
+ * rows are not written.  The caller guarantees token_begin + B <= T (the tables' token count, which this call does not
+ * take).  Plain peer stores, 32 bytes each when q and every rank's out_q are 32-byte aligned and cols % 32 == 0, else 16;
+ * follow with k3g_rs_arrive before the owner reads. */
 int k3g_permute_dispatch(const void* q, const void* sf, const void* ids, const void* exp2perm, const void* blockoff, int B,
                          long long token_begin, int topk, int cols, int experts, int ep_ranks, int strided, const void* out_q_peer,
                          const void* out_sf_peer, void* stream);

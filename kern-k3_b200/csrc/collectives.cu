@@ -209,8 +209,12 @@ template <int INFLIGHT>
 __device__ __forceinline__ void push_span(const unsigned char* __restrict__ s, unsigned char* __restrict__ d,
                                           const unsigned long long* __restrict__ p, long long nb, int rank, int nr, long long tid,
                                           long long stride) {
-  // 32 bytes per access when the span allows it (every rank's copy is then assumed 32-byte aligned like this one)
-  if ((nb & 31) == 0 && ((reinterpret_cast<unsigned long long>(s) | reinterpret_cast<unsigned long long>(d)) & 31ull) == 0) {
+  // 32 bytes per access when the span and every rank's copy allow it (the same answer in every thread of the grid)
+  unsigned long long low = reinterpret_cast<unsigned long long>(s) | reinterpret_cast<unsigned long long>(d) | (unsigned long long)nb;
+#pragma unroll
+  for (int q = 0; q < K3G_MAX_RANKS; ++q)
+    if (q < nr && q != rank) low |= p[q];
+  if ((low & 31ull) == 0) {
     const long long n32 = nb >> 5;
     for (long long i0 = tid; i0 < n32; i0 += INFLIGHT * stride) {   // INFLIGHT vectors loaded before the first store: INFLIGHT x (nr - 1) peer stores in flight
       V16 val[INFLIGHT];

@@ -115,3 +115,27 @@ def test_header_is_plain_c_and_links_from_a_c_program(tmp_path):
                            "-L", libdir, "-lk3g", "-Wl,-rpath," + libdir])
     out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
     assert int(out[0]) == len(names) and int(out[1]) == -1
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` runs on the host cores alone (no GPU): one JSON line with the contract's keys, the same
+    `config` object the GPU arm prints, the requested step / warm-up counts honoured, and a CPU baseline that names its
+    sample."""
+    import json
+    import subprocess
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "2", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    for k in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline", "dtype", "data",
+              "config", "cpu_baseline", "e2e", "gpu_launches"):
+        assert k in d, k
+    assert d["impl"] == "reference" and d["steps"] == 2 and d["warmup"] == 1 and d["n_gpus"] == 2 and d["higher_is_better"] is False
+    assert d["config"]["world"] == 2 and d["config"]["tokens"] == 16384 and "config1" in d["config"]["workload"]
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and "world 2" in d["cpu_baseline"]["sample"]
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"] > 0
+    sys.path.insert(0, ROOT)
+    import bench
+    assert bench.workload_config(2) == d["config"]                # what the GPU arm prints for the same world

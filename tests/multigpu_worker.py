@@ -2,11 +2,13 @@
 
 Part 1 (3 replays, everything against the CPU oracle): flag protocol, pull reduce-scatter, the fused
 reduce-scatter -> residual/RMSNorm/MXFP8 -> all-gather kernel, the reduce-scatter folded into the residual kernel and
-into the latent norm, the four-payload push all-gather with its ticket tail, and the dispatch to owning ranks.
+into the latent norm, the four-payload push all-gather with its ticket tail, and the dispatch to owning ranks (strided
+and blocked expert placement).
 
 Part 2 (soak, K3G_SOAK_REPLAYS replays, default 500): the same protocol round with the inputs CHANGED every replay --
-the rows of every shard are rotated by a replay-dependent amount and the all-gather payloads are xor-ed with a
-replay-dependent byte -- and every output compared bit for bit on the device against the (rotated) oracle result.
+the rows of every shard are rotated by a replay-dependent amount, the all-gather payloads and the dispatched token
+rows are xor-ed with a replay-dependent byte -- and every output compared bit for bit on the device against the
+(rotated / xor-ed) oracle result.
 Nothing synchronises the ranks between replays except the kernels' own arrive / poll barriers, so a stale read, a
 store that lands after the barrier or a ticket published early shows up as a mismatch.  All waits are bounded: an
 expired wait sets the status word, which fails the run.
@@ -30,45 +32,60 @@ from util import bf16_bits, normal_bf16, rng, to_dev, to_dev_bf16  # noqa: E402
 TIMEOUT_US = 5_000_000
 
 
-def dispatch_check(pg, rank, world, dev, s):
-    """Dispatch to owning ranks across real peers: T tokens, 8 slots, 224 / world experts per rank (strided); every
-    owner's live rows against the oracle's expert-sorted gather on that owner's own route_map."""
-    T, K, cols, tile = 64 * world, 8, 7168, 128
-    B, per = T // world, 224 // world
-    g = rng(77)
-    ids = np.stack([g.permutation(224)[:K] for _ in range(T)]).astype(np.int32)
-    q = g.integers(0, 256, (T, cols), dtype=np.uint8); sf = g.integers(0, 256, (T, cols // 32), dtype=np.uint8)
-    want = k3o.moe_route(ids, rank, per, world, 1, tile)
-    rows = int(want["total_padded"][0])
-    cap = max(int(k3o.moe_route(ids, o, per, world, 1, tile)["total_padded"][0]) for o in range(world))
-    b_q, b_sf = pg.symmetric("disp_q", cap * cols), pg.symmetric("disp_sf", cap * cols // 32)
-    b_fl = pg.symmetric("disp_flags", 64)
-    out_q, out_sf = b_q.tensor(torch.uint8, (cap, cols)), b_sf.tensor(torch.uint8, (cap, cols // 32))
-    flags = b_fl.tensor(torch.int64, (8,))
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
-    out_q.fill_(0xEE); out_sf.fill_(0xEE)
-    k3g.call("k3g_flags_init", flags, 8, s)
-    torch.cuda.synchronize(); dist.barrier()
-    blocks, E = (T + 255) // 256, 224
-    nct = T * K // tile + E
-    i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32, device=dev)
-    bc, bo, cb, cl, nne, tot, rm, e2p = i32(blocks, E), i32(blocks, E), i32(nct), i32(nct), i32(1), i32(1), i32(nct * tile), i32(T, K)
-    d_ids = to_dev(ids, dev)
-    k3g.call("k3g_moe_route_count", d_ids, T, -1, E, K, world, 1, bc, s)
-    k3g.call("k3g_moe_route_tables_scatter", d_ids, bc, T, -1, E, K, world, 1, tile, bo, cb, cl, nne, tot, rm, e2p, s)
-    k3g.call("k3g_epoch_bump", flags, 4, s)
-    k3g.call("k3g_permute_dispatch", to_dev(q[rank * B:(rank + 1) * B], dev), to_dev(sf[rank * B:(rank + 1) * B], dev), d_ids, e2p, bo, B, rank * B, K, cols,
-             224, world, 1, b_q.table, b_sf.table, s)
-    k3g.call("k3g_rs_arrive", flags, b_fl.table, 4, 1, world, TIMEOUT_US, status, s)
-    torch.cuda.synchronize()
-    assert not status.cpu().numpy().any(), status
-    o_q, o_sf = k3o.permute_gather(q, sf, want["route_map"], rows)
-    live = np.zeros(rows, bool)
-    live[want["exp2perm"][want["exp2perm"] >= 0]] = True
-    got_q, got_sf = out_q[:rows].cpu().numpy(), out_sf[:rows].cpu().numpy()
-    assert np.array_equal(got_q[live], o_q[live]) and np.array_equal(got_sf[live], o_sf[live])
-    assert (got_q[~live] == 0xEE).all() and (got_sf[~live] == 0xEE).all()
-    dist.barrier()
+class Dispatch:
+    """Dispatch to owning ranks across real peers: T tokens, 8 slots, 224 / world experts per rank, strided or blocked
+    placement.  check() runs one dispatch round and compares every live row this rank received with the oracle's
+    expert-sorted gather on this rank's own route_map; with a key the token rows are xor-ed with it first (so a round
+    that delivers an earlier round's bytes is caught), and the comparison stays on the device."""
+
+    def __init__(self, pg, rank, world, dev, s, strided, tag):
+        self.rank, self.world, self.dev, self.s, self.strided = rank, world, dev, s, strided
+        T, K, cols, tile = 64 * world, 8, 7168, 128
+        self.T, self.K, self.cols, self.B, per = T, K, cols, T // world, 224 // world
+        g = rng(77 + strided)
+        ids = np.stack([g.permutation(224)[:K] for _ in range(T)]).astype(np.int32)
+        self.q = g.integers(0, 256, (T, cols), dtype=np.uint8); self.sf = g.integers(0, 256, (T, cols // 32), dtype=np.uint8)
+        want = k3o.moe_route(ids, rank, per, world, strided, tile)
+        self.rows = int(want["total_padded"][0])
+        cap = max(int(k3o.moe_route(ids, o, per, world, strided, tile)["total_padded"][0]) for o in range(world))
+        self.b_q, self.b_sf = pg.symmetric("disp_q" + tag, cap * cols), pg.symmetric("disp_sf" + tag, cap * cols // 32)
+        self.b_fl = pg.symmetric("disp_flags" + tag, 64)
+        self.out_q, self.out_sf = self.b_q.tensor(torch.uint8, (cap, cols)), self.b_sf.tensor(torch.uint8, (cap, cols // 32))
+        self.flags = self.b_fl.tensor(torch.int64, (8,))
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        k3g.call("k3g_flags_init", self.flags, 8, s)
+        blocks, E = (T + 255) // 256, 224
+        nct = T * K // tile + E
+        i32 = lambda *shape: torch.zeros(shape, dtype=torch.int32, device=dev)
+        bc, self.bo, cb, cl, nne, tot, rm, self.e2p = i32(blocks, E), i32(blocks, E), i32(nct), i32(nct), i32(1), i32(1), i32(nct * tile), i32(T, K)
+        self.d_ids = to_dev(ids, dev)
+        k3g.call("k3g_moe_route_count", self.d_ids, T, -1, E, K, world, strided, bc, s)
+        k3g.call("k3g_moe_route_tables_scatter", self.d_ids, bc, T, -1, E, K, world, strided, tile, self.bo, cb, cl, nne, tot, rm, self.e2p, s)
+        o_q, o_sf = k3o.permute_gather(self.q, self.sf, want["route_map"], self.rows)
+        live = np.zeros(self.rows, bool)
+        live[want["exp2perm"][want["exp2perm"] >= 0]] = True
+        self.live = to_dev(live, dev)
+        self.want_q, self.want_sf = to_dev(o_q, dev), to_dev(o_sf, dev)
+        B = self.B
+        self.my_q, self.my_sf = to_dev(self.q[rank * B:(rank + 1) * B], dev), to_dev(self.sf[rank * B:(rank + 1) * B], dev)
+        self.src_q, self.src_sf = torch.empty_like(self.my_q), torch.empty_like(self.my_sf)
+        torch.cuda.synchronize(); dist.barrier()
+
+    def round(self, key):
+        """One epoch: fill the receive buffers, barrier, dispatch, barrier; returns a device flag: 1 if anything differs."""
+        s = self.s
+        torch.bitwise_xor(self.my_q, key, out=self.src_q); torch.bitwise_xor(self.my_sf, key, out=self.src_sf)
+        self.out_q.fill_(0xEE); self.out_sf.fill_(0xEE)
+        k3g.call("k3g_epoch_bump", self.flags, 4, s)
+        k3g.call("k3g_rs_arrive", self.flags, self.b_fl.table, 4, 1, self.world, TIMEOUT_US, self.status, s)      # every rank's buffers are refilled
+        k3g.call("k3g_permute_dispatch", self.src_q, self.src_sf, self.d_ids, self.e2p, self.bo, self.B, self.rank * self.B, self.K, self.cols, 224,
+                 self.world, self.strided, self.b_q.table, self.b_sf.table, s)
+        k3g.call("k3g_rs_arrive", self.flags, self.b_fl.table, 4, 2, self.world, TIMEOUT_US, self.status, s)      # every rank's rows have landed
+        got_q, got_sf = self.out_q[:self.rows], self.out_sf[:self.rows]
+        lv = self.live[:, None]
+        bad = ((got_q != torch.bitwise_xor(self.want_q, key)) & lv).any() | ((got_sf != torch.bitwise_xor(self.want_sf, key)) & lv).any()
+        bad = bad | ((got_q != 0xEE) & ~lv).any() | ((got_sf != 0xEE) & ~lv).any()             # padding rows untouched
+        return bad.to(torch.int64) + (self.status[0] != 0).to(torch.int64)
 
 
 def main():
@@ -170,8 +187,9 @@ def main():
     f = flags.cpu().numpy()
     assert f[0] == 3 * units and all(f[k] == 3 * units for k in (1, 2, 3, 4))
 
-    if world in (1, 2, 4, 8):
-        dispatch_check(pg, rank, world, dev, s)
+    dispatchers = [Dispatch(pg, rank, world, dev, s, strided, "_s%d" % strided) for strided in (1, 0)] if world in (1, 2, 4, 8) else []
+    for d in dispatchers:
+        assert int(d.round(0)) == 0, ("dispatch", d.strided, d.status.cpu().tolist())
 
     # ---- part 2: soak with inputs that change every replay ------------------------------------------------------------
     replays = int(os.environ.get("K3G_SOAK_REPLAYS", "500"))
@@ -181,7 +199,7 @@ def main():
     base_res_out = to_dev_bf16(want_res, dev)
     base_q, base_sf = to_dev(wq, dev).view(world, rows, H), to_dev(wsf, dev).view(world, rows, H // 32)
     base_gathered = [to_dev(w, dev) for w in want_gathered]
-    bad = torch.zeros(6, dtype=torch.int64, device=dev)
+    bad = torch.zeros(7, dtype=torch.int64, device=dev)
     res_in = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
     dst = torch.empty(rows * H, dtype=torch.bfloat16, device=dev); res_out = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
     soak_src = [torch.empty_like(t) for t in srcs]
@@ -212,10 +230,12 @@ def main():
         bad[3] += (sf_all.view(world, rows, H // 32) != torch.roll(base_sf, shift, dims=1)).any()
         for i in range(4):
             bad[4] += (gathered[i] != torch.bitwise_xor(base_gathered[i], key)).any()
+        for d in dispatchers:                                     # the dispatch to owners, both placements, payload xor key
+            bad[6] += d.round(key)
         if replay % 100 == 99 or replay == replays - 1:
             torch.cuda.synchronize()
             bad[5] = int(status[0])
-            assert not bad.cpu().numpy().any(), ("soak replay %d: mismatching replays [pull, residual, codes, scales, gather4, expired waits] = %s, status %s"
+            assert not bad.cpu().numpy().any(), ("soak replay %d: mismatching replays [pull, residual, codes, scales, gather4, expired waits, dispatch] = %s, status %s"
                                                  % (replay, bad.cpu().tolist(), status.cpu().tolist()))
     torch.cuda.synchronize(); dist.barrier()
     f = flags.cpu().numpy()

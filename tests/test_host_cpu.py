@@ -66,6 +66,39 @@ def test_library_exports_every_declared_symbol():
     assert k3g.raw("k3g_router_topk", 16, 16, 16, 16, 16, 4, 200, 8, None) == -2
 
 
+def _launchers(k3g):
+    """Every declared entry that launches kernels: the set-up helpers (peer memory, wait status, device query) take
+    host pointers and are exercised elsewhere."""
+    skip = ("k3g_peer_", "k3g_wait_status", "k3g_device_sms")
+    return {n: a for n, a in sorted(k3g.PROTOTYPES.items()) if not n.startswith(skip)}
+
+
+def test_every_launcher_rejects_null_pointers_before_any_cuda_call():
+    """All pointers null, every size zero: each launcher must answer K3G_ENULL.  Nothing may reach a launch -- a launch
+    attempt would show as a positive cudaError (on a host without a GPU) or as 0."""
+    sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
+    import k3g
+    entries = _launchers(k3g)
+    assert len(entries) >= 60
+    for name, args in entries.items():
+        vals = [None if "*" in ty else (0.0 if "float" in ty else 0) for ty, _ in args]
+        assert getattr(k3g.lib, name)(*vals) == -1, name
+
+
+def test_no_launcher_launches_on_zero_sizes():
+    """Non-null, 16-byte aligned pointers (never dereferenced on the host) and every size zero: a launcher either
+    rejects the shape or returns 0 for the empty input; none attempts a launch (which would return a positive
+    cudaError on a host without a GPU).  kern_k3_fmha_lens has no size argument (one fixed block) and is left out."""
+    sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
+    import k3g
+    for name, args in _launchers(k3g).items():
+        if name == "k3g_fmha_lens":
+            continue
+        vals = [(None if a == "stream" else 4096) if "*" in ty else (0.0 if "float" in ty else 0) for ty, a in args]
+        rc = getattr(k3g.lib, name)(*vals)
+        assert rc in (0, -2, -4, -5), (name, rc)
+
+
 def test_dropin_cubins_export_reference_entry_names():
     """Every cubin built for a reference module name contains the entry names the manifest launches."""
     cdir = os.path.join(ROOT, "kern-k3_b200", "lib", "cubin")

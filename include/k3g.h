@@ -106,7 +106,8 @@ int k3g_rs_land_add_attnres_rms(const void* partial, const void* partial_peer, i
 /* kern_k3_moe_quant followed by kern_k3_allgather4_push in one launch (no counterpart in the reference): MXFP8 codes and
  * scale bytes of x [rows, cols] bf16 written straight to rows rank * rows .. of every rank's q_all [nranks * rows, cols] /
  * sf_all [nranks * rows, cols / 32] (q_peer / sf_peer = u64 peer tables); payloads s2 -> d2 and s3 -> d3 (n bytes each, the
- * router's indices and weights) gathered as by k3g_allgather4_push; the same barrier tail.  Identical gathered bytes. */
+ * router's indices and weights) gathered as by k3g_allgather4_push; the same barrier tail.  Identical gathered bytes.
+ * nranks 1, 2, 4 or 8. */
 int k3g_moe_quant_allgather_push(const void* x, int rows, int cols, void* q_all, const void* q_peer, void* sf_all, const void* sf_peer,
                                  const void* s2, void* d2, const void* p2, long long n2, const void* s3, void* d3, const void* p3,
                                  long long n3, void* flags, const void* flags_peer, int slot, int rank, int nranks, int units,

@@ -433,14 +433,25 @@ __global__ void __launch_bounds__(256) allgather4_kernel(const unsigned char* s0
 // MXFP8 quantisation of this rank's latent rows written straight into every rank's gathered buffers, then two plain
 // payloads (the router's indices and weights) and the barrier tail: kern_k3_moe_quant + kern_k3_allgather4_push in one
 // launch (the codes are never written locally and read back).  One 32-element group per thread-step, as kern_k3_moe_quant.
-__global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bfloat16* __restrict__ x, long long ngroups, unsigned char* q_all,
-                                                                   const unsigned long long* __restrict__ q_peer, unsigned char* sf_all,
-                                                                   const unsigned long long* __restrict__ sf_peer, const unsigned char* s2,
-                                                                   unsigned char* d2, const unsigned long long* p2, long long n2,
-                                                                   const unsigned char* s3, unsigned char* d3, const unsigned long long* p3,
-                                                                   long long n3, unsigned long long* flags, const unsigned long long* flags_peer,
-                                                                   int slot, int rank, int nranks, long long timeout_ns, unsigned* status, unsigned arrivals) {
-  const int nr = nranks < K3G_MAX_RANKS ? nranks : K3G_MAX_RANKS;
+template <int NR>
+__global__ void __launch_bounds__(256, NR == 1 ? 6 : 4) moe_quant_allgather_kernel(const __nv_bfloat16* __restrict__ x, long long ngroups, unsigned char* q_all,
+                                                                  const unsigned long long* __restrict__ q_peer, unsigned char* sf_all,
+                                                                  const unsigned long long* __restrict__ sf_peer, const unsigned char* s2,
+                                                                  unsigned char* d2, const unsigned long long* p2, long long n2,
+                                                                  const unsigned char* s3, unsigned char* d3, const unsigned long long* p3,
+                                                                  long long n3, unsigned long long* flags, const unsigned long long* flags_peer,
+                                                                  int slot, int rank, long long timeout_ns, unsigned* status, unsigned arrivals) {
+  // The world size is a template argument so that the peers' base pointers are a fixed, small set of registers: the
+  // kernel then fits several 256-thread blocks per SM, which is what hides the HBM round trip of the one group a
+  // thread has in flight (a single rank has no peer code at all).
+  unsigned char* qp[NR > 1 ? NR - 1 : 1];
+  unsigned char* sp[NR > 1 ? NR - 1 : 1];
+#pragma unroll
+  for (int k = 0; k + 1 < NR; ++k) {
+    const int q = k < rank ? k : k + 1;                            // the peers in ascending order, own rank left out
+    qp[k] = reinterpret_cast<unsigned char*>(q_peer[q]);
+    sp[k] = reinterpret_cast<unsigned char*>(sf_peer[q]);
+  }
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
   for (long long g = tid; g < ngroups; g += stride) {
     const __nv_bfloat16* src = x + g * 32;
@@ -462,16 +473,14 @@ __global__ void __launch_bounds__(1024) moe_quant_allgather_kernel(const __nv_bf
     *reinterpret_cast<uint4*>(q_all + at * 32 + 16) = make_uint4(o.w[4], o.w[5], o.w[6], o.w[7]);
     sf_all[at] = (unsigned char)(e + 127);
 #pragma unroll
-    for (int q = 0; q < K3G_MAX_RANKS; ++q) {
-      if (q < nr && q != rank) {
-        st_stream32(reinterpret_cast<unsigned char*>(q_peer[q]) + at * 32, o);
-        reinterpret_cast<unsigned char*>(sf_peer[q])[at] = (unsigned char)(e + 127);
-      }
+    for (int k = 0; k + 1 < NR; ++k) {
+      st_stream32(qp[k] + at * 32, o);
+      sp[k][at] = (unsigned char)(e + 127);
     }
   }
-  if (n2 > 0) push_span<1>(s2, d2, p2, n2, rank, nr, tid, stride);
-  if (n3 > 0) push_span<1>(s3, d3, p3, n3, rank, nr, tid, stride);
-  block_arrive_tail(flags, flags_peer, slot, nranks, timeout_ns, status ? status : g_wait_status, arrivals);
+  if (n2 > 0) push_span<1>(s2, d2, p2, n2, rank, NR, tid, stride);
+  if (n3 > 0) push_span<1>(s3, d3, p3, n3, rank, NR, tid, stride);
+  block_arrive_tail(flags, flags_peer, slot, NR, timeout_ns, status ? status : g_wait_status, arrivals);
 }
 
 }  // namespace
@@ -621,19 +630,31 @@ K3G_API int k3g_moe_quant_allgather_push(const void* x, int rows, int cols, void
   K3G_REQUIRE_PTR(x); K3G_REQUIRE_PTR(q_all); K3G_REQUIRE_PTR(q_peer); K3G_REQUIRE_PTR(sf_all); K3G_REQUIRE_PTR(sf_peer);
   K3G_REQUIRE_PTR(flags); K3G_REQUIRE_PTR(flags_peer);
   K3G_REQUIRE_ALIGNED(x); K3G_REQUIRE((reinterpret_cast<uintptr_t>(q_all) & 31u) == 0, K3G_EALIGN);   // 32-byte code stores, every rank's buffer alike
-  K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0 && nranks >= 1 && nranks <= K3G_MAX_RANKS && units > 0, K3G_ESHAPE);
-  K3G_REQUIRE(rank >= 0 && rank < nranks && slot >= 1 && timeout_us > 0, K3G_ERANGE);
+  K3G_REQUIRE(rows >= 0 && cols > 0 && cols % 32 == 0 && units > 0, K3G_ESHAPE);
+  if (const int rc = check_world(rank, nranks)) return rc;       // 1, 2, 4 or 8 ranks
+  K3G_REQUIRE(slot >= 1 && timeout_us > 0, K3G_ERANGE);
   const void* ss[2] = {s2, s3}; void* dd[2] = {d2, d3}; const void* pp[2] = {p2, p3};
   const long long nn[2] = {n2, n3};
   for (int i = 0; i < 2; ++i) {
     K3G_REQUIRE(nn[i] >= 0 && nn[i] % 16 == 0, K3G_ESHAPE);
     if (nn[i] > 0) { K3G_REQUIRE_PTR(ss[i]); K3G_REQUIRE_PTR(dd[i]); K3G_REQUIRE_PTR(pp[i]); K3G_REQUIRE_ALIGNED(ss[i]); K3G_REQUIRE_ALIGNED(dd[i]); }
   }
-  moe_quant_allgather_kernel<<<push_grid(units), 1024, 0, k3g_stream(stream)>>>(
-      (const __nv_bfloat16*)x, (long long)rows * cols / 32, (unsigned char*)q_all, (const unsigned long long*)q_peer, (unsigned char*)sf_all,
-      (const unsigned long long*)sf_peer, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2, (const unsigned char*)s3,
-      (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags, (const unsigned long long*)flags_peer, slot, rank, nranks,
-      timeout_us * 1000LL, (unsigned*)status, (unsigned)units);
+  // 256-thread blocks, one resident wave (six per SM alone, four with peers: the kernel's launch bounds); the launch
+  // still publishes `units` arrivals
+  const unsigned grid = (unsigned)(units < 148 ? units : 148) * (nranks == 1 ? 6u : 4u);
+#define K3G_MQAG(NR_)                                                                                                                        \
+  moe_quant_allgather_kernel<NR_><<<grid, 256, 0, k3g_stream(stream)>>>(                                                                    \
+      (const __nv_bfloat16*)x, (long long)rows * cols / 32, (unsigned char*)q_all, (const unsigned long long*)q_peer, (unsigned char*)sf_all, \
+      (const unsigned long long*)sf_peer, (const unsigned char*)s2, (unsigned char*)d2, (const unsigned long long*)p2, n2,                   \
+      (const unsigned char*)s3, (unsigned char*)d3, (const unsigned long long*)p3, n3, (unsigned long long*)flags,                           \
+      (const unsigned long long*)flags_peer, slot, rank, timeout_us * 1000LL, (unsigned*)status, (unsigned)units)
+  switch (nranks) {
+    case 1: K3G_MQAG(1); break;
+    case 2: K3G_MQAG(2); break;
+    case 4: K3G_MQAG(4); break;
+    default: K3G_MQAG(8); break;
+  }
+#undef K3G_MQAG
   return k3g_launch_status();
 }
 

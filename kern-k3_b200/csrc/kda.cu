@@ -9,7 +9,8 @@
 // i < 0 come from the stored 3-row window; y = fma(x_i, w3, fma(x_{i-1}, w2, fma(x_{i-3}, w0,
 // x_{i-2} * w1))) (the reference build's contraction of its four-term sum); sb = bf16(y); out = bf16(sb * sigmoid(sb)); the new window is the last three
 // INPUT rows.  A thread owns 4 consecutive columns (8 bytes) and walks a run of rows with the three
-// previous inputs sliding in registers, four row loads in flight at a time, eight blocks per SM;
+// previous inputs sliding in registers, the next four row loads issued before the current four rows are computed
+// and stored, seven blocks per SM;
 // rows per block = max(3, ceil(span / gridDim.z)), so the reference launch (16 rows) and a coarser one
 // (fewer halo re-reads) are both valid.  Three is the floor because only the block that starts at row 0
 // may read the stored window: it also overwrites it, and a block starting at row 1 or 2 would race with
@@ -27,9 +28,10 @@ using namespace k3g;
 namespace {
 
 // A thread owns kVec = 4 consecutive columns (8 bytes): small register footprint (the three sliding
-// taps, one chunk of rows and 16 tap weights), so eight 128-thread blocks stay resident per SM.
+// taps, one chunk of rows, the next chunk's raw loads and 16 tap weights), so seven 128-thread blocks stay
+// resident per SM (eight would spill the prefetched chunk with f32 taps; measured slower).
 #ifndef K3G_SPAN_MINB
-#define K3G_SPAN_MINB 8
+#define K3G_SPAN_MINB 7
 #endif
 constexpr int kVec = 4;
 constexpr int kChunk = 4;
@@ -89,23 +91,30 @@ __device__ __forceinline__ void span_stream(const __nv_bfloat16* __restrict__ pa
     const int i = row0 - 3 + t;
     unpack4(i < 0 ? *reinterpret_cast<const uint2*>(win + (size_t)(i + 3) * inner + c) : ld8_stream(col + (size_t)i * row_stride), x[t]);
   }
-  // full chunks: no per-row predicates, pointers advance by constant strides
+  // full chunks: no per-row predicates, pointers advance by constant strides.  The loads of chunk n + 1 are issued
+  // before chunk n is computed and stored, so a thread always has a chunk of rows on its way from HBM.
   const __nv_bfloat16* pin = col + (size_t)row0 * row_stride;
   __nv_bfloat16* pout = out + (size_t)row0 * inner + c;
   int r = row0;
-  for (; r + kChunk <= row1; r += kChunk) {
-    uint2 raw[kChunk];
+  uint2 raw[kChunk];
+  if (r + kChunk <= row1) {
 #pragma unroll
     for (int k = 0; k < kChunk; ++k) raw[k] = ld8_stream(pin + k * row_stride);
+  }
+  for (; r + kChunk <= row1; r += kChunk) {
 #pragma unroll
     for (int k = 0; k < kChunk; ++k) unpack4(raw[k], x[3 + k]);
+    pin += kChunk * row_stride;
+    if (r + 2 * kChunk <= row1) {
+#pragma unroll
+      for (int k = 0; k < kChunk; ++k) raw[k] = ld8_stream(pin + k * row_stride);
+    }
 #pragma unroll
     for (int k = 0; k < kChunk; ++k) __stcs(reinterpret_cast<uint2*>(pout + (size_t)k * inner), conv_silu_row(x[k], x[k + 1], x[k + 2], x[k + 3], w));
 #pragma unroll
     for (int t = 0; t < 3; ++t)
 #pragma unroll
       for (int k = 0; k < kVec; ++k) x[t][k] = x[kChunk + t][k];
-    pin += kChunk * row_stride;
     pout += (size_t)kChunk * inner;
   }
   for (; r < row1; ++r) {                                   // ragged tail, one row at a time

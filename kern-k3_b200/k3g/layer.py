@@ -19,6 +19,9 @@ from .peer import PeerGroup, collective_units, shard_rows
 
 H, LATENT, EXPERTS, TOPK, TILE = 7168, 3584, 224, 16, 128
 SHARED = 6144
+# grid of an apply-only quantisation launch: every block first reduces the producer's partial maxima, so one resident
+# wave of four 256-thread blocks per SM beats the reference op's 2048 (measured: 2 us per call at 16k tokens)
+APPLY_GRID = 592
 
 
 class LayerGlue:
@@ -184,13 +187,13 @@ class LayerGlue:
                     "k3g_attnres_rms_push_amax", self.blocks, self.sw, self.gamma, self.normed_all, self.b_normed_all.table, nb, 0, B, r, W,
                     self.sw_mlp, self.stats, self.p1, self.p2, self.prefix2, self.hidden, 1, H, 1e-5, self.rowmax_all, self.b_rowmax.table, s())),
                 "qkvg_quant (fp8 tensor, T rows)": ("qkvg_quant (fp8 apply only, T rows)", lambda: call(
-                    "k3g_quant_fp8_apply", self.normed_all, self.fp8_big, self.qscale, self.rowmax_all, T, T * H, 2048, s())),
+                    "k3g_quant_fp8_apply", self.normed_all, self.fp8_big, self.qscale, self.rowmax_all, T, T * H, APPLY_GRID, s())),
                 "reduce_attn (pull RS)": None,
                 "res_mlp (land + attnres + rms, stats)": ("reduce_attn + res_mlp (pull RS inside land + attnres + rms, stats, row maxima)", lambda: call(
                     "k3g_rs_land_add_attnres_rms", self.attn_part, self.b_attn_part.table, r, W, self.hidden, self.blocks, self.sw_mlp, self.gamma,
                     self.prefix2_next, self.normed, nb, 0, B, H, 1e-5, self.stats, nb, self.rowmax, s())),
                 "normed_quant (fp8 tensor, B rows)": ("normed_quant (fp8 apply only, B rows)", lambda: call(
-                    "k3g_quant_fp8_apply", self.normed, self.fp8_small, self.qscale[1:], self.rowmax, B, B * H, 2048, s())),
+                    "k3g_quant_fp8_apply", self.normed, self.fp8_small, self.qscale[1:], self.rowmax, B, B * H, APPLY_GRID, s())),
                 "moe_quant (MXFP8 latent)": None,
                 "gather_small (AG4 push + barrier)": ("moe_quant + gather_small (MXFP8 written straight into every rank's gathered buffers + barrier)",
                                                       lambda: call(
@@ -203,7 +206,7 @@ class LayerGlue:
                     "k3g_rs_situ_rms", self.shared_partial, self.shared_act, self.moe_partial, self.b_moe_partial.table, r, W, self.gamma_lat,
                     self.routed_latent_norm, SHARED, B, LATENT, B, self.item_max, s())),
                 "shared_act_quant (fp8 tensor)": ("shared_act_quant (fp8 apply only)", lambda: call(
-                    "k3g_quant_fp8_apply", self.shared_act, self.shared_q, self.qscale[2:], self.item_max, self.item_max.numel(), B * SHARED, 2048,
+                    "k3g_quant_fp8_apply", self.shared_act, self.shared_q, self.qscale[2:], self.item_max, self.item_max.numel(), B * SHARED, APPLY_GRID,
                     s())),
             }
             c = [swap.get(label, (label, fn)) for label, fn in c if swap.get(label, 0) is not None]

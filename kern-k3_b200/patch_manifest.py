@@ -174,6 +174,7 @@ def fuse(manifest, cubin_dir=CUBIN_DIR):
     if "quant_fp8_apply" not in ops:
         apply_l = json.loads(json.dumps(ops["quant_fp8_tensor"]["impl"]["launches"][1]))      # kern_quant_fp8_apply_v2(x, y, n, partials, nb, scale)
         apply_l["module"] = QUANT
+        apply_l["grid"] = [592, 1, 1]          # every block reduces all partial maxima first: one resident wave, not 2048 blocks
         apply_l["args"] = [{"param": 0}, {"param": 1}, {"param": 5}, {"param": 3}, {"param": 4}, {"param": 2}]
         ops["quant_fp8_apply"] = {"params": ["in buffer<bf16>", "out buffer<u8>", "out buffer<f32>", "in buffer<f32>", "i32", "i32"],
                                   "impl": {"launches": [apply_l]}}

@@ -2,8 +2,9 @@
 
 Part 1 (3 replays, everything against the CPU oracle): flag protocol, pull reduce-scatter, the fused
 reduce-scatter -> residual/RMSNorm/MXFP8 -> all-gather kernel, the reduce-scatter folded into the residual kernel and
-into the latent norm, the four-payload push all-gather with its ticket tail, and the dispatch to owning ranks (strided
-and blocked expert placement).
+into the latent norm, the four-payload push all-gather with its ticket tail, the residual push with its row maxima,
+the epoch-and-barrier launch, the latent quantisation written into every rank's gathered buffers, and the dispatch to
+owning ranks (strided and blocked expert placement).
 
 Part 2 (soak, K3G_SOAK_REPLAYS replays, default 500): the same protocol round with the inputs CHANGED every replay --
 the rows of every shard are rotated by a replay-dependent amount, the all-gather payloads and the dispatched token
@@ -86,6 +87,69 @@ class Dispatch:
         bad = ((got_q != torch.bitwise_xor(self.want_q, key)) & lv).any() | ((got_sf != torch.bitwise_xor(self.want_sf, key)) & lv).any()
         bad = bad | ((got_q != 0xEE) & ~lv).any() | ((got_sf != 0xEE) & ~lv).any()             # padding rows untouched
         return bad.to(torch.int64) + (self.status[0] != 0).to(torch.int64)
+
+
+def layer_entries_check(pg, rank, world, dev, s):
+    """The per-layer entries that store to peers, across real GPUs and against the oracle: the residual push with its
+    row maxima (k3g_attnres_rms_push_amax: every rank ends with all ranks' normed rows and maxima), the barrier that
+    follows it in the fused call list (k3g_epoch_arrive), and the latent quantisation written straight into every
+    rank's gathered buffers with the router payloads and its own barrier tail (k3g_moe_quant_allgather_push)."""
+    from test_residual_push import _case
+    B, H, nb, LAT = 24, 7168, 3, 3584
+    T = world * B
+    cases = [_case(700 + r, B) for r in range(world)]
+    b_n, b_m, b_f = pg.symmetric("le_normed", T * H * 2), pg.symmetric("le_rowmax", T * 4), pg.symmetric("le_flags", 64)
+    normed_all, rowmax_all = b_n.tensor(torch.bfloat16, (T, H)), b_m.tensor(torch.float32, (T,))
+    flags = b_f.tensor(torch.int64, (8,))
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    normed_all.zero_(); rowmax_all.fill_(-1.0)
+    k3g.call("k3g_flags_init", flags, 8, s)
+    g = rng(900 + rank)
+    x = normal_bf16(g, (B, LAT), std=2.0)
+    pay = [g.integers(0, 256, B * 64, dtype=np.uint8) for _ in range(2)]
+    b_q, b_sf = pg.symmetric("le_q", T * LAT), pg.symmetric("le_sf", T * LAT // 32)
+    b_p = [pg.symmetric("le_pay%d" % i, T * 64) for i in range(2)]
+    q_all, sf_all = b_q.tensor(torch.uint8, (T, LAT)), b_sf.tensor(torch.uint8, (T, LAT // 32))
+    pay_all = [b.tensor(torch.uint8, (T * 64,)) for b in b_p]
+    q_all.zero_(); sf_all.zero_()
+    for t in pay_all:
+        t.zero_()
+    torch.cuda.synchronize(); dist.barrier()
+    d = cases[rank]
+    units = 5
+    blocks, hidden = to_dev_bf16(d["blocks"], dev), torch.zeros((B, H), dtype=torch.bfloat16, device=dev)
+    stats = torch.zeros((B, 8, 2), dtype=torch.float32, device=dev)
+    k3g.call("k3g_attnres_rms_push_amax", blocks, to_dev(d["sw"], dev), to_dev_bf16(d["gamma"], dev), normed_all, b_n.table, nb, 1, B, rank, world,
+             to_dev(d["sw_mlp"], dev), stats, to_dev_bf16(d["p1"], dev), to_dev_bf16(d["p2"], dev), to_dev_bf16(d["prefix2"], dev), hidden, 1, H, 1e-5,
+             rowmax_all, b_m.table, s)
+    k3g.call("k3g_epoch_arrive", flags, b_f.table, units, 1, world, TIMEOUT_US, status, s)          # every rank's rows and maxima have landed
+    k3g.call("k3g_moe_quant_allgather_push", to_dev_bf16(x, dev), B, LAT, q_all, b_q.table, sf_all, b_sf.table, to_dev(pay[0], dev), pay_all[0],
+             b_p[0].table, B * 64, to_dev(pay[1], dev), pay_all[1], b_p[1].table, B * 64, flags, b_f.table, 2, rank, world, units, TIMEOUT_US, status, s)
+    torch.cuda.synchronize()
+    assert not status.cpu().numpy().any(), status
+    want_rows = []
+    for r, c in enumerate(cases):
+        o_hidden, o_normed, o_stats = k3o.attnres_rms_push(c["blocks"].copy(), c["sw"], c["gamma"], nb, 1, c["sw_mlp"], c["p1"], c["p2"], c["prefix2"], 1, 1e-5)
+        want_rows.append(o_normed)
+        if r == rank:
+            assert np.array_equal(bf16_bits(hidden), o_hidden) and np.array_equal(stats.cpu().numpy().view(np.uint32), o_stats.view(np.uint32))
+    want = np.concatenate(want_rows)
+    assert np.array_equal(bf16_bits(normed_all), want)
+    assert np.array_equal(rowmax_all.cpu().numpy(), (((want & 0x7fff).max(axis=1).astype(np.uint32)) << 16).view(np.float32))
+    wq, wsf, wpay = [], [], [[], []]
+    for r in range(world):
+        gr = rng(900 + r)
+        xr = normal_bf16(gr, (B, LAT), std=2.0)
+        q, sf = k3o.moe_quant(xr)
+        wq.append(q); wsf.append(sf)
+        for i in range(2):
+            wpay[i].append(gr.integers(0, 256, B * 64, dtype=np.uint8))
+    assert np.array_equal(q_all.cpu().numpy(), np.concatenate(wq)) and np.array_equal(sf_all.cpu().numpy(), np.concatenate(wsf))
+    for i in range(2):
+        assert np.array_equal(pay_all[i].cpu().numpy(), np.concatenate(wpay[i]))
+    f = flags.cpu().numpy()
+    assert f[0] == units and f[1] == units and f[2] == units
+    dist.barrier()
 
 
 def main():
@@ -187,6 +251,8 @@ def main():
     f = flags.cpu().numpy()
     assert f[0] == 3 * units and all(f[k] == 3 * units for k in (1, 2, 3, 4))
 
+    if world in (1, 2, 4, 8):
+        layer_entries_check(pg, rank, world, dev, s)
     dispatchers = [Dispatch(pg, rank, world, dev, s, strided, "_s%d" % strided) for strided in (1, 0)] if world in (1, 2, 4, 8) else []
     for d in dispatchers:
         assert int(d.round(0)) == 0, ("dispatch", d.strided, d.status.cpu().tolist())

@@ -3,8 +3,9 @@
 Part 1 (3 replays, everything against the CPU oracle): flag protocol, pull reduce-scatter, the fused
 reduce-scatter -> residual/RMSNorm/MXFP8 -> all-gather kernel, the reduce-scatter folded into the residual kernel and
 into the latent norm, the four-payload push all-gather with its ticket tail, the residual push with its row maxima,
-the epoch-and-barrier launch, the latent quantisation written into every rank's gathered buffers, and the dispatch to
-owning ranks (strided and blocked expert placement).
+the epoch-and-barrier launch, the latent quantisation written into every rank's gathered buffers, the whole per-layer
+call list (fused list against reference list, byte for byte on every rank), and the dispatch to owning ranks (strided
+and blocked expert placement).
 
 Part 2 (soak, K3G_SOAK_REPLAYS replays, default 500): the same protocol round with the inputs CHANGED every replay --
 the rows of every shard are rotated by a replay-dependent amount, the all-gather payloads and the dispatched token
@@ -152,6 +153,28 @@ def layer_entries_check(pg, rank, world, dev, s):
     dist.barrier()
 
 
+def layer_program_check(rank, world, dev):
+    """The whole per-layer call list over real peers: the fused list must leave, on every rank, exactly the bytes the
+    reference call list leaves (activations, quantised tensors, routing tables, flag counters), for a KDA and an MLA
+    layer, two passes each so that flags and epochs have advanced once."""
+    from k3g.layer import LayerGlue
+    from test_layer_program import OUTPUTS
+    for kind in ("kda", "mla"):
+        got = {}
+        for fused in (False, True):
+            lg = LayerGlue(rank, world, tokens=1024, kind=kind, nb=3, seed=5, fused=fused)
+            lg.run()
+            lg.run()
+            torch.cuda.synchronize()
+            lg.check_status()
+            extra = ["span_q", "span_k", "span_v", "gated"] if kind == "kda" else ["q_norm", "mla_gate", "attn_gated", "latent_rows"]
+            got[fused] = {name: getattr(lg, name).clone() for name in OUTPUTS + extra}
+            dist.barrier()
+            lg.close()
+        bad = [name for name, ref in got[False].items() if not torch.equal(ref.view(torch.uint8), got[True][name].view(torch.uint8))]
+        assert not bad, (kind, bad)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -253,6 +276,7 @@ def main():
 
     if world in (1, 2, 4, 8):
         layer_entries_check(pg, rank, world, dev, s)
+        layer_program_check(rank, world, dev)
     dispatchers = [Dispatch(pg, rank, world, dev, s, strided, "_s%d" % strided) for strided in (1, 0)] if world in (1, 2, 4, 8) else []
     for d in dispatchers:
         assert int(d.round(0)) == 0, ("dispatch", d.strided, d.status.cpu().tolist())

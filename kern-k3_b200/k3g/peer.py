@@ -80,11 +80,21 @@ class SymmetricBuffer:
             __cuda_array_interface__ = {"shape": (n * esz,), "typestr": "|u1", "data": (self.ptr, False), "version": 3}
         return torch.as_tensor(_Arr(), device="cuda").view(dtype).view(*shape)
 
-    def release(self):
+    def close_peers(self):
+        """Unmap the peers' copies (this rank's own memory stays allocated: a peer may still have it mapped)."""
         for r, a in enumerate(self.addrs):
-            if r != self._rank:
+            if r != self._rank and a is not None:
                 self._alloc.close(a)
-        self._alloc.free(self.ptr)
+        self.addrs = [a if r == self._rank else None for r, a in enumerate(self.addrs)]
+
+    def free_own(self):
+        if self.ptr is not None:
+            self._alloc.free(self.ptr)
+            self.ptr = None
+
+    def release(self):
+        self.close_peers()
+        self.free_own()
 
 
 class PeerGroup:
@@ -121,5 +131,9 @@ class PeerGroup:
             import torch.distributed as dist
             dist.barrier(group=self.group)      # nobody unmaps while a peer may still touch the memory
         for b in self.buffers:
-            b.release()
+            b.close_peers()
+        if self.world > 1:
+            dist.barrier(group=self.group)      # nobody frees exported memory while a peer still has it mapped
+        for b in self.buffers:
+            b.free_own()
         self.buffers = []

@@ -3,6 +3,7 @@ fake allocator (no CUDA), the sharded oracle pipeline reassembled across ranks, 
 dispatch (who owns which expert, which row a routed token lands on) played through on the host."""
 import os
 import sys
+import time
 
 import numpy as np
 import torch.distributed as dist
@@ -34,9 +35,11 @@ class FakeAllocator:
 
     def close(self, ptr):
         self.closed.append(ptr)
+        self.last_close = time.monotonic()
 
     def free(self, ptr):
         self.freed.append(ptr)
+        self.first_free = min(getattr(self, "first_free", float("inf")), time.monotonic())
 
     def upload_table(self, addrs):
         return list(addrs)
@@ -58,6 +61,11 @@ def main():
                 assert buf.table[r] >> 60 == 1 and ((buf.table[r] & ((1 << 60) - 1)) >> 40) == r
     pg.release()
     assert len(alloc.closed) == 2 * (world - 1) and len(alloc.freed) == 2
+    # teardown order across ranks: every rank has unmapped its peers' buffers before any rank frees exported memory
+    # (freeing memory a peer still has mapped is undefined with CUDA IPC); the monotonic clock is system-wide
+    times = [None] * world
+    dist.all_gather_object(times, (alloc.last_close, alloc.first_free))
+    assert max(t[0] for t in times) <= min(t[1] for t in times), times
 
     # sharding: rows in block order, one collective grid width for the whole replay
     T, H = 64, 1024

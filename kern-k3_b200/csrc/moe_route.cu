@@ -157,14 +157,37 @@ __device__ __forceinline__ void block_tables(TablesInBlock<MAXE>& tb, const int*
                                              int* __restrict__ num_non_exiting, int* __restrict__ total_padded,
                                              int* __restrict__ route_map) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int tot = 0, pre = 0;
-    for (int b = 0; b < blocks; ++b) {
-      const int c = blockcount[(size_t)b * E + e];      // threads walk adjacent experts: coalesced rows
-      pre += b < blk ? c : 0;
-      tot += c;
+  // Column sums of blockcount over all blocks (count) and over the blocks before this one (pre).  The block's
+  // threads are dealt out as `parts` threads per expert, part p taking the rows p, p + parts, ...: adjacent threads
+  // read adjacent experts of one row (coalesced), a thread's loads are independent and issued eight at a time, and the
+  // parts meet in shared-memory integer adds (order-free, so the sums are the stand-alone kernel's).
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { tb.count[e] = 0; tb.pre[e] = 0; }
+  __syncthreads();
+  {
+    const int parts = max(1, min((int)blockDim.x / E, 16));
+    const int e = threadIdx.x % E, part = threadIdx.x / E;
+    if (part < parts) {
+      int tot = 0, pre = 0;
+#pragma unroll 8
+      for (int b = part; b < blocks; b += parts) {
+        const int c = blockcount[(size_t)b * E + e];
+        pre += b < blk ? c : 0;
+        tot += c;
+      }
+      atomicAdd(&tb.count[e], tot);
+      atomicAdd(&tb.pre[e], pre);
     }
-    tb.count[e] = tot; tb.pre[e] = pre;
+    if (E > (int)blockDim.x) {                            // more experts than threads: the rest, one thread each
+      for (int e2 = threadIdx.x + blockDim.x; e2 < E; e2 += blockDim.x) {
+        int tot = 0, pre = 0;
+        for (int b = 0; b < blocks; ++b) {
+          const int c = blockcount[(size_t)b * E + e2];
+          pre += b < blk ? c : 0;
+          tot += c;
+        }
+        tb.count[e2] = tot; tb.pre[e2] = pre;
+      }
+    }
   }
   __syncthreads();
   if (warp == 0) {

@@ -628,7 +628,7 @@ def run_gpu(args, rank, world, local_rank):
     glue.check_status()
     e2e_us = timed(lambda: glue.step_host_pipelined(hp, hr, ho, hq, hs, chunks=8), e2e_steps, 3)
     glue.check_status()
-    e2e_mode = "row-chunked, 3 streams (H2D / kernels / D2H overlapped), 8 chunks"
+    e2e_mode = "row-chunked, 3 streams (H2D / kernels / D2H overlapped), 8 parts with the last one cut again into 1/2, 1/4, 1/8, 1/8 (11 chunks)"
     if e2e_serial_us < e2e_us:
         e2e_us, e2e_mode = e2e_serial_us, "serial: copy in, graph replay, copy out"
 

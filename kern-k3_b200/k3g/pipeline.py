@@ -88,10 +88,30 @@ class TpGlue:
         host_q_all.copy_(self.q_all, non_blocking=True)
         host_sf_all.copy_(self.sf_all, non_blocking=True)
 
+    @staticmethod
+    def chunk_bounds(rows, chunks, taper=3):
+        """Row ranges [r0, r1) of the host pipeline: `chunks` equal parts, the last of them cut again into
+        1/2, 1/4, ... (`taper` halvings) of a part.  The link into the device is the bottleneck, so what is left once the
+        last copy in has landed -- the last chunk's kernels and its copy out -- is the only part of the pipeline nothing
+        overlaps: the smaller the last chunk, the shorter that tail."""
+        part = max(1, (rows + chunks - 1) // chunks)
+        bounds, r = [], 0
+        while rows - r > part:
+            bounds.append((r, r + part)); r += part
+        left = rows - r
+        for _ in range(taper):
+            piece = left // 2
+            if piece < 1:
+                break
+            bounds.append((r, r + piece)); r += piece; left -= piece
+        if left > 0:
+            bounds.append((r, rows))
+        return bounds
+
     def step_host_pipelined(self, host_partial, host_residual, host_residual_out, host_q_all, host_sf_all, chunks=8):
-        """step_host with the shard cut into row chunks and three streams: while chunk c is reduced,
-        normalised and gathered, chunk c + 1 is on its way in and chunk c - 1 on its way out, so the
-        host link is busy in both directions at once.  Each chunk is a full protocol round (epoch bump,
+        """step_host with the shard cut into row chunks (chunk_bounds: equal parts with a tapered tail) and three
+        streams: while chunk c is reduced, normalised and gathered, chunk c + 1 is on its way in and chunk c - 1 on its
+        way out, so the host link is busy in both directions at once.  Each chunk is a full protocol round (epoch bump,
         arrive, fused kernel over rows [r0, r1) of every shard, arrive)."""
         if not hasattr(self, "_s_in"):
             self._s_in, self._s_cmp, self._s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
@@ -100,9 +120,7 @@ class TpGlue:
         for st in (self._s_in, self._s_cmp, self._s_out):
             st.wait_event(start)
         R, W = self.rows, self.world
-        step_rows = (R + chunks - 1) // chunks
-        for r0 in range(0, R, step_rows):
-            r1 = min(R, r0 + step_rows)
+        for r0, r1 in self.chunk_bounds(R, chunks):
             with torch.cuda.stream(self._s_in):
                 for q in range(W):
                     self.partial[q * R + r0:q * R + r1].copy_(host_partial[q * R + r0:q * R + r1], non_blocking=True)

@@ -99,6 +99,18 @@ def test_no_launcher_launches_on_zero_sizes():
         assert rc in (0, -2, -4, -5), (name, rc)
 
 
+def test_host_pipeline_chunks_partition_the_shard_with_a_tapered_tail():
+    sys.path.insert(0, os.path.join(ROOT, "kern-k3_b200"))
+    from k3g.pipeline import TpGlue
+    for rows in (1, 2, 7, 8, 13, 100, 2048, 16384, 16385):
+        for chunks in (1, 3, 8, 16):
+            b = TpGlue.chunk_bounds(rows, chunks)
+            assert b[0][0] == 0 and b[-1][1] == rows
+            assert all(x[1] == y[0] for x, y in zip(b, b[1:])) and all(x[1] > x[0] for x in b)
+    sizes = [r1 - r0 for r0, r1 in TpGlue.chunk_bounds(16384, 8)]
+    assert sizes == [2048] * 7 + [1024, 512, 256, 256]             # the tail nothing overlaps is one small chunk
+
+
 def test_dropin_cubins_export_reference_entry_names():
     """Every cubin built for a reference module name contains the entry names the manifest launches."""
     cdir = os.path.join(ROOT, "kern-k3_b200", "lib", "cubin")

@@ -626,9 +626,16 @@ def run_gpu(args, rank, world, local_rank):
     e2e_steps = max(3, min(args.steps, 10))
     e2e_serial_us = timed(lambda: glue.step_host(hp, hr, ho, hq, hs), e2e_steps, 3)
     glue.check_status()
-    e2e_us = timed(lambda: glue.step_host_pipelined(hp, hr, ho, hq, hs, chunks=8), e2e_steps, 3)
+    # 8 equal parts, or the same with the last part cut again (1/2, 1/4, 1/8, 1/8): the shorter tail pays on one GPU, the
+    # extra protocol rounds can cost more than they save across GPUs; both are timed, the better one is reported
+    e2e_equal_us = timed(lambda: glue.step_host_pipelined(hp, hr, ho, hq, hs, chunks=8, taper=0), e2e_steps, 3)
     glue.check_status()
-    e2e_mode = "row-chunked, 3 streams (H2D / kernels / D2H overlapped), 8 parts with the last one cut again into 1/2, 1/4, 1/8, 1/8 (11 chunks)"
+    e2e_taper_us = timed(lambda: glue.step_host_pipelined(hp, hr, ho, hq, hs, chunks=8, taper=3), e2e_steps, 3)
+    glue.check_status()
+    if e2e_taper_us < e2e_equal_us:
+        e2e_us, e2e_mode = e2e_taper_us, "row-chunked, 3 streams (H2D / kernels / D2H overlapped), 8 parts with the last one cut again into 1/2, 1/4, 1/8, 1/8 (11 chunks)"
+    else:
+        e2e_us, e2e_mode = e2e_equal_us, "row-chunked, 3 streams (H2D / kernels / D2H overlapped), 8 equal chunks"
     if e2e_serial_us < e2e_us:
         e2e_us, e2e_mode = e2e_serial_us, "serial: copy in, graph replay, copy out"
 
@@ -692,7 +699,7 @@ def run_gpu(args, rank, world, local_rank):
             "ms_per_step": round(step_us / 1e3, 5), "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(W), "verified_rows": verified_rows, "mismatches": mismatches,
             "clocks": clocks, "roofline": roof, "nvlink": nv, "collectives": coll, "launch_mode": "cuda graph replay of 4 kernels per step (epoch bump, arrive, fused kernel, arrive)",
-            "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps, "mode": e2e_mode, "serial_us": round(e2e_serial_us, 1)},
+            "e2e": {"value": round(e2e_us, 1), "unit": UNIT, "h2d_bytes_per_step": glue.h2d_bytes(), "d2h_bytes_per_step": glue.d2h_bytes(), "steps": e2e_steps, "mode": e2e_mode, "serial_us": round(e2e_serial_us, 1), "equal_chunks_us": round(e2e_equal_us, 1), "tapered_us": round(e2e_taper_us, 1)},
             "gpu_launches": LAUNCHES_PER_STEP * args.steps, "eager_step_us": round(eager_us, 2), "tokens_per_s": round(TOKENS / step_us * 1e6)}
     if not args.no_ops:
         glue.close(); glue = None

@@ -108,7 +108,7 @@ class TpGlue:
             bounds.append((r, rows))
         return bounds
 
-    def step_host_pipelined(self, host_partial, host_residual, host_residual_out, host_q_all, host_sf_all, chunks=8):
+    def step_host_pipelined(self, host_partial, host_residual, host_residual_out, host_q_all, host_sf_all, chunks=8, taper=3):
         """step_host with the shard cut into row chunks (chunk_bounds: equal parts with a tapered tail) and three
         streams: while chunk c is reduced, normalised and gathered, chunk c + 1 is on its way in and chunk c - 1 on its
         way out, so the host link is busy in both directions at once.  Each chunk is a full protocol round (epoch bump,
@@ -120,7 +120,7 @@ class TpGlue:
         for st in (self._s_in, self._s_cmp, self._s_out):
             st.wait_event(start)
         R, W = self.rows, self.world
-        for r0, r1 in self.chunk_bounds(R, chunks):
+        for r0, r1 in self.chunk_bounds(R, chunks, taper):
             with torch.cuda.stream(self._s_in):
                 for q in range(W):
                     self.partial[q * R + r0:q * R + r1].copy_(host_partial[q * R + r0:q * R + r1], non_blocking=True)
